@@ -1,0 +1,88 @@
+"""In-tree build of ``libcatcoc_b200.so`` with nvcc for sm_100a.
+
+The library is a plain C-ABI shared object (no Python or torch headers), loaded through
+ctypes by :mod:`mm_rs_with_catlass_b200._native`. Building takes a few seconds and needs no
+GPU; the result is written next to the sources under ``_lib/`` so it travels with the tree.
+"""
+from __future__ import annotations
+
+import hashlib
+import os
+import shutil
+import subprocess
+import sys
+from pathlib import Path
+
+PKG_DIR = Path(__file__).resolve().parent
+CSRC = PKG_DIR / "csrc"
+LIB_DIR = PKG_DIR / "_lib"
+LIB_PATH = LIB_DIR / "libcatcoc_b200.so"
+STAMP_PATH = LIB_DIR / "build.stamp"
+
+SOURCES = [
+    "kernels/launch.cu",
+    "kernels/shmem_prims.cu",
+    "kernels/no_alloc.cu",
+    "shmem/host.cu",
+    "oracle/oracle.cpp",
+]
+
+NVCC_FLAGS = [
+    "-gencode", "arch=compute_100a,code=sm_100a",
+    "-lineinfo", "-O3", "-std=c++17",
+    "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=default",
+    "--expt-relaxed-constexpr",
+    "-shared",
+]
+
+
+def _nvcc() -> str:
+    cand = os.environ.get("CATCOC_NVCC") or shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    if not Path(cand).exists():
+        raise RuntimeError("nvcc not found; set CATCOC_NVCC")
+    return cand
+
+
+def _existing_sources() -> list[Path]:
+    return [CSRC / s for s in SOURCES if (CSRC / s).exists()]
+
+
+def source_digest() -> str:
+    h = hashlib.sha256()
+    files = sorted(list(CSRC.rglob("*.cu")) + list(CSRC.rglob("*.cuh")) + list(CSRC.rglob("*.h"))
+                   + list(CSRC.rglob("*.cpp")))
+    for f in files:
+        h.update(str(f.relative_to(CSRC)).encode())
+        h.update(f.read_bytes())
+    h.update(" ".join(NVCC_FLAGS).encode())
+    return h.hexdigest()
+
+
+def is_current() -> bool:
+    return LIB_PATH.exists() and STAMP_PATH.exists() and STAMP_PATH.read_text().strip() == source_digest()
+
+
+def build(force: bool = False, verbose: bool = False) -> Path:
+    """Compile every CUDA source of the package into one shared library (sm_100a)."""
+    if not force and is_current():
+        return LIB_PATH
+    LIB_DIR.mkdir(exist_ok=True)
+    cmd = [_nvcc(), *NVCC_FLAGS, "-I", str(CSRC / "include")]
+    if verbose:
+        cmd += ["-Xptxas", "-v"]
+    cmd += [str(s) for s in _existing_sources()]
+    tmp = LIB_PATH.with_suffix(".so.tmp%d" % os.getpid())
+    cmd += ["-o", str(tmp)]
+    proc = subprocess.run(cmd, capture_output=True, text=True)
+    if proc.returncode != 0:
+        tmp.unlink(missing_ok=True)
+        raise RuntimeError("nvcc failed:\n%s\n%s" % (" ".join(cmd), proc.stderr[-8000:]))
+    if verbose:
+        sys.stderr.write(proc.stderr)
+    os.replace(tmp, LIB_PATH)
+    STAMP_PATH.write_text(source_digest())
+    return LIB_PATH
+
+
+if __name__ == "__main__":
+    print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))

@@ -1,0 +1,160 @@
+/* C ABI of libcatcoc_b200.so. Everything the Python layer (ctypes) and plain C/C++ callers use.
+ *
+ * Conventions: functions return 0 on success and a negative CATCOC_E_* code (or a positive
+ * cudaError_t / CUresult passed through as -1000-code) on failure; catcoc_last_error() returns
+ * a human-readable description of the most recent failure on the calling thread.
+ *
+ * The op entry points play the role of the reference's launcher functions
+ * (examples/dynamic_tiling/include/launch_map.h:18-19, impl/kernel_fp16.cpp:22-86) and its
+ * per-op __global__ wrappers (examples/00_matmul_allreduce/matmul_allreduce.cpp:50-169). */
+#pragma once
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define CATCOC_MAX_WORLD 8
+
+enum {
+  CATCOC_OK = 0,
+  CATCOC_E_BAD_ARG = -1,
+  CATCOC_E_ALIGNMENT = -2,   /* operand base / leading dimension not 16-byte aligned for TMA */
+  CATCOC_E_DRIVER = -3,
+  CATCOC_E_UNSUPPORTED = -4,
+  CATCOC_E_NOMEM = -5,
+  CATCOC_E_IO = -6,
+  CATCOC_E_TOO_LARGE = -7,
+};
+
+/* operand element formats */
+enum { CATCOC_IN_F16 = 0, CATCOC_IN_BF16 = 1, CATCOC_IN_S8 = 2, CATCOC_IN_E4M3 = 3,
+       CATCOC_IN_E5M2 = 4 };
+/* output / partial element formats (== catcoc::ElemFmt) */
+enum { CATCOC_FMT_F16 = 0, CATCOC_FMT_BF16 = 1, CATCOC_FMT_F32 = 2, CATCOC_FMT_S32 = 3 };
+/* op modes (== catcoc::FusedMode) */
+enum { CATCOC_MODE_LOCAL = 0, CATCOC_MODE_RS = 1, CATCOC_MODE_AR = 2, CATCOC_MODE_AG = 3 };
+
+/* Communication tiling. Field-for-field superset of the reference's CocTilingParams
+ * (examples/dynamic_tiling/include/info.h:29-42); see tiling/config.py for the mapping. */
+typedef struct CatcocTiling {
+  int bn;          /* tile columns: 64, 128 or 256 (0 = default 256)                    */
+  int swizzle;     /* tiles per column group of the raster (0 = default)                */
+  int num_ctas;    /* persistent CTAs (0 = one per SM)                                   */
+  int seg_dim;     /* all-reduce ownership split: 0 rows, 1 cols, -1 auto                */
+  int use_multicast; /* all-reduce broadcast through the NVLS multicast alias if mapped  */
+} CatcocTiling;
+
+typedef struct CatcocOpArgs {
+  int mode;                /* CATCOC_MODE_*                                              */
+  int in_fmt;              /* CATCOC_IN_*                                                */
+  int M, N, K;             /* output grid rows (all-gather: W * m), cols, local K        */
+  int trans_a, trans_b;    /* storage: A is [K, M] if trans_a, B is [N, K] if trans_b    */
+  const void* a; int64_t lda;   /* leading dimension (elements) of the stored matrix     */
+  const void* b; int64_t ldb;
+  void* out; int64_t ldc; int out_fmt;
+  CatcocTiling tiling;
+
+  /* distributed part (ignored when W <= 1 or mode == LOCAL) */
+  int rank, W;
+  int partial_fmt;                         /* format of tiles crossing NVLink            */
+  void* stage[CATCOC_MAX_WORLD];           /* staging slabs, one base per rank           */
+  uint32_t* arrive[CATCOC_MAX_WORLD];      /* arrival stamps                             */
+  void* ar_out[CATCOC_MAX_WORLD];          /* all-reduce output (parity 0) on every rank */
+  int64_t ar_out_parity_bytes;
+  void* ar_out_mc;                         /* multicast alias or NULL                    */
+  uint32_t* done[CATCOC_MAX_WORLD];
+  uint32_t* done_mc;
+  void* gathered[CATCOC_MAX_WORLD];        /* all-gather: gathered A (parity 0)          */
+  int64_t gathered_parity_bytes;
+  uint32_t* gflags[CATCOC_MAX_WORLD];
+  int ag_m;                                /* all-gather: rows of one shard              */
+
+  /* quantised epilogue */
+  const float* scale_m; const float* scale_n; const int32_t* bias;
+
+  uint32_t* epoch_ptr; uint32_t* cta_counter; uint32_t* status;
+  uint64_t timeout_ns;
+  int withhold_signals;
+} CatcocOpArgs;
+
+const char* catcoc_last_error(void);
+int catcoc_version(void);
+
+/* Launches the fused kernel on `stream` (a cudaStream_t). */
+int catcoc_fused_launch(const CatcocOpArgs* args, void* stream);
+
+/* Workspace sizes (bytes / words) for given problem + tiling, identical on every rank. */
+int64_t catcoc_stage_bytes(int M, int N, int W, int seg_dim, int bn, int partial_fmt);
+int64_t catcoc_arrive_words(int M, int N, int W, int seg_dim, int bn);
+int64_t catcoc_done_words(int M, int N, int W, int seg_dim, int bn);
+int64_t catcoc_gather_flag_words(int m, int K, int W, int elt_bytes);
+int catcoc_num_sms(int device);
+
+/* ---- scheduler introspection (host-side replay of the device index math, for tests) ---- */
+typedef struct CatcocTile {
+  int seg, tile_in_seg, mi, ni, m0, n0, rows, cols;
+} CatcocTile;
+int catcoc_sched_total_tiles(int M, int N, int bm, int bn, int W, int seg_dim);
+int catcoc_sched_get_tile(int M, int N, int bm, int bn, int W, int seg_dim, int first_seg,
+                          int swizzle, int t, CatcocTile* out);
+
+/* ---- CPU oracle (naive fp32 / int32 loops; see csrc/oracle/oracle.cpp) ---- */
+int catcoc_oracle_matmul_f32(const float* a, const float* b, float* c, int M, int N, int K,
+                             int trans_a, int trans_b);
+int catcoc_oracle_quant_matmul(const int8_t* a, const int8_t* b, const int32_t* bias,
+                               int32_t* acc, int M, int N, int K, int trans_a, int trans_b);
+int catcoc_oracle_dequant(const int32_t* acc, const float* scale_m, const float* scale_n,
+                          float* out, int M, int N);
+int64_t catcoc_oracle_compare(const float* out, const float* golden, int64_t n, float rtol,
+                              double* mean_rel_bias);
+
+/* ---- symmetric heap (csrc/shmem/host.cu) ---- */
+typedef struct CatcocHeap CatcocHeap;
+int catcoc_heap_create(int device, int rank, int world, int64_t bytes, CatcocHeap** out);
+int64_t catcoc_heap_bytes(const CatcocHeap* h);          /* rounded-up size per rank       */
+int catcoc_heap_export_fd(CatcocHeap* h);                /* POSIX fd of the local handle   */
+int catcoc_heap_import_peer(CatcocHeap* h, int peer, int fd);  /* map a peer's handle      */
+void* catcoc_heap_base(const CatcocHeap* h, int peer);   /* address of rank `peer`'s heap  */
+int catcoc_heap_multicast_supported(int device);
+int catcoc_heap_mc_create(CatcocHeap* h);                /* rank 0: create + return fd     */
+int catcoc_heap_mc_join(CatcocHeap* h, int fd);          /* all: import (fd<0: own) + add device */
+int catcoc_heap_mc_bind(CatcocHeap* h);                  /* all, after every rank joined   */
+void* catcoc_heap_mc_base(const CatcocHeap* h);          /* multicast alias or NULL        */
+int catcoc_heap_destroy(CatcocHeap* h);
+/* fd passing between local processes over an abstract unix socket */
+int catcoc_fd_send(const char* sock_name, int fd, int timeout_ms);
+int catcoc_fd_recv_open(const char* sock_name);          /* returns listening socket       */
+int catcoc_fd_recv(int listen_sock, int timeout_ms);     /* returns received fd            */
+int catcoc_fd_close(int fd);
+
+/* ---- device primitive kernels (csrc/kernels/shmem_prims.cu), used by tests and the heap ---- */
+typedef struct CatcocShmemCtx {
+  int rank, W;
+  void* base[CATCOC_MAX_WORLD];   /* heap base of every rank in this process's address space */
+  void* mc_base;                  /* multicast alias or NULL */
+  uint32_t* signal_off;           /* unused */
+  int64_t barrier_off;            /* byte offset of the barrier stamp array in the heap */
+  int64_t scratch_off;
+} CatcocShmemCtx;
+int catcoc_shmem_barrier_all(const CatcocShmemCtx* ctx, uint32_t epoch, uint64_t timeout_ns,
+                             uint32_t* status, void* stream);
+int catcoc_shmem_put(const CatcocShmemCtx* ctx, int peer, int64_t dst_off, const void* src,
+                     int64_t bytes, int64_t signal_off, uint32_t signal_val, void* stream);
+int catcoc_shmem_get(const CatcocShmemCtx* ctx, int peer, void* dst, int64_t src_off,
+                     int64_t bytes, void* stream);
+int catcoc_shmem_wait_until(const CatcocShmemCtx* ctx, int64_t signal_off, uint32_t value,
+                            uint64_t timeout_ns, uint32_t* status, void* stream);
+int catcoc_shmem_mc_broadcast(const CatcocShmemCtx* ctx, int64_t dst_off, const void* src,
+                              int64_t bytes, void* stream);
+int catcoc_shmem_mc_reduce_bf16(const CatcocShmemCtx* ctx, void* dst, int64_t src_off,
+                                int64_t n_elems, void* stream);
+
+int catcoc_shmem_put_blocks(void);  /* blocks a put launches: each adds signal_val once */
+/* copy rows into a buffer whose pitch is TMA-legal, zero-filling the padding */
+int catcoc_pad2d(void* dst, int64_t dst_pitch, const void* src, int64_t src_pitch, int64_t rows,
+                 int64_t row_bytes, void* stream);
+
+#ifdef __cplusplus
+}
+#endif

@@ -1,0 +1,670 @@
+// The one persistent, warp-specialised sm_100a kernel behind every op of this library.
+//
+//   warp 0      TMA producer   : cp.async.bulk.tensor A/B K-slices -> 128B-swizzled smem ring
+//   warp 1      MMA issuer     : one thread issues tcgen05.mma into a double-buffered TMEM
+//                                accumulator, tcgen05.commit frees smem stages / publishes tiles
+//   warps 2..5  epilogue       : tcgen05.ld -> convert -> smem staging -> coalesced 16 B stores
+//                                to local memory, to a peer's staging slab (NVLink P2P) or to
+//                                every rank's output (P2P or multimem.st); owner tiles fold the
+//                                peers' partials into the fp32 / int32 accumulator first
+//   warps 6..7  communication  : all-gather only: push this rank's A shard to the peers
+//
+// The collective is expressed inside the tile loop (see sched.h for the visiting order), so
+// transfers overlap the tensor-core work tile by tile and no NCCL call is involved.
+//
+// Cross-GPU synchronisation uses epoch stamps: a producer writes the launch's epoch number into
+// a per-(tile, source) word with st.release.sys after its data; a consumer polls with
+// ld.acquire.sys until the stamp reaches the epoch. Stamps are never reset, staging buffers are
+// double-buffered by epoch parity, and every wait is bounded (status word + clean return).
+//
+// Roles of the reference this kernel replaces (different construction, same jobs):
+//   include/catcoc/dgemm/kernel/matmul_allreduce.hpp:114-313
+//   include/catcoc/dgemm/kernel/allgather_matmul.hpp:108-263
+//   include/catcoc/dgemm/kernel/matmul_reduce_scatter.hpp:107-298
+//   include/catcoc/dgemm/kernel/quant_matmul_reduce_scatter.hpp:116-351
+//   3rdparty/catlass/include/catlass/gemm/block/block_mmad_pingpong.hpp:181-319
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include "catcoc/params.h"
+#include "catcoc/ptx.cuh"
+
+namespace catcoc {
+
+constexpr int kBM = 128;               // tile rows == UMMA M == TMEM lanes
+constexpr int kMaxBN = 256;            // tile cols upper bound == TMEM columns per accumulator
+constexpr int kStages = 4;             // smem ring depth
+constexpr int kABytes = kBM * 128;     // A stage: 128 rows x 128 B (K-major) or the MN-major equal
+constexpr int kBBytesMax = kMaxBN * 128;
+constexpr int kStageBytes = kABytes + kBBytesMax;  // 48 KiB
+constexpr int kEpiWarps = 4;
+constexpr int kEpiStageBytes = 32 * 128;           // per epilogue warp: 32 rows x 128 B
+constexpr int kThreads = 256;
+constexpr int kTmemCols = 512;
+constexpr int kSmemBytes =
+    kStages * kStageBytes + kEpiWarps * kEpiStageBytes + 256 /*barriers*/ + 1024 /*align slack*/;
+
+struct SmemTail {
+  uint64_t full[kStages];
+  uint64_t empty[kStages];
+  uint64_t acc_full[2];
+  uint64_t acc_empty[2];
+  uint32_t tmem_base;
+  uint32_t abort_flag;
+};
+
+CATCOC_DEVICE void report_status(const FusedParams& p, uint32_t code, uint32_t what,
+                                 uint32_t expected, uint32_t seen, uint32_t peer) {
+  if (p.status == nullptr) return;
+  if (atomicCAS(p.status, 0u, code) == 0u) {
+    p.status[1] = static_cast<uint32_t>(p.rank);
+    p.status[2] = what;
+    p.status[3] = expected;
+    p.status[4] = seen;
+    p.status[5] = peer;
+    p.status[6] = blockIdx.x;
+    __threadfence_system();
+  }
+}
+
+// Polls a stamp until it reaches `epoch` (wrap-safe), the time budget ends or the CTA aborts.
+CATCOC_DEVICE bool wait_stamp(const uint32_t* flag, uint32_t epoch, uint64_t timeout_ns,
+                              volatile uint32_t* abort_flag, uint32_t* seen) {
+  uint32_t v = ptx::ld_acquire_sys_u32(flag);
+  if (static_cast<int32_t>(v - epoch) >= 0) return true;
+  const uint64_t t0 = ptx::globaltimer_ns();
+  uint32_t spins = 0;
+  while (true) {
+    v = ptx::ld_acquire_sys_u32(flag);
+    if (static_cast<int32_t>(v - epoch) >= 0) return true;
+    if ((++spins & 0xf) == 0) {
+      if (*abort_flag || ptx::globaltimer_ns() - t0 > timeout_ns) {
+        *seen = v;
+        return false;
+      }
+      __nanosleep(64);
+    }
+  }
+}
+
+// ---- value conversion helpers ---------------------------------------------------------
+CATCOC_DEVICE uint32_t pack2(float a, float b, int fmt) {
+  if (fmt == FMT_BF16) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&h);
+  }
+  __half2 h = __floats2half2_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+CATCOC_DEVICE float2 unpack2(uint32_t u, int fmt) {
+  if (fmt == FMT_BF16) {
+    __nv_bfloat162 h = *reinterpret_cast<__nv_bfloat162*>(&u);
+    return __bfloat1622float2(h);
+  }
+  __half2 h = *reinterpret_cast<__half2*>(&u);
+  return __half22float2(h);
+}
+
+// ---- epilogue staging -----------------------------------------------------------------
+// Each epilogue warp owns a 32 x 128 B staging area. Thread `lane` (one tile row) writes
+// 16-byte units at a position XOR-swizzled with the row so that neither the row-wise writes
+// nor the unit-wise reads conflict on banks.
+CATCOC_DEVICE void stage_write(uint32_t stg, int lane, int unit, uint4 v) {
+  ptx::st_shared_v4(stg + lane * 128 + ((unit ^ (lane & 7)) << 4), v);
+}
+
+// Writes the staged 32 x 128 B block out. Lanes cooperate so that 8 lanes cover one 128-byte
+// row segment. `cols_valid` counts elements of `elt` bytes inside the matrix within this
+// 128-byte window; `rows_valid` in [0, 32]. Destinations:
+//   mc != nullptr          : one multimem.st per unit reaches every rank (aligned tiles only)
+//   peer_bases != nullptr  : the same block goes to peer_bases[rank], [rank+1], ... (+ off)
+//   otherwise              : `base` only
+CATCOC_DEVICE void flush_staged(uint32_t stg, int lane, uint8_t* base, int64_t pitch,
+                                int rows_valid, int cols_valid, int elt, bool vec_ok,
+                                uint8_t* mc, uint8_t* const* peer_bases, int64_t off, int rank,
+                                int W) {
+  const int unit = lane & 7;
+  const int per_unit = 16 / elt;
+  const int c0 = unit * per_unit;
+  const int ndst = (peer_bases != nullptr) ? W : 1;
+#pragma unroll
+  for (int it = 0; it < 8; ++it) {
+    const int row = it * 4 + (lane >> 3);
+    const uint4 v = ptx::ld_shared_v4(stg + row * 128 + ((unit ^ (row & 7)) << 4));
+    if (row < rows_valid && c0 < cols_valid) {
+      const int64_t rel = row * pitch + unit * 16;
+      const bool full = vec_ok && (c0 + per_unit <= cols_valid);
+      if (mc != nullptr) {
+        ptx::multimem_st_v4(mc + rel, v);
+      } else {
+        for (int d = 0; d < ndst; ++d) {
+          uint8_t* ptr = (peer_bases != nullptr)
+                             ? peer_bases[peer_for_push_rs(rank, d, W)] + off + rel
+                             : base + rel;
+          if (full) {
+            ptx::st_global_v4(ptr, v);
+          } else {
+            const int n = min(per_unit, cols_valid - c0);
+            const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+            if (elt == 2) {
+              for (int e = 0; e < n; ++e)
+                *reinterpret_cast<uint16_t*>(ptr + e * 2) =
+                    static_cast<uint16_t>(w[e >> 1] >> ((e & 1) * 16));
+            } else {
+              for (int e = 0; e < n; ++e) *reinterpret_cast<uint32_t*>(ptr + e * 4) = w[e];
+            }
+          }
+        }
+      }
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// The kernel
+// ---------------------------------------------------------------------------------------
+template <int KIND>
+__global__ void __launch_bounds__(kThreads, 1)
+fused_gemm_kernel(const __grid_constant__ FusedParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>(
+      (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  uint8_t* epi_stage = smem + kStages * kStageBytes;
+  SmemTail* tail = reinterpret_cast<SmemTail*>(epi_stage + kEpiWarps * kEpiStageBytes);
+  volatile uint32_t* abort_flag = &tail->abort_flag;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const TileSched& sched = p.sched;
+  const int BN = sched.BN;
+  const int num_kb = ceil_div(p.K, p.bk);
+  const uint32_t b_stage_bytes = static_cast<uint32_t>(BN) * 128u;
+  const bool fused = (p.mode != MODE_LOCAL) && (p.W > 1);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      ptx::mbar_init(&tail->full[s], 1);
+      ptx::mbar_init(&tail->empty[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      ptx::mbar_init(&tail->acc_full[b], 1);
+      ptx::mbar_init(&tail->acc_empty[b], kEpiWarps);
+    }
+    tail->abort_flag = 0;
+    ptx::mbar_fence_init();
+    ptx::prefetch_tmap(&p.tm_a);
+    ptx::prefetch_tmap(&p.tm_b);
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc(&tail->tmem_base, kTmemCols);
+    ptx::tmem_relinquish();
+  }
+  ptx::tcgen05_fence_before();
+  __syncthreads();
+  ptx::tcgen05_fence_after();
+  const uint32_t tmem_base = tail->tmem_base;
+
+  // Epoch of this launch: completed launches + 1. Read before any CTA can finish.
+  uint32_t epoch = 1;
+  if (fused) epoch = ptx::ld_relaxed_sys_u32(p.epoch_ptr) + 1;
+  const int parity = static_cast<int>(epoch & 1u);
+
+  if (warp == 0) {
+    // =============================== TMA producer ===============================
+    int stage = 0;
+    uint32_t phase = 0;
+    uint32_t issued_mask = 0, issued_parity = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; ok && t < sched.total_tiles; t += gridDim.x) {
+      const TileInfo ti = get_tile(sched, t);
+      const CUtensorMap* tma = &p.tm_a;
+      int a_row = ti.m0;
+      if (p.mode == MODE_AG && p.W > 1) {
+        if (ti.seg == p.rank) {
+          a_row = ti.mi * sched.BM;  // row inside the local shard
+        } else {
+          // wait until every K-slice of this row chunk of source `seg` has landed here
+          const uint32_t* fl = p.gflags[p.rank];
+          for (int s = lane; ok && s < p.gp.n_slices; s += 32) {
+            uint32_t seen = 0;
+            const int64_t idx = gather_flag_index(p.gp, ti.seg, ti.mi, s);
+            if (!wait_stamp(fl + idx, epoch, p.timeout_ns, abort_flag, &seen)) {
+              report_status(p, STATUS_TIMEOUT_GATHER, static_cast<uint32_t>(idx), epoch, seen,
+                            static_cast<uint32_t>(ti.seg));
+              *abort_flag = 1;
+              ok = false;
+            }
+          }
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+          ptx::fence_proxy_async();  // peer-written rows are about to be read by TMA
+          tma = &p.tm_a_gath[parity];
+        }
+      }
+      for (int kb = 0; kb < num_kb; ++kb) {
+        if (!ptx::mbar_wait(&tail->empty[stage], phase ^ 1u, p.timeout_ns, abort_flag)) {
+          if (lane == 0) {
+            report_status(p, STATUS_TIMEOUT_PIPELINE, 0u, static_cast<uint32_t>(t),
+                          static_cast<uint32_t>(kb), 0u);
+            *abort_flag = 1;
+          }
+          ok = false;
+          break;
+        }
+        if (lane == 0) {
+          uint8_t* sa = smem + stage * kStageBytes;
+          uint8_t* sb = sa + kABytes;
+          ptx::mbar_expect_tx(&tail->full[stage], kABytes + b_stage_bytes);
+          const int k0 = kb * p.bk;
+          if (!p.a_mn_major) {
+            ptx::tma_load_2d(sa, tma, &tail->full[stage], k0, a_row);
+          } else {
+            // storage [K, M]: boxes of 128 B along M x bk rows of K
+            const int per_box = 128 / p.elt_bytes_a;
+            const int nbox = kBM / per_box;
+            for (int j = 0; j < nbox; ++j)
+              ptx::tma_load_2d(sa + j * (p.bk * 128), tma, &tail->full[stage],
+                               a_row + j * per_box, k0);
+          }
+          if (!p.b_mn_major) {
+            ptx::tma_load_2d(sb, &p.tm_b, &tail->full[stage], k0, ti.n0);
+          } else {
+            const int per_box = 128 / p.elt_bytes_a;
+            const int nbox = BN / per_box;
+            for (int j = 0; j < nbox; ++j)
+              ptx::tma_load_2d(sb + j * (p.bk * 128), &p.tm_b, &tail->full[stage],
+                               ti.n0 + j * per_box, k0);
+          }
+          issued_mask |= 1u << stage;
+          issued_parity = (issued_parity & ~(1u << stage)) | (phase << stage);
+        }
+        __syncwarp();
+        if (++stage == kStages) { stage = 0; phase ^= 1u; }
+      }
+    }
+    if (*abort_flag && lane == 0) {
+      // let every bulk copy this thread started land before the CTA's smem goes away
+      volatile uint32_t never = 0;
+      for (int s = 0; s < kStages; ++s)
+        if (issued_mask & (1u << s))
+          ptx::mbar_wait(&tail->full[s], (issued_parity >> s) & 1u, 2000000ull, &never);
+    }
+  } else if (warp == 1) {
+    // =============================== MMA issuer ===============================
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      const uint32_t a_lbo = p.a_mn_major ? static_cast<uint32_t>(p.bk) * 128u : 16u;
+      const uint32_t b_lbo = p.b_mn_major ? static_cast<uint32_t>(p.bk) * 128u : 16u;
+      const uint32_t a_kstep = p.a_mn_major ? static_cast<uint32_t>(p.umma_k) * 128u : 32u;
+      const uint32_t b_kstep = p.b_mn_major ? static_cast<uint32_t>(p.umma_k) * 128u : 32u;
+      const int k_per_stage = p.bk / p.umma_k;
+      for (int t = blockIdx.x; ok && t < sched.total_tiles; t += gridDim.x) {
+        if (!ptx::mbar_wait(&tail->acc_empty[acc], acc_phase ^ 1u, p.timeout_ns, abort_flag)) {
+          report_status(p, STATUS_TIMEOUT_PIPELINE, 1u, static_cast<uint32_t>(t), 0u, 0u);
+          *abort_flag = 1;
+          break;
+        }
+        ptx::tcgen05_fence_after();
+        const uint32_t tmem_d = tmem_base + static_cast<uint32_t>(acc * kMaxBN);
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!ptx::mbar_wait(&tail->full[stage], phase, p.timeout_ns, abort_flag)) {
+            report_status(p, STATUS_TIMEOUT_PIPELINE, 2u, static_cast<uint32_t>(t),
+                          static_cast<uint32_t>(kb), 0u);
+            *abort_flag = 1;
+            ok = false;
+            break;
+          }
+          ptx::tcgen05_fence_after();
+          const uint32_t sa = ptx::smem_u32(smem + stage * kStageBytes);
+          const uint32_t sb = sa + kABytes;
+          // K tail: the last stage may hold fewer than bk valid K elements; TMA zero-fills the
+          // rest, so the extra MMAs add zeros and are simply skipped when entirely out of range.
+          const int k_left = p.K - kb * p.bk;
+          const int nk = min(k_per_stage, ceil_div(k_left, p.umma_k));
+          for (int k = 0; k < nk; ++k) {
+            const uint64_t da = ptx::make_smem_desc_sw128(sa + k * a_kstep, a_lbo, 1024u);
+            const uint64_t db = ptx::make_smem_desc_sw128(sb + k * b_kstep, b_lbo, 1024u);
+            const uint32_t accum = (kb | k) != 0 ? 1u : 0u;
+            if (KIND == KIND_F16) ptx::umma_f16(tmem_d, da, db, p.idesc, accum);
+            else if (KIND == KIND_I8) ptx::umma_i8(tmem_d, da, db, p.idesc, accum);
+            else ptx::umma_f8f6f4(tmem_d, da, db, p.idesc, accum);
+          }
+          ptx::tcgen05_commit(&tail->empty[stage]);
+          if (++stage == kStages) { stage = 0; phase ^= 1u; }
+        }
+        if (!ok) break;
+        ptx::tcgen05_commit(&tail->acc_full[acc]);
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1u;
+      }
+      if (*abort_flag) {
+        // wait (bounded) for the tensor core to retire what was issued before TMEM is freed
+        volatile uint32_t never = 0;
+        ptx::tcgen05_commit(&tail->acc_full[acc]);
+        ptx::mbar_wait(&tail->acc_full[acc], acc_phase, 2000000ull, &never);
+      }
+    }
+  } else if (warp < 2 + kEpiWarps) {
+    // =============================== epilogue ===============================
+    // The four epilogue warps never synchronise with each other: warp q owns tile rows
+    // [32q, 32q+32) end to end, including their stamps, so a warp that gives up on a wait
+    // cannot strand the others at a barrier.
+    const int q = warp & 3;                 // TMEM lane quarter this warp may read
+    const uint32_t stg = ptx::smem_u32(epi_stage + (warp - 2) * kEpiStageBytes);
+    const int row_in_tile = q * 32 + lane;
+    const bool is_int = (KIND == KIND_I8);
+    const bool dequant = (p.scale_m != nullptr) || (p.scale_n != nullptr);
+    const int pfmt = p.partial_fmt;
+    const int pelt = fmt_bytes(pfmt);
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    bool ok = true;
+
+    for (int t = blockIdx.x; ok && t < sched.total_tiles; t += gridDim.x) {
+      const TileInfo ti = get_tile(sched, t);
+      const bool own = !fused || (p.mode == MODE_AG) || (ti.seg == p.rank);
+      const bool reduce_here = fused && own && (p.mode == MODE_RS || p.mode == MODE_AR);
+      const int st_fmt = own ? p.out_fmt : pfmt;   // format of what this tile's epilogue stores
+      const int st_elt = fmt_bytes(st_fmt);
+      const int rows_valid = max(0, min(32, ti.rows - q * 32));
+
+      if (reduce_here) {
+        // the peers' rows [32q, 32q+32) of this tile must have landed in my staging slabs
+        if (lane < p.W && lane != p.rank) {
+          uint32_t seen = 0;
+          const int64_t idx = arrive_flag_index(sched, ti.tile_in_seg, lane) * 4 + q;
+          if (!wait_stamp(p.arrive[p.rank] + idx, epoch, p.timeout_ns, abort_flag, &seen)) {
+            report_status(p, STATUS_TIMEOUT_ARRIVE, static_cast<uint32_t>(ti.tile_in_seg), epoch,
+                          seen, static_cast<uint32_t>(lane));
+            *abort_flag = 1;
+            ok = false;
+          }
+        }
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+      }
+
+      if (!ptx::mbar_wait(&tail->acc_full[acc], acc_phase, p.timeout_ns, abort_flag)) {
+        if (lane == 0) {
+          report_status(p, STATUS_TIMEOUT_PIPELINE, 3u, static_cast<uint32_t>(t), 0u, 0u);
+          *abort_flag = 1;
+        }
+        break;
+      }
+      ptx::tcgen05_fence_after();
+      const uint32_t taddr =
+          tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(acc * kMaxBN);
+
+      // Where this warp's 32 rows of the tile go.
+      uint8_t* base = nullptr;           // single destination
+      int64_t pitch = 0;
+      uint8_t* mc = nullptr;             // multicast destination
+      uint8_t* const* peer_bases = nullptr;  // broadcast by per-peer stores
+      int64_t off = 0;
+      bool vec_ok = true;
+      if (!own) {
+        pitch = static_cast<int64_t>(BN) * st_elt;
+        base = p.stage[ti.seg] + stage_slot_offset(sched, st_elt, parity, p.rank, ti.tile_in_seg) +
+               static_cast<int64_t>(q * 32) * pitch;
+      } else if (fused && p.mode == MODE_AR) {
+        pitch = p.ldc * st_elt;
+        off = static_cast<int64_t>(parity) * p.ar_out_parity_bytes +
+              (static_cast<int64_t>(ti.m0 + q * 32) * p.ldc + ti.n0) * st_elt;
+        vec_ok = p.out_vec_ok != 0;
+        if (p.ar_out_mc != nullptr && vec_ok && (ti.cols % (16 / st_elt) == 0)) {
+          mc = p.ar_out_mc + off;
+        } else {
+          peer_bases = p.ar_out;
+        }
+      } else {
+        pitch = p.ldc * st_elt;
+        base = static_cast<uint8_t*>(p.out) +
+               (static_cast<int64_t>(ti.m0 + q * 32 - p.out_row_shift) * p.ldc + ti.n0) * st_elt;
+        vec_ok = p.out_vec_ok != 0;
+      }
+
+      const int groups = BN / 32;                        // 32-column groups in the accumulator
+      const int groups_per_win = (st_elt == 2) ? 2 : 1;  // groups per 128 B window of output
+      const int nwin = groups / groups_per_win;
+      const int last_group = min(groups, ceil_div(ti.cols, 32)) - 1;
+      bool released = false;
+
+      for (int win = 0; win < nwin; ++win) {
+        if (win * groups_per_win * 32 >= ti.cols) break;
+        for (int h = 0; h < groups_per_win; ++h) {
+          const int g = win * groups_per_win + h;
+          const int col0 = g * 32;
+          if (col0 >= ti.cols) break;
+          uint32_t v[32];
+          ptx::tmem_ld_32x32b_x32(taddr + static_cast<uint32_t>(col0), v);
+          ptx::tcgen05_wait_ld();
+          if (g == last_group) {
+            // every TMEM read of this tile is done: hand the accumulator back to the MMA warp
+            ptx::tcgen05_fence_before();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(&tail->acc_empty[acc]);
+            released = true;
+          }
+
+          if (is_int && p.bias != nullptr) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              const int c = ti.n0 + col0 + j;
+              const int32_t b = (c < sched.N) ? __ldg(p.bias + c) : 0;
+              v[j] = static_cast<uint32_t>(static_cast<int32_t>(v[j]) + b);
+            }
+          }
+
+          if (reduce_here && row_in_tile < ti.rows) {
+            // fold the peers' partials in a fixed source order => deterministic sum
+            for (int src = 0; src < p.W; ++src) {
+              if (src == p.rank) continue;
+              const uint8_t* sp = p.stage[p.rank] +
+                                  stage_slot_offset(sched, pelt, parity, src, ti.tile_in_seg) +
+                                  (static_cast<int64_t>(row_in_tile) * BN + col0) * pelt;
+              if (pelt == 2) {
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                  const uint4 w = ptx::ld_global_v4(sp + u * 16);
+                  const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+                  for (int e = 0; e < 4; ++e) {
+                    const float2 f = unpack2(ww[e], pfmt);
+                    v[u * 8 + e * 2] = __float_as_uint(__uint_as_float(v[u * 8 + e * 2]) + f.x);
+                    v[u * 8 + e * 2 + 1] =
+                        __float_as_uint(__uint_as_float(v[u * 8 + e * 2 + 1]) + f.y);
+                  }
+                }
+              } else {
+#pragma unroll
+                for (int u = 0; u < 8; ++u) {
+                  const uint4 w = ptx::ld_global_v4(sp + u * 16);
+                  const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+                  for (int e = 0; e < 4; ++e) {
+                    if (pfmt == FMT_S32)
+                      v[u * 4 + e] = static_cast<uint32_t>(static_cast<int32_t>(v[u * 4 + e]) +
+                                                           static_cast<int32_t>(ww[e]));
+                    else
+                      v[u * 4 + e] = __float_as_uint(__uint_as_float(v[u * 4 + e]) +
+                                                     __uint_as_float(ww[e]));
+                  }
+                }
+              }
+            }
+          }
+
+          // convert this row's 32 values to the stored format and stage them
+          if (st_fmt == FMT_S32 || (st_fmt == FMT_F32 && !is_int && !(dequant && own))) {
+#pragma unroll
+            for (int u = 0; u < 8; ++u)
+              stage_write(stg, lane, u,
+                          make_uint4(v[u * 4], v[u * 4 + 1], v[u * 4 + 2], v[u * 4 + 3]));
+          } else {
+            float f[32];
+            if (is_int) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) f[j] = static_cast<float>(static_cast<int32_t>(v[j]));
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
+            }
+            if (dequant && own) {
+              const int grow = ti.m0 + row_in_tile;
+              const float sm =
+                  (p.scale_m != nullptr && grow < sched.M) ? __ldg(p.scale_m + grow) : 1.0f;
+#pragma unroll
+              for (int j = 0; j < 32; ++j) {
+                const int c = ti.n0 + col0 + j;
+                const float sn =
+                    (p.scale_n != nullptr && c < sched.N) ? __ldg(p.scale_n + c) : 1.0f;
+                f[j] = f[j] * sn * sm;
+              }
+            }
+            if (st_fmt == FMT_F32) {
+#pragma unroll
+              for (int u = 0; u < 8; ++u)
+                stage_write(stg, lane, u,
+                            make_uint4(__float_as_uint(f[u * 4]), __float_as_uint(f[u * 4 + 1]),
+                                       __float_as_uint(f[u * 4 + 2]),
+                                       __float_as_uint(f[u * 4 + 3])));
+            } else {
+#pragma unroll
+              for (int u = 0; u < 4; ++u)
+                stage_write(stg, lane, h * 4 + u,
+                            make_uint4(pack2(f[u * 8], f[u * 8 + 1], st_fmt),
+                                       pack2(f[u * 8 + 2], f[u * 8 + 3], st_fmt),
+                                       pack2(f[u * 8 + 4], f[u * 8 + 5], st_fmt),
+                                       pack2(f[u * 8 + 6], f[u * 8 + 7], st_fmt)));
+            }
+          }
+        }
+        __syncwarp();
+        {
+          const int per_win = 128 / st_elt;
+          const int cols_valid = min(per_win, ti.cols - win * per_win);
+          const int64_t wb = static_cast<int64_t>(win) * 128;
+          flush_staged(stg, lane, base != nullptr ? base + wb : nullptr, pitch, rows_valid,
+                       cols_valid, st_elt, vec_ok, mc != nullptr ? mc + wb : nullptr, peer_bases,
+                       off + wb, p.rank, p.W);
+        }
+        __syncwarp();
+      }
+      if (!released) {
+        // degenerate (empty) tile: nothing was read, still return the accumulator
+        ptx::tcgen05_fence_before();
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(&tail->acc_empty[acc]);
+      }
+
+      // ---- publish this warp's quarter of the tile ----
+      if (fused && (p.mode == MODE_RS || p.mode == MODE_AR) && (!own || p.mode == MODE_AR)) {
+        ptx::fence_acq_rel_sys();   // every lane: my stores before the stamp, system-wide
+        __syncwarp();
+        if (!p.withhold_signals) {
+          if (!own) {
+            if (lane == 0)
+              ptx::st_release_sys_u32(
+                  p.arrive[ti.seg] + arrive_flag_index(sched, ti.tile_in_seg, p.rank) * 4 + q,
+                  epoch);
+          } else {
+            // the reduced rows are in every rank's output: stamp them everywhere
+            const int gid = (ti.seg * sched.tiles_per_seg + ti.tile_in_seg) * 4 + q;
+            if (p.done_mc != nullptr && mc != nullptr) {
+              if (lane == 0) ptx::multimem_st_release_u32(p.done_mc + gid, epoch);
+            } else if (lane < p.W) {
+              ptx::st_release_sys_u32(p.done[lane] + gid, epoch);
+            }
+          }
+        }
+      }
+
+      acc ^= 1;
+      if (acc == 0) acc_phase ^= 1u;
+    }
+
+    // all-reduce tail: this rank's output is complete only when every owner's tiles landed
+    if (fused && p.mode == MODE_AR && ok && !*abort_flag) {
+      const int et = (warp - 2) * 32 + lane;
+      const int nstamps = sched.total_tiles * 4;
+      for (int j = blockIdx.x + et * gridDim.x; j < nstamps; j += gridDim.x * kEpiWarps * 32) {
+        uint32_t seen = 0;
+        if (!wait_stamp(p.done[p.rank] + j, epoch, p.timeout_ns, abort_flag, &seen)) {
+          report_status(p, STATUS_TIMEOUT_DONE, static_cast<uint32_t>(j), epoch, seen,
+                        static_cast<uint32_t>((j / 4) / sched.tiles_per_seg));
+          *abort_flag = 1;
+          break;
+        }
+      }
+    }
+  } else {
+    // ======================= communication warps (all-gather) =======================
+    // Push this rank's A shard into every rank's gathered buffer in units of
+    // chunk_rows x 512 B, peer-major: the peer that consumes the shard first is served first.
+    if (fused && p.mode == MODE_AG) {
+      const int cw = warp - (2 + kEpiWarps);
+      const int ncw = (kThreads / 32) - (2 + kEpiWarps);
+      const GatherPlan& gp = p.gp;
+      const int units_per_peer = gp.n_chunks * gp.n_slices;
+      const int64_t total_units = static_cast<int64_t>(p.W) * units_per_peer;
+      const int slice_bytes = gp.slice_cols * p.elt_bytes_a;   // <= 512
+      const int64_t row_bytes = static_cast<int64_t>(gp.K) * p.elt_bytes_a;
+      for (int64_t u = static_cast<int64_t>(blockIdx.x) * ncw + cw; u < total_units;
+           u += static_cast<int64_t>(gridDim.x) * ncw) {
+        if (*abort_flag) break;
+        const int step = static_cast<int>(u / units_per_peer);  // W-1 remote peers, then local
+        const int rem = static_cast<int>(u - static_cast<int64_t>(step) * units_per_peer);
+        const int chunk = rem / gp.n_slices;
+        const int slice = rem - chunk * gp.n_slices;
+        const int peer = (step == p.W - 1) ? p.rank : peer_for_push_ag(p.rank, step + 1, p.W);
+        const int r0 = chunk * gp.chunk_rows;
+        const int nrows = min(gp.chunk_rows, gp.m - r0);
+        const int64_t cb = static_cast<int64_t>(slice) * slice_bytes + lane * 16;
+        const bool col_ok = (lane * 16 < slice_bytes) && (cb + 16 <= row_bytes);
+        const uint8_t* src = p.a_local + static_cast<int64_t>(r0) * p.a_local_pitch + cb;
+        uint8_t* dstp = p.gathered[peer] + static_cast<int64_t>(parity) * p.gathered_parity_bytes +
+                        (static_cast<int64_t>(p.rank) * gp.m + r0) * p.gathered_pitch + cb;
+        if (col_ok) {
+          for (int r = 0; r < nrows; r += 8) {
+            uint4 buf[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+              if (r + i < nrows)
+                buf[i] = ptx::ld_global_nc_v4(src + static_cast<int64_t>(r + i) * p.a_local_pitch);
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+              if (r + i < nrows)
+                ptx::st_global_v4(dstp + static_cast<int64_t>(r + i) * p.gathered_pitch, buf[i]);
+          }
+        }
+        ptx::fence_acq_rel_sys();
+        __syncwarp();
+        if (lane == 0 && !p.withhold_signals)
+          ptx::st_release_sys_u32(p.gflags[peer] + gather_flag_index(gp, p.rank, chunk, slice),
+                                  epoch);
+      }
+    }
+  }
+
+  // =============================== teardown ===============================
+  ptx::tcgen05_fence_before();
+  __syncthreads();
+  ptx::tcgen05_fence_after();
+  if (warp == 1) ptx::tmem_dealloc(tmem_base, kTmemCols);
+  if (fused && threadIdx.x == 0) {
+    // the last CTA to finish publishes the new epoch for the next launch on this stream
+    __threadfence();
+    const uint32_t prev = atomicAdd(p.cta_counter, 1u);
+    if (prev == gridDim.x - 1) {
+      *p.cta_counter = 0;
+      if (!*abort_flag && *p.status == 0u) *p.epoch_ptr = epoch;
+      __threadfence();
+    }
+  }
+}
+
+}  // namespace catcoc

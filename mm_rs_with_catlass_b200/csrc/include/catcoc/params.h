@@ -1,0 +1,102 @@
+// Kernel parameter block and enums shared by the fused kernels, their launchers and the C API.
+#pragma once
+#include <cstdint>
+#include <cuda.h>
+#include "catcoc/sched.h"
+
+namespace catcoc {
+
+constexpr int kMaxWorld = 8;
+
+// What the epilogue / producer do around the GEMM tiles.
+enum FusedMode : int {
+  MODE_LOCAL = 0,  // plain GEMM: tile -> out
+  MODE_RS = 1,     // matmul + reduce-scatter: push partial tile to its owner, owner sums
+  MODE_AR = 2,     // matmul + all-reduce: as RS, then the owner broadcasts the reduced tile
+  MODE_AG = 3,     // all-gather + matmul: comm warps push the A shard, producer waits per chunk
+};
+
+// Tensor-core flavour (template parameter of the kernel).
+enum MmaKind : int {
+  KIND_F16 = 0,  // fp16 / bf16 operands, fp32 accumulate   (tcgen05 kind::f16)
+  KIND_I8 = 1,   // int8 operands, int32 accumulate          (tcgen05 kind::i8)
+  KIND_F8 = 2,   // e4m3 / e5m2 operands, fp32 accumulate    (tcgen05 kind::f8f6f4)
+};
+
+// Element formats of outputs and of the partial tiles that cross NVLink.
+enum ElemFmt : int { FMT_F16 = 0, FMT_BF16 = 1, FMT_F32 = 2, FMT_S32 = 3 };
+
+CATCOC_HD int fmt_bytes(int fmt) { return (fmt == FMT_F16 || fmt == FMT_BF16) ? 2 : 4; }
+
+// Error codes written to status[0] by a kernel that gave up on a wait.
+enum StatusCode : uint32_t {
+  STATUS_OK = 0,
+  STATUS_TIMEOUT_PIPELINE = 1,  // an intra-CTA mbarrier wait ran out of time
+  STATUS_TIMEOUT_ARRIVE = 2,    // a peer's partial tile never arrived (RS / AR owner side)
+  STATUS_TIMEOUT_DONE = 3,      // an owner's reduced tile never arrived (AR tail)
+  STATUS_TIMEOUT_GATHER = 4,    // a peer's A chunk never arrived (AG producer)
+  STATUS_TIMEOUT_BARRIER = 5,   // barrier_all / wait_until ran out of time
+  STATUS_BAD_ARGUMENT = 6,
+};
+
+// Layout of the status block (uint32 words): [0] code, [1] rank, [2] what (tile / chunk id),
+// [3] expected, [4] seen, [5] peer, [6] blockIdx, [7] reserved.
+constexpr int kStatusWords = 8;
+
+struct alignas(64) FusedParams {
+  CUtensorMap tm_a;          // A operand (AG: this rank's shard)
+  CUtensorMap tm_a_gath[2];  // AG: gathered A, one map per parity buffer
+  CUtensorMap tm_b;
+
+  TileSched sched;
+  int K;
+  int mode;
+  int rank, W;
+
+  // operand staging: K elements per pipeline stage and per MMA instruction; smem majors
+  int bk, umma_k;
+  int a_mn_major, b_mn_major;
+  uint32_t idesc;
+
+  // output (MODE_LOCAL / MODE_AG / RS own tiles): row-major [rows, ldc]
+  void* out;
+  int64_t ldc;
+  int out_fmt;      // ElemFmt of `out`
+  int out_vec_ok;   // 1 when 16-byte vector stores to `out` are aligned
+  int64_t out_row_shift;  // subtracted from the tile's global row to index `out` (RS: seg begin)
+
+  // partial tiles that cross NVLink
+  int partial_fmt;               // ElemFmt of pushed partial tiles
+  uint8_t* stage[kMaxWorld];     // per-rank staging base (peer-mapped), see sched.h
+  uint32_t* arrive[kMaxWorld];   // per-rank arrival stamps
+  // all-reduce broadcast targets
+  uint8_t* ar_out[kMaxWorld];    // per-rank parity-0 output base; parity 1 at + ar_out_parity_bytes
+  int64_t ar_out_parity_bytes;
+  uint8_t* ar_out_mc;            // multicast alias of the same buffer (null => per-peer stores)
+  uint32_t* done[kMaxWorld];     // per-rank "reduced tile landed" stamps
+  uint32_t* done_mc;
+
+  // all-gather
+  const uint8_t* a_local;        // this rank's shard, row-major [m, K]
+  int64_t a_local_pitch;         // bytes
+  uint8_t* gathered[kMaxWorld];  // per-rank gathered buffer base (parity 0)
+  int64_t gathered_parity_bytes;
+  int64_t gathered_pitch;        // bytes per row of the gathered buffer
+  uint32_t* gflags[kMaxWorld];   // per-rank chunk stamps
+  GatherPlan gp;
+  int elt_bytes_a;
+
+  // quantised epilogue (KIND_I8 / KIND_F8): out = cast(float(acc) * scale_m[row] * scale_n[col])
+  const float* scale_m;   // per output row (token), indexed by the global row; may be null
+  const float* scale_n;   // per output column (channel); may be null
+  const int32_t* bias;    // int32 [N], added to every rank's accumulator; may be null
+
+  // launch bookkeeping
+  uint32_t* epoch_ptr;       // completed launches on this workspace (local memory)
+  uint32_t* cta_counter;     // CTAs finished in this launch (local memory)
+  uint32_t* status;          // kStatusWords words, host-visible
+  uint64_t timeout_ns;
+  int withhold_signals;      // test hook: this rank posts no arrival / done / chunk stamps
+};
+
+}  // namespace catcoc

@@ -1,0 +1,167 @@
+// Tile scheduling and offset arithmetic shared by host and device code.
+//
+// One persistent scheduler serves every fused op. The output grid [M, N] is cut into W
+// "segments" along rows or columns (one per rank that owns / supplied that part), each segment
+// is tiled independently with BM x BN tiles (ragged last tiles are clipped), and segments are
+// visited in a rotated order so that every rank starts on a different peer:
+//   matmul_reduce_scatter / matmul_allreduce : destination-major, first = rank+1, own last
+//   allgather_matmul                        : source-major, first = rank (local rows need no wait)
+// Inside a segment tiles run in column groups of `swizzle` tiles with a serpentine walk over
+// rows, which keeps the set of concurrently running tiles compact for L2 reuse.
+//
+// Counterparts in the reference (same job, different construction):
+//   3rdparty/catlass/include/catlass/gemm/block/block_swizzle.hpp:24-125   (tile swizzle)
+//   include/catcoc/dgemm/block/block_swizzle_allgather.hpp:29-116          (source-major order)
+//   include/catcoc/dgemm/kernel/matmul_reduce_scatter.hpp:157-166          (destination-major)
+//   include/catcoc/comm_epilogue/block/comm_block_swizzle.hpp:148-186      (peer rotation)
+#pragma once
+#include <cstdint>
+
+#if defined(__CUDACC__)
+#define CATCOC_HD __host__ __device__ inline
+#else
+#define CATCOC_HD inline
+#endif
+
+namespace catcoc {
+
+CATCOC_HD int ceil_div(int a, int b) { return (a + b - 1) / b; }
+CATCOC_HD int round_up(int a, int b) { return ceil_div(a, b) * b; }
+CATCOC_HD int imin(int a, int b) { return a < b ? a : b; }
+
+enum SegDim : int { SEG_ROWS = 0, SEG_COLS = 1 };
+
+struct TileSched {
+  int M, N;          // extent of the grid being tiled (output rows / cols)
+  int BM, BN;        // tile shape
+  int W;             // number of segments (= world size; 1 for a local GEMM)
+  int seg_dim;       // SEG_ROWS or SEG_COLS
+  int seg_len;       // rows (or cols) per segment
+  int first_seg;     // segment visited first
+  int swizzle;       // tiles per column group (>= 1)
+  int seg_mt, seg_nt;    // tiles per segment along rows / cols
+  int tiles_per_seg;     // seg_mt * seg_nt
+  int total_tiles;       // W * tiles_per_seg
+};
+
+struct TileInfo {
+  int seg;          // which segment (owner rank for RS/AR, source rank for AG)
+  int tile_in_seg;  // 0 .. tiles_per_seg-1, identical on every rank for the same (seg, mi, ni)
+  int mi, ni;       // tile coordinates inside the segment
+  int m0, n0;       // first row / col in the full grid
+  int rows, cols;   // valid rows / cols (clipped)
+};
+
+CATCOC_HD TileSched make_sched(int M, int N, int BM, int BN, int W, int seg_dim, int first_seg,
+                               int swizzle) {
+  TileSched s;
+  s.M = M; s.N = N; s.BM = BM; s.BN = BN; s.W = W < 1 ? 1 : W;
+  s.seg_dim = seg_dim;
+  s.swizzle = swizzle < 1 ? 1 : swizzle;
+  if (seg_dim == SEG_ROWS) {
+    s.seg_len = ceil_div(M, s.W);
+    s.seg_mt = ceil_div(s.seg_len, BM);
+    s.seg_nt = ceil_div(N, BN);
+  } else {
+    s.seg_len = ceil_div(N, s.W);
+    s.seg_mt = ceil_div(M, BM);
+    s.seg_nt = ceil_div(s.seg_len, BN);
+  }
+  s.first_seg = ((first_seg % s.W) + s.W) % s.W;
+  s.tiles_per_seg = s.seg_mt * s.seg_nt;
+  s.total_tiles = s.tiles_per_seg * s.W;
+  return s;
+}
+
+// Position of a tile inside its segment from its linear index (swizzled order).
+CATCOC_HD void seg_tile_coord(const TileSched& s, int i, int* mi, int* ni) {
+  const int group_tiles = s.swizzle * s.seg_mt;
+  const int g = i / group_tiles;
+  const int within = i - g * group_tiles;
+  const int gw = imin(s.swizzle, s.seg_nt - g * s.swizzle);
+  int m = within / gw;
+  const int n = g * s.swizzle + (within - m * gw);
+  if (g & 1) m = s.seg_mt - 1 - m;  // serpentine: odd groups walk rows bottom-up
+  *mi = m;
+  *ni = n;
+}
+
+// Inverse of seg_tile_coord: the canonical id used to address staging slots and flags.
+// The id is position-based (mi * seg_nt + ni), not order-based, so ranks that use different
+// swizzles still agree on which slot a tile lives in.
+CATCOC_HD int seg_tile_id(const TileSched& s, int mi, int ni) { return mi * s.seg_nt + ni; }
+
+CATCOC_HD TileInfo get_tile(const TileSched& s, int t) {
+  TileInfo ti;
+  const int phase = t / s.tiles_per_seg;
+  const int i = t - phase * s.tiles_per_seg;
+  ti.seg = (s.first_seg + phase) % s.W;
+  seg_tile_coord(s, i, &ti.mi, &ti.ni);
+  ti.tile_in_seg = seg_tile_id(s, ti.mi, ti.ni);
+  if (s.seg_dim == SEG_ROWS) {
+    const int seg_begin = ti.seg * s.seg_len;
+    const int seg_end = imin(seg_begin + s.seg_len, s.M);
+    ti.m0 = seg_begin + ti.mi * s.BM;
+    ti.n0 = ti.ni * s.BN;
+    ti.rows = imin(s.BM, seg_end - ti.m0);
+    ti.cols = imin(s.BN, s.N - ti.n0);
+  } else {
+    const int seg_begin = ti.seg * s.seg_len;
+    const int seg_end = imin(seg_begin + s.seg_len, s.N);
+    ti.m0 = ti.mi * s.BM;
+    ti.n0 = seg_begin + ti.ni * s.BN;
+    ti.rows = imin(s.BM, s.M - ti.m0);
+    ti.cols = imin(s.BN, seg_end - ti.n0);
+  }
+  if (ti.rows < 0) ti.rows = 0;
+  if (ti.cols < 0) ti.cols = 0;
+  return ti;
+}
+
+// Order in which a pusher visits its peers: the peer that consumes this rank's data earliest
+// comes first. For source-major consumers (allgather_matmul) rank r reads source q in phase
+// (q - r) mod W, so q serves q-1, q-2, ... For destination-major producers the order is
+// rank+1, rank+2, ...
+CATCOC_HD int peer_for_push_ag(int rank, int step, int W) { return ((rank - step) % W + W) % W; }
+CATCOC_HD int peer_for_push_rs(int rank, int step, int W) { return (rank + step) % W; }
+
+// ---------------------------------------------------------------------------------------
+// Workspace geometry (bytes) for the fused ops; all ranks compute identical numbers.
+// ---------------------------------------------------------------------------------------
+// Staging for pushed partial tiles: [parity 2][source W][tiles_per_seg] slabs of BM x BN elements.
+CATCOC_HD int64_t stage_tile_bytes(const TileSched& s, int elt_bytes) {
+  return static_cast<int64_t>(s.BM) * s.BN * elt_bytes;
+}
+CATCOC_HD int64_t stage_slot_offset(const TileSched& s, int elt_bytes, int parity, int src,
+                                    int tile_in_seg) {
+  return ((static_cast<int64_t>(parity) * s.W + src) * s.tiles_per_seg + tile_in_seg) *
+         stage_tile_bytes(s, elt_bytes);
+}
+CATCOC_HD int64_t stage_total_bytes(const TileSched& s, int elt_bytes) {
+  return 2 * static_cast<int64_t>(s.W) * s.tiles_per_seg * stage_tile_bytes(s, elt_bytes);
+}
+// Arrival stamps: one 32-bit word per (tile_in_seg, source).
+CATCOC_HD int64_t arrive_flag_index(const TileSched& s, int tile_in_seg, int src) {
+  return static_cast<int64_t>(tile_in_seg) * s.W + src;
+}
+
+// All-gather chunk geometry: the local shard [m, K] is pushed in units of
+// `chunk_rows` x `slice_cols` elements; a consumer needs every slice of a row chunk.
+struct GatherPlan {
+  int m, K;          // shard rows, row length (elements)
+  int chunk_rows;    // rows per chunk (= BM of the consumer)
+  int slice_cols;    // elements per slice
+  int n_chunks, n_slices;
+};
+CATCOC_HD GatherPlan make_gather_plan(int m, int K, int chunk_rows, int slice_cols) {
+  GatherPlan g;
+  g.m = m; g.K = K; g.chunk_rows = chunk_rows; g.slice_cols = slice_cols;
+  g.n_chunks = ceil_div(m, chunk_rows);
+  g.n_slices = ceil_div(K, slice_cols);
+  return g;
+}
+CATCOC_HD int64_t gather_flag_index(const GatherPlan& g, int src, int chunk, int slice) {
+  return (static_cast<int64_t>(src) * g.n_chunks + chunk) * g.n_slices + slice;
+}
+
+}  // namespace catcoc

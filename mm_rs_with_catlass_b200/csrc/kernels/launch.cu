@@ -1,0 +1,347 @@
+// Host launcher of the fused kernel: validates arguments, encodes the TMA tensor maps, fills
+// the parameter block and launches one persistent grid. Also exposes the workspace geometry
+// and a host-side replay of the tile scheduler for unit tests.
+//
+// Reference counterparts: examples/dynamic_tiling/impl/kernel_fp16.cpp:22-86 (layout dispatch +
+// launch) and examples/dynamic_tiling/impl/kernel/matmul_allreduce.h:152-212 (tiling -> params).
+#include <cstring>
+#include <mutex>
+#include "catcoc/capi.h"
+#include "catcoc/fused_gemm.cuh"
+#include "catcoc/host_util.h"
+
+namespace catcoc {
+namespace host {
+
+static thread_local std::string g_error;
+
+void set_error(const char* fmt, ...) {
+  char buf[1024];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof(buf), fmt, ap);
+  va_end(ap);
+  g_error = buf;
+}
+const char* last_error() { return g_error.c_str(); }
+
+void* driver_symbol(const char* name) {
+  void* fn = nullptr;
+  cudaDriverEntryPointQueryResult q;
+  cudaError_t e = cudaGetDriverEntryPoint(name, &fn, cudaEnableDefault, &q);
+  if (e != cudaSuccess || q != cudaDriverEntryPointSuccess || fn == nullptr) {
+    cudaGetLastError();
+    set_error("CUDA driver symbol %s is unavailable (%s)", name, cudaGetErrorString(e));
+    return nullptr;
+  }
+  return fn;
+}
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// 2-D row-major matrix [rows, cols] (cols contiguous, leading dimension ld elements) viewed by
+// TMA with a box of box_cols x box_rows elements and 128-byte swizzle; out-of-range elements
+// read as zero.
+static int encode_2d(CUtensorMap* tm, const void* base, int elt_bytes, CUtensorMapDataType dt,
+                     int64_t rows, int64_t cols, int64_t ld, int box_cols, int box_rows) {
+  static EncodeTiledFn fn = driver_fn<EncodeTiledFn>("cuTensorMapEncodeTiled");
+  if (fn == nullptr) return CATCOC_E_DRIVER;
+  if ((reinterpret_cast<uintptr_t>(base) & 15) != 0 || ((ld * elt_bytes) & 15) != 0) {
+    set_error("TMA operand needs a 16-byte aligned base and row pitch (base %p, pitch %lld B)",
+              base, static_cast<long long>(ld * elt_bytes));
+    return CATCOC_E_ALIGNMENT;
+  }
+  if (box_cols * elt_bytes != 128 || box_rows > 256 || box_rows < 1) {
+    set_error("bad TMA box %d x %d", box_cols, box_rows);
+    return CATCOC_E_BAD_ARG;
+  }
+  cuuint64_t gdim[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
+  cuuint64_t gstride[1] = {static_cast<cuuint64_t>(ld) * elt_bytes};
+  cuuint32_t box[2] = {static_cast<cuuint32_t>(box_cols), static_cast<cuuint32_t>(box_rows)};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(tm, dt, 2, const_cast<void*>(base), gdim, gstride, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    set_error("cuTensorMapEncodeTiled failed: CUresult %d (rows %lld cols %lld ld %lld box %dx%d)",
+              static_cast<int>(r), static_cast<long long>(rows), static_cast<long long>(cols),
+              static_cast<long long>(ld), box_cols, box_rows);
+    return CATCOC_E_DRIVER;
+  }
+  return CATCOC_OK;
+}
+
+static int sm_count(int device) {
+  static int cached[64];
+  static std::once_flag once;
+  std::call_once(once, [] { memset(cached, 0, sizeof(cached)); });
+  if (device < 0 || device >= 64) return 148;
+  if (cached[device] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || n <= 0) {
+      cudaGetLastError();
+      n = 148;
+    }
+    cached[device] = n;
+  }
+  return cached[device];
+}
+
+struct Resolved {
+  int kind, elt, bk, umma_k, a_fmt, c_fmt;
+  CUtensorMapDataType dt;
+};
+
+static int resolve_format(int in_fmt, Resolved* r) {
+  switch (in_fmt) {
+    case CATCOC_IN_F16:
+      *r = {KIND_F16, 2, 64, 16, 0, 1, CU_TENSOR_MAP_DATA_TYPE_FLOAT16};
+      return 0;
+    case CATCOC_IN_BF16:
+      *r = {KIND_F16, 2, 64, 16, 1, 1, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16};
+      return 0;
+    case CATCOC_IN_S8:
+      *r = {KIND_I8, 1, 128, 32, 1, 2, CU_TENSOR_MAP_DATA_TYPE_UINT8};
+      return 0;
+    case CATCOC_IN_E4M3:
+      *r = {KIND_F8, 1, 128, 32, 0, 1, CU_TENSOR_MAP_DATA_TYPE_UINT8};
+      return 0;
+    case CATCOC_IN_E5M2:
+      *r = {KIND_F8, 1, 128, 32, 1, 1, CU_TENSOR_MAP_DATA_TYPE_UINT8};
+      return 0;
+    default:
+      set_error("unknown operand format %d", in_fmt);
+      return CATCOC_E_BAD_ARG;
+  }
+}
+
+static int pick_seg_dim(const CatcocOpArgs& a) {
+  if (a.mode != CATCOC_MODE_AR) return SEG_ROWS;
+  if (a.tiling.seg_dim == 0 || a.tiling.seg_dim == 1) return a.tiling.seg_dim;
+  // all-reduce may split ownership either way: rows while every rank still gets full tiles
+  return (a.M >= a.W * kBM) ? SEG_ROWS : SEG_COLS;
+}
+
+static TileSched build_sched(const CatcocOpArgs& a, int bn, int seg_dim) {
+  const bool fused = a.mode != CATCOC_MODE_LOCAL && a.W > 1;
+  const int W = fused ? a.W : 1;
+  int first = 0;
+  if (fused) first = (a.mode == CATCOC_MODE_AG) ? a.rank : (a.rank + 1) % W;
+  const int swz = a.tiling.swizzle > 0 ? a.tiling.swizzle : 8;
+  return make_sched(a.M, a.N, kBM, bn, W, seg_dim, first, swz);
+}
+
+}  // namespace host
+}  // namespace catcoc
+
+using namespace catcoc;
+using namespace catcoc::host;
+
+extern "C" const char* catcoc_last_error(void) { return last_error(); }
+extern "C" int catcoc_version(void) { return 100; }
+extern "C" int catcoc_num_sms(int device) { return sm_count(device); }
+
+static int norm_bn(int bn) { return (bn == 64 || bn == 128 || bn == 256) ? bn : 256; }
+
+extern "C" int64_t catcoc_stage_bytes(int M, int N, int W, int seg_dim, int bn, int partial_fmt) {
+  TileSched s = make_sched(M, N, kBM, norm_bn(bn), W, seg_dim, 0, 1);
+  return stage_total_bytes(s, fmt_bytes(partial_fmt));
+}
+extern "C" int64_t catcoc_arrive_words(int M, int N, int W, int seg_dim, int bn) {
+  TileSched s = make_sched(M, N, kBM, norm_bn(bn), W, seg_dim, 0, 1);
+  return static_cast<int64_t>(s.tiles_per_seg) * s.W * 4;
+}
+extern "C" int64_t catcoc_done_words(int M, int N, int W, int seg_dim, int bn) {
+  TileSched s = make_sched(M, N, kBM, norm_bn(bn), W, seg_dim, 0, 1);
+  return static_cast<int64_t>(s.total_tiles) * 4;
+}
+extern "C" int64_t catcoc_gather_flag_words(int m, int K, int W, int elt_bytes) {
+  GatherPlan g = make_gather_plan(m, K, kBM, 512 / elt_bytes);
+  return static_cast<int64_t>(W) * g.n_chunks * g.n_slices;
+}
+
+extern "C" int catcoc_sched_total_tiles(int M, int N, int bm, int bn, int W, int seg_dim) {
+  return make_sched(M, N, bm, bn, W, seg_dim, 0, 1).total_tiles;
+}
+extern "C" int catcoc_sched_get_tile(int M, int N, int bm, int bn, int W, int seg_dim,
+                                     int first_seg, int swizzle, int t, CatcocTile* out) {
+  TileSched s = make_sched(M, N, bm, bn, W, seg_dim, first_seg, swizzle);
+  if (t < 0 || t >= s.total_tiles || out == nullptr) return CATCOC_E_BAD_ARG;
+  TileInfo ti = get_tile(s, t);
+  out->seg = ti.seg; out->tile_in_seg = ti.tile_in_seg; out->mi = ti.mi; out->ni = ti.ni;
+  out->m0 = ti.m0; out->n0 = ti.n0; out->rows = ti.rows; out->cols = ti.cols;
+  return CATCOC_OK;
+}
+
+// Fills the parameter block; shared by the normal and the allocation-free entry points.
+int catcoc_build_params(const CatcocOpArgs* args, FusedParams* p, int* kind_out, int* grid_out) {
+  if (args == nullptr) { set_error("null args"); return CATCOC_E_BAD_ARG; }
+  const CatcocOpArgs& a = *args;
+  if (a.M <= 0 || a.N <= 0 || a.K <= 0) {
+    set_error("bad problem size M=%d N=%d K=%d", a.M, a.N, a.K);
+    return CATCOC_E_BAD_ARG;
+  }
+  if (a.mode < CATCOC_MODE_LOCAL || a.mode > CATCOC_MODE_AG) {
+    set_error("bad mode %d", a.mode);
+    return CATCOC_E_BAD_ARG;
+  }
+  const bool fused = a.mode != CATCOC_MODE_LOCAL && a.W > 1;
+  if (fused && (a.W > kMaxWorld || a.rank < 0 || a.rank >= a.W)) {
+    set_error("bad rank/world %d/%d", a.rank, a.W);
+    return CATCOC_E_BAD_ARG;
+  }
+  Resolved rf;
+  int rc = resolve_format(a.in_fmt, &rf);
+  if (rc != 0) return rc;
+  const int bn = norm_bn(a.tiling.bn);
+  const int seg_dim = pick_seg_dim(a);
+
+  memset(p, 0, sizeof(*p));
+  p->sched = build_sched(a, bn, seg_dim);
+  p->K = a.K;
+  p->mode = a.mode;
+  p->rank = fused ? a.rank : 0;
+  p->W = fused ? a.W : 1;
+  p->bk = rf.bk;
+  p->umma_k = rf.umma_k;
+  p->a_mn_major = a.trans_a ? 1 : 0;     // stored [K, M]: M contiguous
+  p->b_mn_major = a.trans_b ? 0 : 1;     // stored [K, N]: N contiguous
+  p->idesc = ptx::make_instr_desc(rf.c_fmt, rf.a_fmt, rf.a_fmt, p->a_mn_major, p->b_mn_major, kBM, bn);
+  p->elt_bytes_a = rf.elt;
+
+  if (fused && (a.mode == CATCOC_MODE_RS) && (a.M % a.W != 0)) {
+    set_error("matmul_reduce_scatter needs M %% W == 0 (M=%d, W=%d)", a.M, a.W);
+    return CATCOC_E_BAD_ARG;
+  }
+
+  // ---- operands ----
+  const int per128 = 128 / rf.elt;
+  if (!a.trans_b && bn < per128) {
+    set_error("8-bit operands stored [K, N] need bn >= 128 (one 128-byte run of N per TMA box)");
+    return CATCOC_E_UNSUPPORTED;
+  }
+  if (a.mode == CATCOC_MODE_AG && fused) {
+    if (a.trans_a) { set_error("allgather_matmul supports trans_a=False only"); return CATCOC_E_UNSUPPORTED; }
+    if (a.ag_m <= 0 || a.ag_m * a.W != a.M) { set_error("allgather: M must be W * m"); return CATCOC_E_BAD_ARG; }
+    rc = encode_2d(&p->tm_a, a.a, rf.elt, rf.dt, a.ag_m, a.K, a.lda, rf.bk, kBM);
+    if (rc != 0) return rc;
+    const int64_t gpitch = static_cast<int64_t>(a.K) * rf.elt;
+    if ((gpitch & 15) != 0) { set_error("allgather: K * elt must be a multiple of 16 bytes"); return CATCOC_E_ALIGNMENT; }
+    for (int par = 0; par < 2; ++par) {
+      const uint8_t* gb = static_cast<const uint8_t*>(a.gathered[a.rank]) + par * a.gathered_parity_bytes;
+      rc = encode_2d(&p->tm_a_gath[par], gb, rf.elt, rf.dt, a.M, a.K, a.K, rf.bk, kBM);
+      if (rc != 0) return rc;
+    }
+    p->a_local = static_cast<const uint8_t*>(a.a);
+    p->a_local_pitch = a.lda * rf.elt;
+    if ((p->a_local_pitch & 15) != 0) { set_error("allgather: A pitch must be a multiple of 16 bytes"); return CATCOC_E_ALIGNMENT; }
+    p->gathered_parity_bytes = a.gathered_parity_bytes;
+    p->gathered_pitch = gpitch;
+    p->gp = make_gather_plan(a.ag_m, a.K, kBM, 512 / rf.elt);
+    for (int r = 0; r < a.W; ++r) {
+      p->gathered[r] = static_cast<uint8_t*>(a.gathered[r]);
+      p->gflags[r] = a.gflags[r];
+      if (p->gathered[r] == nullptr || p->gflags[r] == nullptr) { set_error("allgather: missing peer buffers"); return CATCOC_E_BAD_ARG; }
+    }
+  } else if (!a.trans_a) {
+    rc = encode_2d(&p->tm_a, a.a, rf.elt, rf.dt, a.M, a.K, a.lda, rf.bk, kBM);
+    if (rc != 0) return rc;
+  } else {
+    rc = encode_2d(&p->tm_a, a.a, rf.elt, rf.dt, a.K, a.M, a.lda, per128, rf.bk);
+    if (rc != 0) return rc;
+  }
+  if (a.trans_b) {
+    rc = encode_2d(&p->tm_b, a.b, rf.elt, rf.dt, a.N, a.K, a.ldb, rf.bk, bn);
+  } else {
+    rc = encode_2d(&p->tm_b, a.b, rf.elt, rf.dt, a.K, a.N, a.ldb, per128, rf.bk);
+  }
+  if (rc != 0) return rc;
+
+  // ---- output ----
+  p->out = a.out;
+  p->ldc = a.ldc;
+  p->out_fmt = a.out_fmt;
+  const int oelt = fmt_bytes(a.out_fmt);
+  p->out_row_shift = 0;
+  if (fused && a.mode == CATCOC_MODE_RS) p->out_row_shift = static_cast<int64_t>(a.rank) * p->sched.seg_len;
+  p->partial_fmt = a.partial_fmt;
+  if (fused && a.mode == CATCOC_MODE_AR) {
+    for (int r = 0; r < a.W; ++r) {
+      p->ar_out[r] = static_cast<uint8_t*>(a.ar_out[r]);
+      p->done[r] = a.done[r];
+      if (p->ar_out[r] == nullptr || p->done[r] == nullptr) { set_error("allreduce: missing peer buffers"); return CATCOC_E_BAD_ARG; }
+    }
+    p->ar_out_parity_bytes = a.ar_out_parity_bytes;
+    p->ar_out_mc = a.tiling.use_multicast ? static_cast<uint8_t*>(a.ar_out_mc) : nullptr;
+    p->done_mc = a.tiling.use_multicast ? a.done_mc : nullptr;
+    p->out_vec_ok = (((a.ldc * oelt) & 15) == 0 && (a.ar_out_parity_bytes & 15) == 0 &&
+                     (reinterpret_cast<uintptr_t>(a.ar_out[a.rank]) & 15) == 0) ? 1 : 0;
+  } else {
+    if (a.out == nullptr) { set_error("null output"); return CATCOC_E_BAD_ARG; }
+    p->out_vec_ok = (((a.ldc * oelt) & 15) == 0 && (reinterpret_cast<uintptr_t>(a.out) & 15) == 0) ? 1 : 0;
+  }
+  if (fused && (a.mode == CATCOC_MODE_RS || a.mode == CATCOC_MODE_AR)) {
+    for (int r = 0; r < a.W; ++r) {
+      p->stage[r] = static_cast<uint8_t*>(a.stage[r]);
+      p->arrive[r] = a.arrive[r];
+      if (p->stage[r] == nullptr || p->arrive[r] == nullptr) { set_error("missing staging buffers for rank %d", r); return CATCOC_E_BAD_ARG; }
+    }
+  }
+  p->scale_m = a.scale_m;
+  p->scale_n = a.scale_n;
+  p->bias = a.bias;
+  if (a.bias != nullptr && rf.kind != KIND_I8) { set_error("bias is only supported for int8 operands"); return CATCOC_E_UNSUPPORTED; }
+
+  p->epoch_ptr = a.epoch_ptr;
+  p->cta_counter = a.cta_counter;
+  p->status = a.status;
+  if (a.status == nullptr) { set_error("null status block"); return CATCOC_E_BAD_ARG; }
+  if (fused && (a.epoch_ptr == nullptr || a.cta_counter == nullptr)) { set_error("null epoch / counter"); return CATCOC_E_BAD_ARG; }
+  p->timeout_ns = a.timeout_ns ? a.timeout_ns : 10000000000ull;
+  p->withhold_signals = a.withhold_signals;
+
+  int device = 0;
+  cudaGetDevice(&device);
+  int grid = a.tiling.num_ctas > 0 ? a.tiling.num_ctas : sm_count(device);
+  grid = imin(grid, sm_count(device));
+  // All-gather needs every CTA's communication warps; otherwise never launch idle CTAs.
+  if (!(fused && a.mode == CATCOC_MODE_AG)) grid = imin(grid, p->sched.total_tiles);
+  if (grid < 1) grid = 1;
+  *grid_out = grid;
+  *kind_out = rf.kind;
+  return CATCOC_OK;
+}
+
+int catcoc_launch_params(const FusedParams& p, int kind, int grid, cudaStream_t stream) {
+  static std::once_flag once;
+  static cudaError_t attr_err = cudaSuccess;
+  std::call_once(once, [] {
+    cudaError_t e;
+    e = cudaFuncSetAttribute(fused_gemm_kernel<KIND_F16>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    if (e != cudaSuccess) attr_err = e;
+    e = cudaFuncSetAttribute(fused_gemm_kernel<KIND_I8>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    if (e != cudaSuccess) attr_err = e;
+    e = cudaFuncSetAttribute(fused_gemm_kernel<KIND_F8>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    if (e != cudaSuccess) attr_err = e;
+  });
+  if (attr_err != cudaSuccess) {
+    set_error("cudaFuncSetAttribute failed: %s", cudaGetErrorString(attr_err));
+    return -1000 - static_cast<int>(attr_err);
+  }
+  if (kind == KIND_F16) fused_gemm_kernel<KIND_F16><<<grid, kThreads, kSmemBytes, stream>>>(p);
+  else if (kind == KIND_I8) fused_gemm_kernel<KIND_I8><<<grid, kThreads, kSmemBytes, stream>>>(p);
+  else fused_gemm_kernel<KIND_F8><<<grid, kThreads, kSmemBytes, stream>>>(p);
+  CATCOC_CUDA_OK(cudaGetLastError());
+  return CATCOC_OK;
+}
+
+extern "C" int catcoc_fused_launch(const CatcocOpArgs* args, void* stream) {
+  FusedParams p;
+  int kind = 0, grid = 0;
+  int rc = catcoc_build_params(args, &p, &kind, &grid);
+  if (rc != 0) return rc;
+  return catcoc_launch_params(p, kind, grid, static_cast<cudaStream_t>(stream));
+}

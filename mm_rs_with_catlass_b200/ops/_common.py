@@ -1,0 +1,160 @@
+"""Shared plumbing of the op layer: dtype tables, operand normalisation and native launches."""
+from __future__ import annotations
+
+import ctypes as C
+import os
+from dataclasses import dataclass
+from typing import Optional, Tuple
+
+import torch
+
+from .. import _native as N
+from ..tiling.config import TilingConfig
+
+_IN_FMT = {
+    torch.float16: N.IN_F16,
+    torch.bfloat16: N.IN_BF16,
+    torch.int8: N.IN_S8,
+}
+if hasattr(torch, "float8_e4m3fn"):
+    _IN_FMT[torch.float8_e4m3fn] = N.IN_E4M3
+    _IN_FMT[torch.float8_e5m2] = N.IN_E5M2
+
+_OUT_FMT = {
+    torch.float16: N.FMT_F16,
+    torch.bfloat16: N.FMT_BF16,
+    torch.float32: N.FMT_F32,
+    torch.int32: N.FMT_S32,
+}
+
+
+def in_fmt(dtype: torch.dtype) -> int:
+    try:
+        return _IN_FMT[dtype]
+    except KeyError:
+        raise TypeError("unsupported operand dtype %s (fp16, bf16, int8, fp8 e4m3/e5m2)" % dtype) from None
+
+
+def out_fmt(dtype: torch.dtype) -> int:
+    try:
+        return _OUT_FMT[dtype]
+    except KeyError:
+        raise TypeError("unsupported output dtype %s (fp16, bf16, fp32, int32)" % dtype) from None
+
+
+def require_cuda(*tensors: torch.Tensor) -> torch.device:
+    dev = None
+    for t in tensors:
+        if t is None:
+            continue
+        if not t.is_cuda:
+            raise RuntimeError(
+                "this op runs only on a CUDA device (sm_100a); got a %s tensor. The CPU goldens live in "
+                "mm_rs_with_catlass_b200.ops.reference" % t.device)
+        if dev is None:
+            dev = t.device
+        elif t.device != dev:
+            raise RuntimeError("operands live on different devices: %s vs %s" % (dev, t.device))
+    return dev
+
+
+@dataclass
+class Operand:
+    """A matrix as the kernel sees it: storage pointer, leading dimension and whether the
+    *stored* matrix is the transpose of the logical one."""
+    tensor: torch.Tensor  # keeps the (possibly padded) storage alive until the launch is queued
+    ptr: int
+    ld: int
+    trans: bool
+
+
+def _tma_legal(t: torch.Tensor) -> bool:
+    elt = t.element_size()
+    return t.stride(-1) == 1 and (t.stride(0) * elt) % 16 == 0 and t.data_ptr() % 16 == 0 and t.stride(0) >= t.shape[1]
+
+
+def pad_rows(t: torch.Tensor) -> torch.Tensor:
+    """Returns a copy of the 2-D row-major tensor whose row pitch is a multiple of 16 bytes,
+    made by the library's own pad kernel (the analogue of the reference's padding prologue,
+    3rdparty/catlass/include/catlass/gemm/kernel/padding_matmul.hpp:32-347)."""
+    elt = t.element_size()
+    rows, cols = t.shape
+    per16 = 16 // elt
+    ld = (cols + per16 - 1) // per16 * per16
+    buf = torch.empty((rows, ld), dtype=t.dtype, device=t.device)
+    src = t if t.stride(-1) == 1 else t.contiguous()
+    stream = torch.cuda.current_stream(t.device).cuda_stream
+    N.check(N.lib().catcoc_pad2d(buf.data_ptr(), ld * elt, src.data_ptr(), src.stride(0) * elt, rows, cols * elt,
+                                 C.c_void_p(stream)))
+    return buf
+
+
+def as_operand(x: torch.Tensor, trans: bool) -> Operand:
+    """Normalises a 2-D operand.
+
+    ``x`` is the *stored* matrix ([M, K] or, with ``trans``, [K, M]; likewise for B). A stored
+    matrix that is itself a column-major view (``x.stride(0) == 1``) is folded into the
+    transpose flag instead of being copied, as the reference's Python wrapper does
+    (3rdparty/catlass/examples/python_extension/src/wrapper/catlass_kernel_wrapper.cpp:71-85).
+    """
+    if x.dim() != 2:
+        raise ValueError("operands must be 2-D, got shape %s" % (tuple(x.shape),))
+    if x.stride(-1) != 1 and x.stride(0) == 1 and x.shape[0] > 1 and x.shape[1] > 1:
+        x = x.t()
+        trans = not trans
+    if not _tma_legal(x):
+        x = pad_rows(x)
+    return Operand(x, x.data_ptr(), x.stride(0), trans)
+
+
+def fill_tiling(args: N.OpArgs, tiling: Optional[TilingConfig]) -> None:
+    t = tiling or TilingConfig()
+    args.tiling.bn = t.bn
+    args.tiling.swizzle = t.swizzle
+    args.tiling.num_ctas = t.num_ctas
+    args.tiling.seg_dim = t.seg_dim
+    args.tiling.use_multicast = 1 if t.use_multicast else 0
+
+
+def default_timeout_ns() -> int:
+    """Time budget of every device-side wait (``CATCOC_TIMEOUT_MS``, default 10 s)."""
+    return int(float(os.environ.get("CATCOC_TIMEOUT_MS", "10000")) * 1e6)
+
+
+def launch(args: N.OpArgs, device: torch.device) -> None:
+    if not args.timeout_ns:
+        args.timeout_ns = default_timeout_ns()
+    stream = torch.cuda.current_stream(device).cuda_stream
+    N.check(N.lib().catcoc_fused_launch(C.byref(args), C.c_void_p(stream)))
+
+
+_status_cache = {}
+
+
+def local_status(device: torch.device) -> torch.Tensor:
+    """Per-device status block for launches that involve no peers."""
+    key = (device.type, device.index)
+    st = _status_cache.get(key)
+    if st is None:
+        st = torch.zeros(8, dtype=torch.int32, device=device)
+        _status_cache[key] = st
+    return st
+
+
+def raise_on_status(status: torch.Tensor, what: str) -> None:
+    """Reads a status block (synchronises) and raises if a kernel reported a failed wait."""
+    vals = status.cpu().tolist()
+    if vals[0] != 0:
+        status.zero_()
+        raise RuntimeError(
+            "%s failed on rank %d: %s (what=%d expected=%d seen=%d peer=%d cta=%d)"
+            % (what, vals[1], N.STATUS_NAMES.get(vals[0], "code %d" % vals[0]), vals[2], vals[3], vals[4], vals[5],
+               vals[6]))
+
+
+def logical_shape(a: torch.Tensor, trans_a: bool, b: torch.Tensor, trans_b: bool) -> Tuple[int, int, int]:
+    m, k = (a.shape[1], a.shape[0]) if trans_a else (a.shape[0], a.shape[1])
+    kb, n = (b.shape[1], b.shape[0]) if trans_b else (b.shape[0], b.shape[1])
+    if k != kb:
+        raise ValueError("inner dimensions differ: A gives K=%d, B gives K=%d" % (k, kb))
+    return m, n, k
