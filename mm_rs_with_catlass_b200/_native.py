@@ -58,7 +58,7 @@ class OpArgs(C.Structure):
         ("gathered", C.c_void_p * MAX_WORLD),
         ("gathered_parity_bytes", C.c_int64),
         ("gflags", C.c_void_p * MAX_WORLD),
-        ("ag_m", C.c_int),
+        ("ag_m", C.c_int), ("ag_ld", C.c_int),
         ("scale_m", C.c_void_p), ("scale_n", C.c_void_p), ("bias", C.c_void_p),
         ("epoch_ptr", C.c_void_p), ("cta_counter", C.c_void_p), ("status", C.c_void_p),
         ("timeout_ns", C.c_uint64),
@@ -114,9 +114,9 @@ def _declare(lib) -> None:
         "catcoc_heap_mc_bind": (i32, [vp]),
         "catcoc_heap_mc_base": (vp, [vp]),
         "catcoc_heap_destroy": (i32, [vp]),
-        "catcoc_fd_send": (i32, [C.c_char_p, i32, i32]),
+        "catcoc_fd_send": (i32, [C.c_char_p, i32, i32, i32]),
         "catcoc_fd_recv_open": (i32, [C.c_char_p]),
-        "catcoc_fd_recv": (i32, [i32, i32]),
+        "catcoc_fd_recv": (i32, [i32, i32, P(i32)]),
         "catcoc_fd_close": (i32, [i32]),
         "catcoc_shmem_barrier_all": (i32, [P(ShmemCtx), u32, u64, vp, vp]),
         "catcoc_shmem_put": (i32, [P(ShmemCtx), i32, i64, vp, i64, i64, u32, vp]),

@@ -69,6 +69,7 @@ typedef struct CatcocOpArgs {
   int64_t gathered_parity_bytes;
   uint32_t* gflags[CATCOC_MAX_WORLD];
   int ag_m;                                /* all-gather: rows of one shard              */
+  int ag_ld;                               /* all-gather: row pitch (elements) of the gathered buffer, >= K, 16-byte multiple */
 
   /* quantised epilogue */
   const float* scale_m; const float* scale_n; const int32_t* bias;
@@ -123,9 +124,10 @@ int catcoc_heap_mc_bind(CatcocHeap* h);                  /* all, after every ran
 void* catcoc_heap_mc_base(const CatcocHeap* h);          /* multicast alias or NULL        */
 int catcoc_heap_destroy(CatcocHeap* h);
 /* fd passing between local processes over an abstract unix socket */
-int catcoc_fd_send(const char* sock_name, int fd, int timeout_ms);
+/* (one datagram = one fd + a one-byte tag chosen by the sender, e.g. its rank) */
+int catcoc_fd_send(const char* sock_name, int fd, int tag, int timeout_ms);
 int catcoc_fd_recv_open(const char* sock_name);          /* returns listening socket       */
-int catcoc_fd_recv(int listen_sock, int timeout_ms);     /* returns received fd            */
+int catcoc_fd_recv(int listen_sock, int timeout_ms, int* tag);  /* returns received fd     */
 int catcoc_fd_close(int fd);
 
 /* ---- device primitive kernels (csrc/kernels/shmem_prims.cu), used by tests and the heap ---- */

@@ -414,7 +414,7 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
         pitch = p.ldc * st_elt;
         off = static_cast<int64_t>(parity) * p.ar_out_parity_bytes +
               (static_cast<int64_t>(ti.m0 + q * 32) * p.ldc + ti.n0) * st_elt;
-        vec_ok = p.out_vec_ok != 0;
+        vec_ok = (p.out_vec_ok != 0) && ((ti.n0 * st_elt) % 16 == 0);
         if (p.ar_out_mc != nullptr && vec_ok && (ti.cols % (16 / st_elt) == 0)) {
           mc = p.ar_out_mc + off;
         } else {
@@ -424,7 +424,7 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
         pitch = p.ldc * st_elt;
         base = static_cast<uint8_t*>(p.out) +
                (static_cast<int64_t>(ti.m0 + q * 32 - p.out_row_shift) * p.ldc + ti.n0) * st_elt;
-        vec_ok = p.out_vec_ok != 0;
+        vec_ok = (p.out_vec_ok != 0) && ((ti.n0 * st_elt) % 16 == 0);
       }
 
       const int groups = BN / 32;                        // 32-column groups in the accumulator

@@ -98,7 +98,7 @@ CATCOC_DEVICE void named_bar_sync(uint32_t id, uint32_t nthreads) {
 
 // ---------------------------------------------------------------------------------------
 // TMA: tiled 2-D loads from (local or peer) global memory into shared memory.
-// No `.multicast::cluster` form exists in this library on purpose.
+// Every load is issued per CTA; this library has no cluster-broadcast form of these copies.
 // ---------------------------------------------------------------------------------------
 CATCOC_DEVICE void prefetch_tmap(const void* tmap) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(tmap)) : "memory");

@@ -218,6 +218,21 @@ int catcoc_build_params(const CatcocOpArgs* args, FusedParams* p, int* kind_out,
   }
 
   // ---- operands ----
+  // TMA alignment of tile origins: the innermost TMA coordinate must be a multiple of 16 bytes.
+  // It is the tile's first row for an A stored [K, M] and its first column for a B stored
+  // [K, N]; tile origins inside a segment are multiples of 128 / bn, so only the segment
+  // origins (multiples of seg_len) can break the rule.
+  const int per16 = 16 / rf.elt;
+  if (p->sched.W > 1) {
+    if (a.trans_a && seg_dim == SEG_ROWS && (p->sched.seg_len % per16) != 0) {
+      set_error("trans_a needs rows-per-rank (%d) to be a multiple of %d", p->sched.seg_len, per16);
+      return CATCOC_E_ALIGNMENT;
+    }
+    if (!a.trans_b && seg_dim == SEG_COLS && (p->sched.seg_len % per16) != 0) {
+      set_error("column-split ownership needs cols-per-rank (%d) to be a multiple of %d", p->sched.seg_len, per16);
+      return CATCOC_E_ALIGNMENT;
+    }
+  }
   const int per128 = 128 / rf.elt;
   if (!a.trans_b && bn < per128) {
     set_error("8-bit operands stored [K, N] need bn >= 128 (one 128-byte run of N per TMA box)");
@@ -228,11 +243,16 @@ int catcoc_build_params(const CatcocOpArgs* args, FusedParams* p, int* kind_out,
     if (a.ag_m <= 0 || a.ag_m * a.W != a.M) { set_error("allgather: M must be W * m"); return CATCOC_E_BAD_ARG; }
     rc = encode_2d(&p->tm_a, a.a, rf.elt, rf.dt, a.ag_m, a.K, a.lda, rf.bk, kBM);
     if (rc != 0) return rc;
-    const int64_t gpitch = static_cast<int64_t>(a.K) * rf.elt;
-    if ((gpitch & 15) != 0) { set_error("allgather: K * elt must be a multiple of 16 bytes"); return CATCOC_E_ALIGNMENT; }
+    const int ag_ld = a.ag_ld > 0 ? a.ag_ld : a.K;
+    const int64_t gpitch = static_cast<int64_t>(ag_ld) * rf.elt;
+    if ((gpitch & 15) != 0 || ag_ld < a.K || a.lda < ag_ld) {
+      set_error("allgather: gathered pitch must be >= K, <= lda and a multiple of 16 bytes (K=%d ag_ld=%d lda=%lld)",
+                a.K, ag_ld, static_cast<long long>(a.lda));
+      return CATCOC_E_ALIGNMENT;
+    }
     for (int par = 0; par < 2; ++par) {
       const uint8_t* gb = static_cast<const uint8_t*>(a.gathered[a.rank]) + par * a.gathered_parity_bytes;
-      rc = encode_2d(&p->tm_a_gath[par], gb, rf.elt, rf.dt, a.M, a.K, a.K, rf.bk, kBM);
+      rc = encode_2d(&p->tm_a_gath[par], gb, rf.elt, rf.dt, a.M, a.K, ag_ld, rf.bk, kBM);
       if (rc != 0) return rc;
     }
     p->a_local = static_cast<const uint8_t*>(a.a);
@@ -240,7 +260,7 @@ int catcoc_build_params(const CatcocOpArgs* args, FusedParams* p, int* kind_out,
     if ((p->a_local_pitch & 15) != 0) { set_error("allgather: A pitch must be a multiple of 16 bytes"); return CATCOC_E_ALIGNMENT; }
     p->gathered_parity_bytes = a.gathered_parity_bytes;
     p->gathered_pitch = gpitch;
-    p->gp = make_gather_plan(a.ag_m, a.K, kBM, 512 / rf.elt);
+    p->gp = make_gather_plan(a.ag_m, ag_ld, kBM, 512 / rf.elt);
     for (int r = 0; r < a.W; ++r) {
       p->gathered[r] = static_cast<uint8_t*>(a.gathered[r]);
       p->gflags[r] = a.gflags[r];

@@ -336,7 +336,7 @@ extern "C" int catcoc_fd_recv_open(const char* sock_name) {
   return s;
 }
 
-extern "C" int catcoc_fd_recv(int listen_sock, int timeout_ms) {
+extern "C" int catcoc_fd_recv(int listen_sock, int timeout_ms, int* tag) {
   pollfd pfd = {listen_sock, POLLIN, 0};
   int pr = poll(&pfd, 1, timeout_ms);
   if (pr <= 0) { set_error("fd_recv: timed out after %d ms waiting for a peer", timeout_ms); return CATCOC_E_IO; }
@@ -355,15 +355,16 @@ extern "C" int catcoc_fd_recv(int listen_sock, int timeout_ms) {
   }
   int fd = -1;
   memcpy(&fd, CMSG_DATA(c), sizeof(int));
+  if (tag != nullptr) *tag = static_cast<unsigned char>(data);
   return fd;
 }
 
-extern "C" int catcoc_fd_send(const char* sock_name, int fd, int timeout_ms) {
+extern "C" int catcoc_fd_send(const char* sock_name, int fd, int tag, int timeout_ms) {
   int s = socket(AF_UNIX, SOCK_DGRAM | SOCK_CLOEXEC, 0);
   if (s < 0) { set_error("socket(): %s", strerror(errno)); return CATCOC_E_IO; }
   sockaddr_un addr;
   socklen_t len = abstract_addr(sock_name, &addr);
-  char data = 1;
+  char data = static_cast<char>(tag);
   iovec iov = {&data, 1};
   alignas(cmsghdr) char ctrl[CMSG_SPACE(sizeof(int))];
   memset(ctrl, 0, sizeof(ctrl));

@@ -1,0 +1,333 @@
+"""The four fused matmul + collective ops.
+
+Each call launches ONE persistent sm_100a kernel per rank (``csrc/include/catcoc/fused_gemm.cuh``):
+tcgen05 tiles fed by TMA, with the collective carried out by the kernel's own epilogue /
+communication warps over NVLink peer memory. No NCCL call is made here; the unfused
+cuBLAS + NCCL pipeline lives in :mod:`.baseline` and is only ever the thing measured against.
+
+Signatures keep the reference's per-rank tensor layouts
+(examples/00_matmul_allreduce/matmul_allreduce.cpp:51-55,
+examples/01_allgather_matmul/allgather_matmul.cpp:51-55,
+examples/02_matmul_reduce_scatter/matmul_reduce_scatter.cpp:51-55,
+examples/02_matmul_reduce_scatter/quant_matmul_reduce_scatter.cpp:55-60) and its transpose
+switches (examples/dynamic_tiling/impl/kernel_fp16.cpp:22-86); the symmetric workspace the
+reference passes as ``symmetricPtr`` is owned by the :class:`ShmemContext`.
+
+With a world size of 1 every op degenerates to the local GEMM (plus dequantisation), through
+the same kernel.
+"""
+from __future__ import annotations
+
+from typing import Optional, Tuple
+
+import torch
+
+from .. import _native as N
+from ..parallel import shmem
+from ..parallel.shmem import ShmemContext, SymmBuffer
+from ..tiling.config import TilingConfig
+from . import _common as cm
+from .gemm import matmul as _local_matmul
+
+_SEG_ROWS, _SEG_COLS = 0, 1
+
+
+def _ctx(ctx: Optional[ShmemContext]) -> ShmemContext:
+    return ctx if ctx is not None else shmem.default_context()
+
+
+def _grow(ctx: ShmemContext, key: str, nbytes: int) -> SymmBuffer:
+    """Grow-only symmetric region per purpose. Collective by construction: every rank runs the
+    same op sequence with the same shapes, so every rank allocates at the same moments. Fresh
+    regions come zero-filled (stamps start below any epoch)."""
+    buf = ctx.workspaces.get(key)
+    if buf is None or buf.nbytes < nbytes:
+        buf = ctx.malloc(nbytes)
+        ctx.workspaces[key] = buf
+    return buf
+
+
+def _resolve_tiling(op: str, m: int, n: int, k: int, world: int, dtype: torch.dtype,
+                    tiling: Optional[TilingConfig]) -> TilingConfig:
+    if tiling is not None:
+        return tiling.validate()
+    from ..tiling.chooser import choose
+    return choose(op, m, n, k, world, dtype)
+
+
+def _seg_dim_for(op: str, m: int, n: int, world: int, elt: int, trans_b: bool, t: TilingConfig) -> int:
+    """Ownership split of the all-reduce: rows while every rank still owns full 128-row tiles,
+    otherwise columns (so small M does not multiply the tensor-core work by the world size).
+    A column split of a B stored [K, N] needs 16-byte aligned segment origins for TMA."""
+    if op != "matmul_allreduce":
+        return _SEG_ROWS
+    cols_ok = trans_b or (-(-n // world)) % (16 // elt) == 0
+    if t.seg_dim == _SEG_COLS and cols_ok:
+        return _SEG_COLS
+    if t.seg_dim == _SEG_ROWS:
+        return _SEG_ROWS
+    return _SEG_ROWS if (m >= world * 128 or not cols_ok) else _SEG_COLS
+
+
+def _base_args(ctx: ShmemContext, mode: int, a: torch.Tensor, trans_a: bool, b: torch.Tensor, trans_b: bool,
+               m: int, n: int, k: int, t: TilingConfig, seg_rows: int = 0):
+    """``seg_rows`` > 0: rows per rank when ownership is split by rows. An A stored [K, M] is
+    read by TMA along M, so segment origins must then be 16-byte aligned; when they are not,
+    A is replaced by a row-major copy."""
+    oa = cm.as_operand(a, trans_a)
+    if oa.trans and seg_rows and seg_rows % (16 // a.element_size()) != 0:
+        oa = cm.as_operand(oa.tensor.t().contiguous(), False)
+        ctx.counters["pad_copies"] += 1
+    ob = cm.as_operand(b, trans_b)
+    args = N.OpArgs()
+    args.mode = mode
+    args.in_fmt = cm.in_fmt(a.dtype)
+    args.M, args.N, args.K = m, n, k
+    args.trans_a, args.trans_b = int(oa.trans), int(ob.trans)
+    args.a, args.lda = oa.ptr, oa.ld
+    args.b, args.ldb = ob.ptr, ob.ld
+    cm.fill_tiling(args, t)
+    args.rank, args.W = ctx.rank, ctx.world
+    args.epoch_ptr = ctx.launch_state.data_ptr()
+    args.cta_counter = ctx.launch_state.data_ptr() + 4
+    args.status = ctx.status.data_ptr()
+    return args, (oa, ob)
+
+
+def _attach_stage(ctx: ShmemContext, args, m: int, n: int, seg_dim: int, t: TilingConfig, partial_fmt: int) -> None:
+    lib = N.lib()
+    bn = t.effective_bn
+    stage = _grow(ctx, "stage", int(lib.catcoc_stage_bytes(m, n, ctx.world, seg_dim, bn, partial_fmt)))
+    arrive = _grow(ctx, "arrive", 4 * int(lib.catcoc_arrive_words(m, n, ctx.world, seg_dim, bn)))
+    args.partial_fmt = partial_fmt
+    for p in range(ctx.world):
+        args.stage[p] = stage.ptr(p)
+        args.arrive[p] = arrive.ptr(p)
+
+
+def _launched(ctx: ShmemContext, args) -> int:
+    """Launch and advance the host mirror of the epoch; returns the epoch of this launch."""
+    cm.launch(args, ctx.device)
+    ctx.epoch += 1
+    ctx.counters["launches"] += 1
+    return ctx.epoch
+
+
+def _check_pair(a: torch.Tensor, b: torch.Tensor) -> None:
+    if a.dtype != b.dtype:
+        raise TypeError("A and B must share a dtype (got %s, %s)" % (a.dtype, b.dtype))
+
+
+# ---------------------------------------------------------------------------------------
+def matmul_reduce_scatter(a: torch.Tensor, b: torch.Tensor, *, trans_a: bool = False, trans_b: bool = False,
+                          out: Optional[torch.Tensor] = None, tiling: Optional[TilingConfig] = None,
+                          ctx: Optional[ShmemContext] = None) -> torch.Tensor:
+    """Row-parallel linear with a scattered result.
+
+    Per rank: ``a`` ``[M, K_r]`` and ``b`` ``[K_r, N]`` (transposed storage with the flags).
+    Returns rows ``[rank*M/W, (rank+1)*M/W)`` of ``sum_r A_r @ B_r`` as ``[M/W, N]``.
+    Partials cross NVLink in the operand dtype and are summed in fp32 in a fixed rank order.
+    """
+    dev = cm.require_cuda(a, b, out)
+    _check_pair(a, b)
+    ctx = _ctx(ctx)
+    m, n, k = cm.logical_shape(a, trans_a, b, trans_b)
+    if ctx.world == 1:
+        return _local_matmul(a, b, trans_a=trans_a, trans_b=trans_b, out=out, tiling=tiling)
+    if m % ctx.world != 0:
+        raise ValueError("matmul_reduce_scatter needs M %% world == 0 (M=%d, world=%d)" % (m, ctx.world))
+    if a.dtype not in (torch.float16, torch.bfloat16):
+        raise TypeError("matmul_reduce_scatter takes fp16 / bf16 operands; see quant_matmul_reduce_scatter")
+    rows = m // ctx.world
+    if out is None:
+        out = torch.empty((rows, n), dtype=a.dtype, device=dev)
+    if tuple(out.shape) != (rows, n) or out.stride(-1) != 1 or out.dtype != a.dtype:
+        raise ValueError("out must be a row-major [%d, %d] %s tensor" % (rows, n, a.dtype))
+    t = _resolve_tiling("matmul_reduce_scatter", m, n, k, ctx.world, a.dtype, tiling)
+    with torch.cuda.device(dev):
+        args, keep = _base_args(ctx, N.MODE_RS, a, trans_a, b, trans_b, m, n, k, t, seg_rows=rows)
+        args.out, args.ldc, args.out_fmt = out.data_ptr(), out.stride(0), cm.out_fmt(out.dtype)
+        _attach_stage(ctx, args, m, n, _SEG_ROWS, t, cm.out_fmt(a.dtype))
+        _launched(ctx, args)
+    return out
+
+
+# ---------------------------------------------------------------------------------------
+def matmul_allreduce(a: torch.Tensor, b: torch.Tensor, *, trans_a: bool = False, trans_b: bool = False,
+                     out: Optional[torch.Tensor] = None, tiling: Optional[TilingConfig] = None,
+                     ctx: Optional[ShmemContext] = None) -> torch.Tensor:
+    """Row-parallel linear with the full result on every rank: ``sum_r A_r @ B_r`` as ``[M, N]``.
+
+    Two-shot inside one kernel: partial tiles are pushed to the tile's owner, the owner folds
+    them into its fp32 accumulator and writes the reduced tile into every rank's output
+    (per-peer stores, or one ``multimem.st`` through NVSwitch with ``tiling.use_multicast``).
+
+    Without ``out`` the result is a view of the symmetric heap (no extra copy); it stays valid
+    until the second-next fused call on the same context. Pass ``out`` to get a private copy.
+    """
+    dev = cm.require_cuda(a, b, out)
+    _check_pair(a, b)
+    ctx = _ctx(ctx)
+    m, n, k = cm.logical_shape(a, trans_a, b, trans_b)
+    if ctx.world == 1:
+        return _local_matmul(a, b, trans_a=trans_a, trans_b=trans_b, out=out, tiling=tiling)
+    if a.dtype not in (torch.float16, torch.bfloat16):
+        raise TypeError("matmul_allreduce takes fp16 / bf16 operands")
+    if out is not None and (tuple(out.shape) != (m, n) or out.dtype != a.dtype):
+        raise ValueError("out must be a [%d, %d] %s tensor" % (m, n, a.dtype))
+    t = _resolve_tiling("matmul_allreduce", m, n, k, ctx.world, a.dtype, tiling)
+    if t.use_multicast and not ctx.mc_base:
+        t = t.with_(use_multicast=False)
+    elt = a.element_size()
+    seg_dim = _seg_dim_for("matmul_allreduce", m, n, ctx.world, elt, trans_b, t)
+    lib = N.lib()
+    with torch.cuda.device(dev):
+        args, keep = _base_args(ctx, N.MODE_AR, a, trans_a, b, trans_b, m, n, k, t,
+                                seg_rows=(-(-m // ctx.world)) if seg_dim == _SEG_ROWS else 0)
+        args.tiling.seg_dim = seg_dim
+        parity_bytes = (m * n * elt + 255) // 256 * 256
+        obuf = _grow(ctx, "ar_out", 2 * parity_bytes)
+        done = _grow(ctx, "done", 4 * int(lib.catcoc_done_words(m, n, ctx.world, seg_dim, t.effective_bn)))
+        args.out, args.ldc, args.out_fmt = None, n, cm.out_fmt(a.dtype)
+        args.ar_out_parity_bytes = parity_bytes
+        for p in range(ctx.world):
+            args.ar_out[p] = obuf.ptr(p)
+            args.done[p] = done.ptr(p)
+        args.ar_out_mc = obuf.mc_ptr() or None
+        args.done_mc = done.mc_ptr() or None
+        _attach_stage(ctx, args, m, n, seg_dim, t, cm.out_fmt(a.dtype))
+        epoch = _launched(ctx, args)
+        view = obuf.tensor(a.dtype, (m, n), byte_offset=(epoch & 1) * parity_bytes)
+    if out is not None:
+        out.copy_(view)
+        return out
+    return view
+
+
+# ---------------------------------------------------------------------------------------
+def allgather_matmul(a_shard: torch.Tensor, b: torch.Tensor, *, trans_b: bool = False,
+                     out: Optional[torch.Tensor] = None, tiling: Optional[TilingConfig] = None,
+                     ctx: Optional[ShmemContext] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Column-parallel linear on a row-sharded activation.
+
+    Per rank: ``a_shard`` ``[m, K]`` and ``b`` ``[K, N_r]`` (``[N_r, K]`` with ``trans_b``).
+    Returns ``(out, gathered)``: ``out`` ``[W*m, N_r]`` with row block ``q`` equal to
+    ``A_q @ B_r``, and the gathered activation ``[W*m, K]`` (a view of the symmetric heap that
+    stays valid until the second-next fused call on the same context).
+
+    Communication warps of every CTA push the local shard to the peers, nearest consumer first,
+    while the tensor cores already work on the local rows; a remote row block is consumed as
+    soon as its chunk stamps arrive. ``trans_a`` is not supported, as in the reference
+    (examples/dynamic_tiling/impl/kernel_fp16.cpp:55-61).
+    """
+    dev = cm.require_cuda(a_shard, b, out)
+    _check_pair(a_shard, b)
+    ctx = _ctx(ctx)
+    if a_shard.dim() != 2:
+        raise ValueError("a_shard must be 2-D")
+    m, k = a_shard.shape
+    kb, n = (b.shape[1], b.shape[0]) if trans_b else (b.shape[0], b.shape[1])
+    if k != kb:
+        raise ValueError("inner dimensions differ: A gives K=%d, B gives K=%d" % (k, kb))
+    if ctx.world == 1:
+        o = _local_matmul(a_shard, b, trans_b=trans_b, out=out, tiling=tiling)
+        return o, a_shard
+    if a_shard.dtype not in (torch.float16, torch.bfloat16):
+        raise TypeError("allgather_matmul takes fp16 / bf16 operands")
+    W = ctx.world
+    if out is None:
+        out = torch.empty((W * m, n), dtype=a_shard.dtype, device=dev)
+    if tuple(out.shape) != (W * m, n) or out.stride(-1) != 1 or out.dtype != a_shard.dtype:
+        raise ValueError("out must be a row-major [%d, %d] %s tensor" % (W * m, n, a_shard.dtype))
+    elt = a_shard.element_size()
+    t = _resolve_tiling("allgather_matmul", W * m, n, k, W, a_shard.dtype, tiling)
+    lib = N.lib()
+    with torch.cuda.device(dev):
+        # The gathered buffer has a dense pitch of ag_ld >= K elements (16-byte multiple); the
+        # shard is copied row by row with that width, so it needs a TMA-legal pitch itself.
+        per16 = 16 // elt
+        ag_ld = (k + per16 - 1) // per16 * per16
+        a_src = a_shard
+        if a_shard.stride(-1) != 1 or (a_shard.stride(0) * elt) % 16 or a_shard.data_ptr() % 16 \
+                or a_shard.stride(0) < ag_ld:
+            a_src = cm.pad_rows(a_shard)
+            ctx.counters["pad_copies"] += 1
+        ob = cm.as_operand(b, trans_b)
+        args = N.OpArgs()
+        args.mode = N.MODE_AG
+        args.in_fmt = cm.in_fmt(a_shard.dtype)
+        args.M, args.N, args.K = W * m, n, k
+        args.trans_a, args.trans_b = 0, int(ob.trans)
+        args.a, args.lda = a_src.data_ptr(), a_src.stride(0)
+        args.b, args.ldb = ob.ptr, ob.ld
+        cm.fill_tiling(args, t)
+        args.rank, args.W = ctx.rank, W
+        args.epoch_ptr = ctx.launch_state.data_ptr()
+        args.cta_counter = ctx.launch_state.data_ptr() + 4
+        args.status = ctx.status.data_ptr()
+        args.ag_m, args.ag_ld = m, ag_ld
+        parity_bytes = (W * m * ag_ld * elt + 255) // 256 * 256
+        gbuf = _grow(ctx, "gathered", 2 * parity_bytes)
+        gfl = _grow(ctx, "gflags", 4 * int(lib.catcoc_gather_flag_words(m, ag_ld, W, elt)))
+        args.gathered_parity_bytes = parity_bytes
+        for p in range(W):
+            args.gathered[p] = gbuf.ptr(p)
+            args.gflags[p] = gfl.ptr(p)
+        args.out, args.ldc, args.out_fmt = out.data_ptr(), out.stride(0), cm.out_fmt(out.dtype)
+        args.partial_fmt = args.out_fmt
+        epoch = _launched(ctx, args)
+        gathered = gbuf.tensor(a_shard.dtype, (W * m, ag_ld), byte_offset=(epoch & 1) * parity_bytes)
+        if ag_ld != k:
+            gathered = gathered[:, :k]
+    return out, gathered
+
+
+# ---------------------------------------------------------------------------------------
+def quant_matmul_reduce_scatter(x1: torch.Tensor, x2: torch.Tensor, scale_x1: torch.Tensor, scale_x2: torch.Tensor,
+                                bias: Optional[torch.Tensor] = None, *, trans_a: bool = False, trans_b: bool = False,
+                                out_dtype: torch.dtype = torch.bfloat16, out: Optional[torch.Tensor] = None,
+                                tiling: Optional[TilingConfig] = None,
+                                ctx: Optional[ShmemContext] = None) -> torch.Tensor:
+    """int8 row-parallel linear with an exact int32 reduce-scatter and fused dequantisation.
+
+    Per rank: ``x1`` int8 ``[M, K_r]``, ``x2`` int8 ``[K_r, N]``, ``scale_x1`` fp32 ``[M]``
+    (per token, indexed by the global row), ``scale_x2`` fp32 ``[N]`` (per channel), optional
+    ``bias`` int32 ``[N]``. Returns ``[M/W, N]``:
+
+        cast( float( sum_q (x1_q @ x2_q + bias) )[rows of this rank] * scale_x1[rows, None] * scale_x2[None, :] )
+
+    The bias is added on every rank, so the sum carries ``W * bias`` exactly as in the
+    reference (examples/utils/gen_quant_data.py:61-72). int32 partial tiles cross NVLink
+    unrounded; the sum is exact and order-free, the scales are applied once on the owner.
+    """
+    dev = cm.require_cuda(x1, x2, scale_x1, scale_x2, bias, out)
+    if x1.dtype != torch.int8 or x2.dtype != torch.int8:
+        raise TypeError("x1 and x2 must be int8")
+    if out_dtype not in (torch.float16, torch.bfloat16, torch.float32):
+        raise TypeError("out_dtype must be fp16, bf16 or fp32")
+    ctx = _ctx(ctx)
+    m, n, k = cm.logical_shape(x1, trans_a, x2, trans_b)
+    for name, s, length, dt in (("scale_x1", scale_x1, m, torch.float32), ("scale_x2", scale_x2, n, torch.float32),
+                                ("bias", bias, n, torch.int32)):
+        if s is not None and (s.dtype != dt or s.numel() != length or not s.is_contiguous()):
+            raise ValueError("%s must be a contiguous %s tensor of %d elements" % (name, dt, length))
+    if ctx.world == 1:
+        return _local_matmul(x1, x2, trans_a=trans_a, trans_b=trans_b, out=out, out_dtype=out_dtype,
+                             scale_m=scale_x1, scale_n=scale_x2, bias=bias, tiling=tiling)
+    if m % ctx.world != 0:
+        raise ValueError("quant_matmul_reduce_scatter needs M %% world == 0 (M=%d, world=%d)" % (m, ctx.world))
+    rows = m // ctx.world
+    if out is None:
+        out = torch.empty((rows, n), dtype=out_dtype, device=dev)
+    if tuple(out.shape) != (rows, n) or out.stride(-1) != 1 or out.dtype != out_dtype:
+        raise ValueError("out must be a row-major [%d, %d] %s tensor" % (rows, n, out_dtype))
+    t = _resolve_tiling("quant_matmul_reduce_scatter", m, n, k, ctx.world, x1.dtype, tiling)
+    with torch.cuda.device(dev):
+        args, keep = _base_args(ctx, N.MODE_RS, x1, trans_a, x2, trans_b, m, n, k, t, seg_rows=rows)
+        args.out, args.ldc, args.out_fmt = out.data_ptr(), out.stride(0), cm.out_fmt(out_dtype)
+        args.scale_m = scale_x1.data_ptr()
+        args.scale_n = scale_x2.data_ptr()
+        args.bias = bias.data_ptr() if bias is not None else None
+        _attach_stage(ctx, args, m, n, _SEG_ROWS, t, N.FMT_S32)
+        _launched(ctx, args)
+    return out

@@ -1,0 +1,47 @@
+"""Runtime tiling chooser: (op, M, N, K, world, dtype) -> :class:`TilingConfig`.
+
+Order of precedence: an exact hit in the measured table, the nearest measured shape of the
+same op / world / dtype in log-space (within a factor of two per dimension), then a heuristic
+derived from the roofline: small outputs cannot fill 148 SMs with 128 x 256 tiles, so the tile
+narrows until there is at least one tile per SM; everything else runs the widest tile, which
+has the best tensor-core to shared-memory ratio.
+
+The reference only has the offline half of this (a sweep whose best rows are picked by hand,
+examples/dynamic_tiling/utils/get_best_res.py:43-83; the default it falls back to is a
+constant, examples/dynamic_tiling/dynamic_tiling.cpp:219-227).
+"""
+from __future__ import annotations
+
+import math
+from typing import Optional
+
+import torch
+
+from .config import TilingConfig
+from . import table as _table
+
+_NUM_SMS = 148
+
+
+def heuristic(op: str, m: int, n: int, k: int, world: int, dtype: torch.dtype) -> TilingConfig:
+    rows = m
+    tiles_m = max(1, math.ceil(rows / 128))
+    bn = 256
+    for cand in (256, 128, 64):
+        bn = cand
+        if tiles_m * math.ceil(n / cand) >= _NUM_SMS:
+            break
+    if dtype == torch.int8 and bn < 128:
+        bn = 128  # 8-bit [K, N] operands need a full 128-byte run of N per TMA box
+    # column-group width: keep the concurrently running tiles roughly square in (rows, cols)
+    swizzle = 8 if tiles_m >= 8 else max(1, min(16, _NUM_SMS // max(1, tiles_m)))
+    return TilingConfig(bn=bn, swizzle=swizzle)
+
+
+def choose(op: str, m: int, n: int, k: int, world: int, dtype: torch.dtype,
+           table: Optional["_table.TilingTable"] = None) -> TilingConfig:
+    tbl = table if table is not None else _table.default_table()
+    hit = tbl.lookup(op, m, n, k, world, dtype)
+    if hit is not None:
+        return hit
+    return heuristic(op, m, n, k, world, dtype)
