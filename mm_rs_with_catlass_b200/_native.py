@@ -34,7 +34,7 @@ STATUS_NAMES = {
 
 class Tiling(C.Structure):
     _fields_ = [("bn", C.c_int), ("swizzle", C.c_int), ("num_ctas", C.c_int), ("seg_dim", C.c_int),
-                ("use_multicast", C.c_int)]
+                ("use_multicast", C.c_int), ("cta_pair", C.c_int)]
 
 
 class OpArgs(C.Structure):
@@ -93,9 +93,9 @@ def _declare(lib) -> None:
         "catcoc_version": (i32, []),
         "catcoc_num_sms": (i32, [i32]),
         "catcoc_fused_launch": (i32, [P(OpArgs), vp]),
-        "catcoc_stage_bytes": (i64, [i32, i32, i32, i32, i32, i32]),
-        "catcoc_arrive_words": (i64, [i32, i32, i32, i32, i32]),
-        "catcoc_done_words": (i64, [i32, i32, i32, i32, i32]),
+        "catcoc_stage_bytes": (i64, [i32, i32, i32, i32, i32, i32, i32]),
+        "catcoc_arrive_words": (i64, [i32, i32, i32, i32, i32, i32]),
+        "catcoc_done_words": (i64, [i32, i32, i32, i32, i32, i32]),
         "catcoc_gather_flag_words": (i64, [i32, i32, i32, i32]),
         "catcoc_sched_total_tiles": (i32, [i32] * 6),
         "catcoc_sched_get_tile": (i32, [i32] * 9 + [P(Tile)]),

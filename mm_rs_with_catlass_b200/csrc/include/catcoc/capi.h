@@ -43,6 +43,7 @@ typedef struct CatcocTiling {
   int num_ctas;    /* persistent CTAs (0 = one per SM)                                   */
   int seg_dim;     /* all-reduce ownership split: 0 rows, 1 cols, -1 auto                */
   int use_multicast; /* all-reduce broadcast through the NVLS multicast alias if mapped  */
+  int cta_pair;    /* 2: 256-row tiles on 2-CTA clusters (tcgen05 cta_group::2); else 1 CTA */
 } CatcocTiling;
 
 typedef struct CatcocOpArgs {
@@ -86,9 +87,9 @@ int catcoc_version(void);
 int catcoc_fused_launch(const CatcocOpArgs* args, void* stream);
 
 /* Workspace sizes (bytes / words) for given problem + tiling, identical on every rank. */
-int64_t catcoc_stage_bytes(int M, int N, int W, int seg_dim, int bn, int partial_fmt);
-int64_t catcoc_arrive_words(int M, int N, int W, int seg_dim, int bn);
-int64_t catcoc_done_words(int M, int N, int W, int seg_dim, int bn);
+int64_t catcoc_stage_bytes(int M, int N, int W, int seg_dim, int bn, int cta_pair, int partial_fmt);
+int64_t catcoc_arrive_words(int M, int N, int W, int seg_dim, int bn, int cta_pair);
+int64_t catcoc_done_words(int M, int N, int W, int seg_dim, int bn, int cta_pair);
 int64_t catcoc_gather_flag_words(int m, int K, int W, int elt_bytes);
 int catcoc_num_sms(int device);
 

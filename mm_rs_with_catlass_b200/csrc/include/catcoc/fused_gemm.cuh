@@ -31,22 +31,32 @@
 
 namespace catcoc {
 
-constexpr int kBM = 128;               // tile rows == UMMA M == TMEM lanes
+constexpr int kBM = 128;               // rows per CTA == TMEM lanes
 constexpr int kMaxBN = 256;            // tile cols upper bound == TMEM columns per accumulator
-constexpr int kStages = 4;             // smem ring depth
 constexpr int kABytes = kBM * 128;     // A stage: 128 rows x 128 B (K-major) or the MN-major equal
-constexpr int kBBytesMax = kMaxBN * 128;
-constexpr int kStageBytes = kABytes + kBBytesMax;  // 48 KiB
 constexpr int kEpiWarps = 4;
 constexpr int kEpiStageBytes = 32 * 128;           // per epilogue warp: 32 rows x 128 B
 constexpr int kThreads = 256;
 constexpr int kTmemCols = 512;
-constexpr int kSmemBytes =
-    kStages * kStageBytes + kEpiWarps * kEpiStageBytes + 256 /*barriers*/ + 1024 /*align slack*/;
+constexpr int kMaxStages = 6;
+
+// Two flavours of the same kernel:
+//   single : one CTA per 128 x bn tile, B stage = bn rows            (48 KiB / stage, 4 stages)
+//   pair   : a 2-CTA cluster per 256 x bn tile (tcgen05 cta_group::2). Each CTA loads its own
+//            128 rows of A and HALF of the B tile; the pair's leader issues one MMA that reads
+//            both halves, so operand traffic into shared memory per FLOP halves
+//                                                                     (32 KiB / stage, 6 stages)
+template <bool CTA2> struct Geo {
+  static constexpr int kStages = CTA2 ? 6 : 4;
+  static constexpr int kBBytesMax = (CTA2 ? kMaxBN / 2 : kMaxBN) * 128;
+  static constexpr int kStageBytes = kABytes + kBBytesMax;
+  static constexpr int kSmemBytes =
+      kStages * kStageBytes + kEpiWarps * kEpiStageBytes + 256 /*barriers*/ + 1024 /*align slack*/;
+};
 
 struct SmemTail {
-  uint64_t full[kStages];
-  uint64_t empty[kStages];
+  uint64_t full[kMaxStages];
+  uint64_t empty[kMaxStages];
   uint64_t acc_full[2];
   uint64_t acc_empty[2];
   uint32_t tmem_base;
@@ -163,9 +173,12 @@ CATCOC_DEVICE void flush_staged(uint32_t stg, int lane, uint8_t* base, int64_t p
 // ---------------------------------------------------------------------------------------
 // The kernel
 // ---------------------------------------------------------------------------------------
-template <int KIND>
+template <int KIND, bool CTA2>
 __global__ void __launch_bounds__(kThreads, 1)
 fused_gemm_kernel(const __grid_constant__ FusedParams p) {
+  using G = Geo<CTA2>;
+  constexpr int kStages = G::kStages;
+  constexpr int kStageBytes = G::kStageBytes;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
@@ -178,8 +191,15 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
   const TileSched& sched = p.sched;
   const int BN = sched.BN;
   const int num_kb = ceil_div(p.K, p.bk);
-  const uint32_t b_stage_bytes = static_cast<uint32_t>(BN) * 128u;
   const bool fused = (p.mode != MODE_LOCAL) && (p.W > 1);
+  // Pair flavour: `sub` is this CTA's half of the 256-row tile, work is dealt out per pair.
+  const int sub = CTA2 ? static_cast<int>(ptx::cluster_ctarank()) : 0;
+  const bool leader = (sub == 0);
+  const int worker = CTA2 ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
+  const int num_workers = CTA2 ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
+  const int b_cols_cta = CTA2 ? BN / 2 : BN;   // columns of the B tile this CTA loads
+  const uint32_t b_stage_bytes = static_cast<uint32_t>(b_cols_cta) * 128u;
+  const int qpt = sched.BM / 32;               // 32-row quarters per tile: 4 (single) or 8 (pair)
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
@@ -188,7 +208,7 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
     }
     for (int b = 0; b < 2; ++b) {
       ptx::mbar_init(&tail->acc_full[b], 1);
-      ptx::mbar_init(&tail->acc_empty[b], kEpiWarps);
+      ptx::mbar_init(&tail->acc_empty[b], CTA2 ? 2 * kEpiWarps : kEpiWarps);
     }
     tail->abort_flag = 0;
     ptx::mbar_fence_init();
@@ -196,11 +216,17 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
     ptx::prefetch_tmap(&p.tm_b);
   }
   if (warp == 1) {
-    ptx::tmem_alloc(&tail->tmem_base, kTmemCols);
-    ptx::tmem_relinquish();
+    if (CTA2) {
+      ptx::tmem_alloc_pair(&tail->tmem_base, kTmemCols);
+      ptx::tmem_relinquish_pair();
+    } else {
+      ptx::tmem_alloc(&tail->tmem_base, kTmemCols);
+      ptx::tmem_relinquish();
+    }
   }
   ptx::tcgen05_fence_before();
   __syncthreads();
+  if (CTA2) ptx::cluster_sync_all();   // the peer's barriers exist before anyone signals them
   ptx::tcgen05_fence_after();
   const uint32_t tmem_base = tail->tmem_base;
 
@@ -215,13 +241,14 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
     uint32_t phase = 0;
     uint32_t issued_mask = 0, issued_parity = 0;
     bool ok = true;
-    for (int t = blockIdx.x; ok && t < sched.total_tiles; t += gridDim.x) {
+    for (int t = worker; ok && t < sched.total_tiles; t += num_workers) {
       const TileInfo ti = get_tile(sched, t);
       const CUtensorMap* tma = &p.tm_a;
-      int a_row = ti.m0;
+      int a_row = ti.m0 + sub * kBM;
+      const int b_col = ti.n0 + sub * b_cols_cta;
       if (p.mode == MODE_AG && p.W > 1) {
         if (ti.seg == p.rank) {
-          a_row = ti.mi * sched.BM;  // row inside the local shard
+          a_row = ti.mi * sched.BM + sub * kBM;  // row inside the local shard
         } else {
           // wait until every K-slice of this row chunk of source `seg` has landed here
           const uint32_t* fl = p.gflags[p.rank];
@@ -254,26 +281,43 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
         if (lane == 0) {
           uint8_t* sa = smem + stage * kStageBytes;
           uint8_t* sb = sa + kABytes;
-          ptx::mbar_expect_tx(&tail->full[stage], kABytes + b_stage_bytes);
           const int k0 = kb * p.bk;
-          if (!p.a_mn_major) {
-            ptx::tma_load_2d(sa, tma, &tail->full[stage], k0, a_row);
+          const int per_box = 128 / p.elt_bytes_a;
+          if (!CTA2) {
+            ptx::mbar_expect_tx(&tail->full[stage], kABytes + b_stage_bytes);
+            if (!p.a_mn_major) {
+              ptx::tma_load_2d(sa, tma, &tail->full[stage], k0, a_row);
+            } else {
+              // storage [K, M]: boxes of 128 B along M x bk rows of K
+              for (int j = 0; j < kBM / per_box; ++j)
+                ptx::tma_load_2d(sa + j * (p.bk * 128), tma, &tail->full[stage],
+                                 a_row + j * per_box, k0);
+            }
+            if (!p.b_mn_major) {
+              ptx::tma_load_2d(sb, &p.tm_b, &tail->full[stage], k0, b_col);
+            } else {
+              for (int j = 0; j < b_cols_cta / per_box; ++j)
+                ptx::tma_load_2d(sb + j * (p.bk * 128), &p.tm_b, &tail->full[stage],
+                                 b_col + j * per_box, k0);
+            }
           } else {
-            // storage [K, M]: boxes of 128 B along M x bk rows of K
-            const int per_box = 128 / p.elt_bytes_a;
-            const int nbox = kBM / per_box;
-            for (int j = 0; j < nbox; ++j)
-              ptx::tma_load_2d(sa + j * (p.bk * 128), tma, &tail->full[stage],
-                               a_row + j * per_box, k0);
-          }
-          if (!p.b_mn_major) {
-            ptx::tma_load_2d(sb, &p.tm_b, &tail->full[stage], k0, ti.n0);
-          } else {
-            const int per_box = 128 / p.elt_bytes_a;
-            const int nbox = BN / per_box;
-            for (int j = 0; j < nbox; ++j)
-              ptx::tma_load_2d(sb + j * (p.bk * 128), &p.tm_b, &tail->full[stage],
-                               ti.n0 + j * per_box, k0);
+            // Both CTAs' copies are credited to the leader's barrier; only the leader arms it,
+            // with the bytes of the whole pair.
+            const uint32_t bar = ptx::map_to_cta(ptx::smem_u32(&tail->full[stage]), 0u);
+            if (leader) ptx::mbar_expect_tx(&tail->full[stage], 2u * (kABytes + b_stage_bytes));
+            if (!p.a_mn_major) {
+              ptx::tma_load_2d_pair(sa, tma, bar, k0, a_row);
+            } else {
+              for (int j = 0; j < kBM / per_box; ++j)
+                ptx::tma_load_2d_pair(sa + j * (p.bk * 128), tma, bar, a_row + j * per_box, k0);
+            }
+            if (!p.b_mn_major) {
+              ptx::tma_load_2d_pair(sb, &p.tm_b, bar, k0, b_col);
+            } else {
+              for (int j = 0; j < b_cols_cta / per_box; ++j)
+                ptx::tma_load_2d_pair(sb + j * (p.bk * 128), &p.tm_b, bar, b_col + j * per_box,
+                                      k0);
+            }
           }
           issued_mask |= 1u << stage;
           issued_parity = (issued_parity & ~(1u << stage)) | (phase << stage);
@@ -282,7 +326,7 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
         if (++stage == kStages) { stage = 0; phase ^= 1u; }
       }
     }
-    if (*abort_flag && lane == 0) {
+    if (*abort_flag && lane == 0 && leader) {
       // let every bulk copy this thread started land before the CTA's smem goes away
       volatile uint32_t never = 0;
       for (int s = 0; s < kStages; ++s)
@@ -291,7 +335,7 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
     }
   } else if (warp == 1) {
     // =============================== MMA issuer ===============================
-    if (lane == 0) {
+    if (lane == 0 && leader) {
       int stage = 0;
       uint32_t phase = 0;
       int acc = 0;
@@ -302,7 +346,7 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
       const uint32_t a_kstep = p.a_mn_major ? static_cast<uint32_t>(p.umma_k) * 128u : 32u;
       const uint32_t b_kstep = p.b_mn_major ? static_cast<uint32_t>(p.umma_k) * 128u : 32u;
       const int k_per_stage = p.bk / p.umma_k;
-      for (int t = blockIdx.x; ok && t < sched.total_tiles; t += gridDim.x) {
+      for (int t = worker; ok && t < sched.total_tiles; t += num_workers) {
         if (!ptx::mbar_wait(&tail->acc_empty[acc], acc_phase ^ 1u, p.timeout_ns, abort_flag)) {
           report_status(p, STATUS_TIMEOUT_PIPELINE, 1u, static_cast<uint32_t>(t), 0u, 0u);
           *abort_flag = 1;
@@ -329,22 +373,32 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
             const uint64_t da = ptx::make_smem_desc_sw128(sa + k * a_kstep, a_lbo, 1024u);
             const uint64_t db = ptx::make_smem_desc_sw128(sb + k * b_kstep, b_lbo, 1024u);
             const uint32_t accum = (kb | k) != 0 ? 1u : 0u;
-            if (KIND == KIND_F16) ptx::umma_f16(tmem_d, da, db, p.idesc, accum);
-            else if (KIND == KIND_I8) ptx::umma_i8(tmem_d, da, db, p.idesc, accum);
-            else ptx::umma_f8f6f4(tmem_d, da, db, p.idesc, accum);
+            if (CTA2) {
+              if (KIND == KIND_F16) ptx::umma_f16_pair(tmem_d, da, db, p.idesc, accum);
+              else if (KIND == KIND_I8) ptx::umma_i8_pair(tmem_d, da, db, p.idesc, accum);
+              else ptx::umma_f8f6f4_pair(tmem_d, da, db, p.idesc, accum);
+            } else {
+              if (KIND == KIND_F16) ptx::umma_f16(tmem_d, da, db, p.idesc, accum);
+              else if (KIND == KIND_I8) ptx::umma_i8(tmem_d, da, db, p.idesc, accum);
+              else ptx::umma_f8f6f4(tmem_d, da, db, p.idesc, accum);
+            }
           }
-          ptx::tcgen05_commit(&tail->empty[stage]);
+          // frees this smem stage (in both CTAs of a pair) once the MMAs above retire
+          if (CTA2) ptx::tcgen05_commit_pair(&tail->empty[stage], 3);
+          else ptx::tcgen05_commit(&tail->empty[stage]);
           if (++stage == kStages) { stage = 0; phase ^= 1u; }
         }
         if (!ok) break;
-        ptx::tcgen05_commit(&tail->acc_full[acc]);
+        if (CTA2) ptx::tcgen05_commit_pair(&tail->acc_full[acc], 3);
+        else ptx::tcgen05_commit(&tail->acc_full[acc]);
         acc ^= 1;
         if (acc == 0) acc_phase ^= 1u;
       }
       if (*abort_flag) {
         // wait (bounded) for the tensor core to retire what was issued before TMEM is freed
         volatile uint32_t never = 0;
-        ptx::tcgen05_commit(&tail->acc_full[acc]);
+        if (CTA2) ptx::tcgen05_commit_pair(&tail->acc_full[acc], 3);
+        else ptx::tcgen05_commit(&tail->acc_full[acc]);
         ptx::mbar_wait(&tail->acc_full[acc], acc_phase, 2000000ull, &never);
       }
     }
@@ -355,7 +409,9 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
     // cannot strand the others at a barrier.
     const int q = warp & 3;                 // TMEM lane quarter this warp may read
     const uint32_t stg = ptx::smem_u32(epi_stage + (warp - 2) * kEpiStageBytes);
-    const int row_in_tile = q * 32 + lane;
+    const int row_base = sub * kBM + q * 32;   // first tile row of this warp
+    const int row_in_tile = row_base + lane;
+    const int qid = sub * 4 + q;               // quarter index inside the tile
     const bool is_int = (KIND == KIND_I8);
     const bool dequant = (p.scale_m != nullptr) || (p.scale_n != nullptr);
     const int pfmt = p.partial_fmt;
@@ -364,19 +420,19 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
     uint32_t acc_phase = 0;
     bool ok = true;
 
-    for (int t = blockIdx.x; ok && t < sched.total_tiles; t += gridDim.x) {
+    for (int t = worker; ok && t < sched.total_tiles; t += num_workers) {
       const TileInfo ti = get_tile(sched, t);
       const bool own = !fused || (p.mode == MODE_AG) || (ti.seg == p.rank);
       const bool reduce_here = fused && own && (p.mode == MODE_RS || p.mode == MODE_AR);
       const int st_fmt = own ? p.out_fmt : pfmt;   // format of what this tile's epilogue stores
       const int st_elt = fmt_bytes(st_fmt);
-      const int rows_valid = max(0, min(32, ti.rows - q * 32));
+      const int rows_valid = max(0, min(32, ti.rows - row_base));
 
       if (reduce_here) {
         // the peers' rows [32q, 32q+32) of this tile must have landed in my staging slabs
         if (lane < p.W && lane != p.rank) {
           uint32_t seen = 0;
-          const int64_t idx = arrive_flag_index(sched, ti.tile_in_seg, lane) * 4 + q;
+          const int64_t idx = arrive_flag_index(sched, ti.tile_in_seg, lane) * qpt + qid;
           if (!wait_stamp(p.arrive[p.rank] + idx, epoch, p.timeout_ns, abort_flag, &seen)) {
             report_status(p, STATUS_TIMEOUT_ARRIVE, static_cast<uint32_t>(ti.tile_in_seg), epoch,
                           seen, static_cast<uint32_t>(lane));
@@ -409,11 +465,11 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
       if (!own) {
         pitch = static_cast<int64_t>(BN) * st_elt;
         base = p.stage[ti.seg] + stage_slot_offset(sched, st_elt, parity, p.rank, ti.tile_in_seg) +
-               static_cast<int64_t>(q * 32) * pitch;
+               static_cast<int64_t>(row_base) * pitch;
       } else if (fused && p.mode == MODE_AR) {
         pitch = p.ldc * st_elt;
         off = static_cast<int64_t>(parity) * p.ar_out_parity_bytes +
-              (static_cast<int64_t>(ti.m0 + q * 32) * p.ldc + ti.n0) * st_elt;
+              (static_cast<int64_t>(ti.m0 + row_base) * p.ldc + ti.n0) * st_elt;
         vec_ok = (p.out_vec_ok != 0) && ((ti.n0 * st_elt) % 16 == 0);
         if (p.ar_out_mc != nullptr && vec_ok && (ti.cols % (16 / st_elt) == 0)) {
           mc = p.ar_out_mc + off;
@@ -423,7 +479,7 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
       } else {
         pitch = p.ldc * st_elt;
         base = static_cast<uint8_t*>(p.out) +
-               (static_cast<int64_t>(ti.m0 + q * 32 - p.out_row_shift) * p.ldc + ti.n0) * st_elt;
+               (static_cast<int64_t>(ti.m0 + row_base - p.out_row_shift) * p.ldc + ti.n0) * st_elt;
         vec_ok = (p.out_vec_ok != 0) && ((ti.n0 * st_elt) % 16 == 0);
       }
 
@@ -446,7 +502,10 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
             // every TMEM read of this tile is done: hand the accumulator back to the MMA warp
             ptx::tcgen05_fence_before();
             __syncwarp();
-            if (lane == 0) ptx::mbar_arrive(&tail->acc_empty[acc]);
+            if (lane == 0) {
+              if (CTA2) ptx::mbar_arrive_cluster(ptx::map_to_cta(ptx::smem_u32(&tail->acc_empty[acc]), 0u));
+              else ptx::mbar_arrive(&tail->acc_empty[acc]);
+            }
             released = true;
           }
 
@@ -558,7 +617,10 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
         // degenerate (empty) tile: nothing was read, still return the accumulator
         ptx::tcgen05_fence_before();
         __syncwarp();
-        if (lane == 0) ptx::mbar_arrive(&tail->acc_empty[acc]);
+        if (lane == 0) {
+          if (CTA2) ptx::mbar_arrive_cluster(ptx::map_to_cta(ptx::smem_u32(&tail->acc_empty[acc]), 0u));
+          else ptx::mbar_arrive(&tail->acc_empty[acc]);
+        }
       }
 
       // ---- publish this warp's quarter of the tile ----
@@ -569,11 +631,11 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
           if (!own) {
             if (lane == 0)
               ptx::st_release_sys_u32(
-                  p.arrive[ti.seg] + arrive_flag_index(sched, ti.tile_in_seg, p.rank) * 4 + q,
+                  p.arrive[ti.seg] + arrive_flag_index(sched, ti.tile_in_seg, p.rank) * qpt + qid,
                   epoch);
           } else {
             // the reduced rows are in every rank's output: stamp them everywhere
-            const int gid = (ti.seg * sched.tiles_per_seg + ti.tile_in_seg) * 4 + q;
+            const int gid = (ti.seg * sched.tiles_per_seg + ti.tile_in_seg) * qpt + qid;
             if (p.done_mc != nullptr && mc != nullptr) {
               if (lane == 0) ptx::multimem_st_release_u32(p.done_mc + gid, epoch);
             } else if (lane < p.W) {
@@ -590,12 +652,12 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
     // all-reduce tail: this rank's output is complete only when every owner's tiles landed
     if (fused && p.mode == MODE_AR && ok && !*abort_flag) {
       const int et = (warp - 2) * 32 + lane;
-      const int nstamps = sched.total_tiles * 4;
+      const int nstamps = sched.total_tiles * qpt;
       for (int j = blockIdx.x + et * gridDim.x; j < nstamps; j += gridDim.x * kEpiWarps * 32) {
         uint32_t seen = 0;
         if (!wait_stamp(p.done[p.rank] + j, epoch, p.timeout_ns, abort_flag, &seen)) {
           report_status(p, STATUS_TIMEOUT_DONE, static_cast<uint32_t>(j), epoch, seen,
-                        static_cast<uint32_t>((j / 4) / sched.tiles_per_seg));
+                        static_cast<uint32_t>((j / qpt) / sched.tiles_per_seg));
           *abort_flag = 1;
           break;
         }
@@ -653,8 +715,12 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
   // =============================== teardown ===============================
   ptx::tcgen05_fence_before();
   __syncthreads();
+  if (CTA2) ptx::cluster_sync_all();   // neither CTA of a pair leaves while the other may touch it
   ptx::tcgen05_fence_after();
-  if (warp == 1) ptx::tmem_dealloc(tmem_base, kTmemCols);
+  if (warp == 1) {
+    if (CTA2) ptx::tmem_dealloc_pair(tmem_base, kTmemCols);
+    else ptx::tmem_dealloc(tmem_base, kTmemCols);
+  }
   if (fused && threadIdx.x == 0) {
     // the last CTA to finish publishes the new epoch for the next launch on this stream
     __threadfence();

@@ -229,6 +229,77 @@ CATCOC_DEVICE void tmem_ld_32x32b_x32(uint32_t taddr, uint32_t (&r)[32]) {
 }
 
 // ---------------------------------------------------------------------------------------
+// CTA pairs (thread-block clusters of 2) for tcgen05 cta_group::2
+// ---------------------------------------------------------------------------------------
+CATCOC_DEVICE uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+CATCOC_DEVICE void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Address of the same shared-memory location in CTA `rank` of this cluster.
+CATCOC_DEVICE uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+  return r;
+}
+CATCOC_DEVICE void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr)
+               : "memory");
+}
+// TMA load issued by either CTA of a pair; completion bytes are credited to `bar_cluster_addr`,
+// which may live in the peer CTA (the pair's leader).
+CATCOC_DEVICE void tma_load_2d_pair(void* smem_dst, const void* tmap, uint32_t bar_cluster_addr,
+                                    int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(smem_dst)),
+      "l"(reinterpret_cast<uint64_t>(tmap)), "r"(bar_cluster_addr), "r"(x), "r"(y)
+      : "memory");
+}
+CATCOC_DEVICE void tmem_alloc_pair(uint32_t* smem_result, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                   smem_u32(smem_result)),
+               "r"(ncols)
+               : "memory");
+}
+CATCOC_DEVICE void tmem_relinquish_pair() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+CATCOC_DEVICE void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols)
+               : "memory");
+}
+// Arrives on the barrier at the same shared-memory offset in every CTA of `cta_mask` once all
+// tcgen05.mma issued so far by this thread have completed.
+CATCOC_DEVICE void tcgen05_commit_pair(uint64_t* bar, uint16_t cta_mask) {
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+      ::"r"(smem_u32(bar)), "h"(cta_mask)
+      : "memory");
+}
+#define CATCOC_UMMA_PAIR(NAME, KINDSTR)                                                          \
+  CATCOC_DEVICE void NAME(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,       \
+                          uint32_t accumulate) {                                                   \
+    asm volatile(                                                                                  \
+        "{\n\t"                                                                                    \
+        ".reg .pred p;\n\t"                                                                        \
+        "setp.ne.b32 p, %4, 0;\n\t"                                                                \
+        "tcgen05.mma.cta_group::2.kind::" KINDSTR " [%0], %1, %2, %3, p;\n\t"                      \
+        "}\n" ::"r"(tmem_d),                                                                       \
+        "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)                                      \
+        : "memory");                                                                               \
+  }
+CATCOC_UMMA_PAIR(umma_f16_pair, "f16")
+CATCOC_UMMA_PAIR(umma_i8_pair, "i8")
+CATCOC_UMMA_PAIR(umma_f8f6f4_pair, "f8f6f4")
+#undef CATCOC_UMMA_PAIR
+
+// ---------------------------------------------------------------------------------------
 // Scoped global loads / stores used for cross-GPU signalling and data movement
 // ---------------------------------------------------------------------------------------
 CATCOC_DEVICE uint32_t ld_acquire_sys_u32(const uint32_t* p) {

@@ -125,13 +125,13 @@ static int pick_seg_dim(const CatcocOpArgs& a) {
   return (a.M >= a.W * kBM) ? SEG_ROWS : SEG_COLS;
 }
 
-static TileSched build_sched(const CatcocOpArgs& a, int bn, int seg_dim) {
+static TileSched build_sched(const CatcocOpArgs& a, int bm, int bn, int seg_dim) {
   const bool fused = a.mode != CATCOC_MODE_LOCAL && a.W > 1;
   const int W = fused ? a.W : 1;
   int first = 0;
   if (fused) first = (a.mode == CATCOC_MODE_AG) ? a.rank : (a.rank + 1) % W;
   const int swz = a.tiling.swizzle > 0 ? a.tiling.swizzle : 8;
-  return make_sched(a.M, a.N, kBM, bn, W, seg_dim, first, swz);
+  return make_sched(a.M, a.N, bm, bn, W, seg_dim, first, swz);
 }
 
 }  // namespace host
@@ -146,17 +146,19 @@ extern "C" int catcoc_num_sms(int device) { return sm_count(device); }
 
 static int norm_bn(int bn) { return (bn == 64 || bn == 128 || bn == 256) ? bn : 256; }
 
-extern "C" int64_t catcoc_stage_bytes(int M, int N, int W, int seg_dim, int bn, int partial_fmt) {
-  TileSched s = make_sched(M, N, kBM, norm_bn(bn), W, seg_dim, 0, 1);
+static int norm_bm(int cta_pair) { return cta_pair == 2 ? 2 * kBM : kBM; }
+
+extern "C" int64_t catcoc_stage_bytes(int M, int N, int W, int seg_dim, int bn, int cta_pair, int partial_fmt) {
+  TileSched s = make_sched(M, N, norm_bm(cta_pair), norm_bn(bn), W, seg_dim, 0, 1);
   return stage_total_bytes(s, fmt_bytes(partial_fmt));
 }
-extern "C" int64_t catcoc_arrive_words(int M, int N, int W, int seg_dim, int bn) {
-  TileSched s = make_sched(M, N, kBM, norm_bn(bn), W, seg_dim, 0, 1);
-  return static_cast<int64_t>(s.tiles_per_seg) * s.W * 4;
+extern "C" int64_t catcoc_arrive_words(int M, int N, int W, int seg_dim, int bn, int cta_pair) {
+  TileSched s = make_sched(M, N, norm_bm(cta_pair), norm_bn(bn), W, seg_dim, 0, 1);
+  return static_cast<int64_t>(s.tiles_per_seg) * s.W * (s.BM / 32);
 }
-extern "C" int64_t catcoc_done_words(int M, int N, int W, int seg_dim, int bn) {
-  TileSched s = make_sched(M, N, kBM, norm_bn(bn), W, seg_dim, 0, 1);
-  return static_cast<int64_t>(s.total_tiles) * 4;
+extern "C" int64_t catcoc_done_words(int M, int N, int W, int seg_dim, int bn, int cta_pair) {
+  TileSched s = make_sched(M, N, norm_bm(cta_pair), norm_bn(bn), W, seg_dim, 0, 1);
+  return static_cast<int64_t>(s.total_tiles) * (s.BM / 32);
 }
 extern "C" int64_t catcoc_gather_flag_words(int m, int K, int W, int elt_bytes) {
   GatherPlan g = make_gather_plan(m, K, kBM, 512 / elt_bytes);
@@ -176,8 +178,10 @@ extern "C" int catcoc_sched_get_tile(int M, int N, int bm, int bn, int W, int se
   return CATCOC_OK;
 }
 
+int max_active_pairs(int kind);
+
 // Fills the parameter block; shared by the normal and the allocation-free entry points.
-int catcoc_build_params(const CatcocOpArgs* args, FusedParams* p, int* kind_out, int* grid_out) {
+int catcoc_build_params(const CatcocOpArgs* args, FusedParams* p, int* kind_out, int* grid_out, int* pair_out) {
   if (args == nullptr) { set_error("null args"); return CATCOC_E_BAD_ARG; }
   const CatcocOpArgs& a = *args;
   if (a.M <= 0 || a.N <= 0 || a.K <= 0) {
@@ -198,9 +202,12 @@ int catcoc_build_params(const CatcocOpArgs* args, FusedParams* p, int* kind_out,
   if (rc != 0) return rc;
   const int bn = norm_bn(a.tiling.bn);
   const int seg_dim = pick_seg_dim(a);
+  const bool pair = (a.tiling.cta_pair == 2);
+  const int bm = pair ? 2 * kBM : kBM;
+  if (pair && bn < 128) { set_error("cta_pair=2 needs bn >= 128"); return CATCOC_E_UNSUPPORTED; }
 
   memset(p, 0, sizeof(*p));
-  p->sched = build_sched(a, bn, seg_dim);
+  p->sched = build_sched(a, bm, bn, seg_dim);
   p->K = a.K;
   p->mode = a.mode;
   p->rank = fused ? a.rank : 0;
@@ -209,7 +216,7 @@ int catcoc_build_params(const CatcocOpArgs* args, FusedParams* p, int* kind_out,
   p->umma_k = rf.umma_k;
   p->a_mn_major = a.trans_a ? 1 : 0;     // stored [K, M]: M contiguous
   p->b_mn_major = a.trans_b ? 0 : 1;     // stored [K, N]: N contiguous
-  p->idesc = ptx::make_instr_desc(rf.c_fmt, rf.a_fmt, rf.a_fmt, p->a_mn_major, p->b_mn_major, kBM, bn);
+  p->idesc = ptx::make_instr_desc(rf.c_fmt, rf.a_fmt, rf.a_fmt, p->a_mn_major, p->b_mn_major, bm, bn);
   p->elt_bytes_a = rf.elt;
 
   if (fused && (a.mode == CATCOC_MODE_RS) && (a.M % a.W != 0)) {
@@ -234,7 +241,7 @@ int catcoc_build_params(const CatcocOpArgs* args, FusedParams* p, int* kind_out,
     }
   }
   const int per128 = 128 / rf.elt;
-  if (!a.trans_b && bn < per128) {
+  if (!a.trans_b && (pair ? bn / 2 : bn) < per128) {
     set_error("8-bit operands stored [K, N] need bn >= 128 (one 128-byte run of N per TMA box)");
     return CATCOC_E_UNSUPPORTED;
   }
@@ -260,7 +267,7 @@ int catcoc_build_params(const CatcocOpArgs* args, FusedParams* p, int* kind_out,
     if ((p->a_local_pitch & 15) != 0) { set_error("allgather: A pitch must be a multiple of 16 bytes"); return CATCOC_E_ALIGNMENT; }
     p->gathered_parity_bytes = a.gathered_parity_bytes;
     p->gathered_pitch = gpitch;
-    p->gp = make_gather_plan(a.ag_m, ag_ld, kBM, 512 / rf.elt);
+    p->gp = make_gather_plan(a.ag_m, ag_ld, bm, 512 / rf.elt);
     for (int r = 0; r < a.W; ++r) {
       p->gathered[r] = static_cast<uint8_t*>(a.gathered[r]);
       p->gflags[r] = a.gflags[r];
@@ -274,7 +281,7 @@ int catcoc_build_params(const CatcocOpArgs* args, FusedParams* p, int* kind_out,
     if (rc != 0) return rc;
   }
   if (a.trans_b) {
-    rc = encode_2d(&p->tm_b, a.b, rf.elt, rf.dt, a.N, a.K, a.ldb, rf.bk, bn);
+    rc = encode_2d(&p->tm_b, a.b, rf.elt, rf.dt, a.N, a.K, a.ldb, rf.bk, pair ? bn / 2 : bn);
   } else {
     rc = encode_2d(&p->tm_b, a.b, rf.elt, rf.dt, a.K, a.N, a.ldb, per128, rf.bk);
   }
@@ -325,43 +332,125 @@ int catcoc_build_params(const CatcocOpArgs* args, FusedParams* p, int* kind_out,
 
   int device = 0;
   cudaGetDevice(&device);
-  int grid = a.tiling.num_ctas > 0 ? a.tiling.num_ctas : sm_count(device);
-  grid = imin(grid, sm_count(device));
+  const int sms = sm_count(device);
+  int grid = a.tiling.num_ctas > 0 ? a.tiling.num_ctas : sms;
+  grid = imin(grid, sms);
+  const int per_tile = pair ? 2 : 1;
   // All-gather needs every CTA's communication warps; otherwise never launch idle CTAs.
-  if (!(fused && a.mode == CATCOC_MODE_AG)) grid = imin(grid, p->sched.total_tiles);
+  if (!(fused && a.mode == CATCOC_MODE_AG)) grid = imin(grid, p->sched.total_tiles * per_tile);
+  if (pair) {
+    grid = imin(grid, 2 * max_active_pairs(rf.kind));
+    grid &= ~1;
+    if (grid < 2) grid = 2;
+  }
   if (grid < 1) grid = 1;
   *grid_out = grid;
   *kind_out = rf.kind;
+  *pair_out = pair ? 1 : 0;
   return CATCOC_OK;
 }
 
-int catcoc_launch_params(const FusedParams& p, int kind, int grid, cudaStream_t stream) {
+template <int KIND, bool CTA2>
+static cudaError_t set_smem_attr() {
+  return cudaFuncSetAttribute(fused_gemm_kernel<KIND, CTA2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                              Geo<CTA2>::kSmemBytes);
+}
+
+static cudaError_t prepare_kernels() {
   static std::once_flag once;
-  static cudaError_t attr_err = cudaSuccess;
+  static cudaError_t err = cudaSuccess;
   std::call_once(once, [] {
     cudaError_t e;
-    e = cudaFuncSetAttribute(fused_gemm_kernel<KIND_F16>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
-    if (e != cudaSuccess) attr_err = e;
-    e = cudaFuncSetAttribute(fused_gemm_kernel<KIND_I8>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
-    if (e != cudaSuccess) attr_err = e;
-    e = cudaFuncSetAttribute(fused_gemm_kernel<KIND_F8>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
-    if (e != cudaSuccess) attr_err = e;
+    if ((e = set_smem_attr<KIND_F16, false>()) != cudaSuccess) err = e;
+    if ((e = set_smem_attr<KIND_I8, false>()) != cudaSuccess) err = e;
+    if ((e = set_smem_attr<KIND_F8, false>()) != cudaSuccess) err = e;
+    if ((e = set_smem_attr<KIND_F16, true>()) != cudaSuccess) err = e;
+    if ((e = set_smem_attr<KIND_I8, true>()) != cudaSuccess) err = e;
+    if ((e = set_smem_attr<KIND_F8, true>()) != cudaSuccess) err = e;
   });
-  if (attr_err != cudaSuccess) {
-    set_error("cudaFuncSetAttribute failed: %s", cudaGetErrorString(attr_err));
-    return -1000 - static_cast<int>(attr_err);
+  return err;
+}
+
+template <int KIND>
+static int query_pairs() {
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3(2, 1, 1);
+  cfg.blockDim = dim3(kThreads, 1, 1);
+  cfg.dynamicSmemBytes = Geo<true>::kSmemBytes;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  int n = 0;
+  if (cudaOccupancyMaxActiveClusters(&n, fused_gemm_kernel<KIND, true>, &cfg) != cudaSuccess || n <= 0) {
+    cudaGetLastError();
+    n = 0;
   }
-  if (kind == KIND_F16) fused_gemm_kernel<KIND_F16><<<grid, kThreads, kSmemBytes, stream>>>(p);
-  else if (kind == KIND_I8) fused_gemm_kernel<KIND_I8><<<grid, kThreads, kSmemBytes, stream>>>(p);
-  else fused_gemm_kernel<KIND_F8><<<grid, kThreads, kSmemBytes, stream>>>(p);
-  CATCOC_CUDA_OK(cudaGetLastError());
+  return n;
+}
+
+// How many 2-CTA clusters of the pair kernel can be resident at once (the persistent grid must
+// not exceed it: CTAs of different ranks wait on each other).
+int max_active_pairs(int kind) {
+  static int cached[3] = {-1, -1, -1};
+  if (kind < 0 || kind > 2) return 1;
+  if (cached[kind] < 0) {
+    if (prepare_kernels() != cudaSuccess) return 1;
+    int n = kind == KIND_F16 ? query_pairs<KIND_F16>() : kind == KIND_I8 ? query_pairs<KIND_I8>() : query_pairs<KIND_F8>();
+    int device = 0;
+    cudaGetDevice(&device);
+    if (n <= 0) n = sm_count(device) / 2;
+    cached[kind] = n;
+  }
+  return cached[kind];
+}
+
+template <int KIND, bool CTA2>
+static cudaError_t launch_one(const FusedParams& p, int grid, cudaStream_t stream) {
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3(grid, 1, 1);
+  cfg.blockDim = dim3(kThreads, 1, 1);
+  cfg.dynamicSmemBytes = Geo<CTA2>::kSmemBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  if (CTA2) {
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+  }
+  return cudaLaunchKernelEx(&cfg, fused_gemm_kernel<KIND, CTA2>, p);
+}
+
+int catcoc_launch_params(const FusedParams& p, int kind, int grid, int pair, cudaStream_t stream) {
+  cudaError_t e = prepare_kernels();
+  if (e != cudaSuccess) {
+    set_error("cudaFuncSetAttribute failed: %s", cudaGetErrorString(e));
+    return -1000 - static_cast<int>(e);
+  }
+  if (pair) {
+    e = kind == KIND_F16 ? launch_one<KIND_F16, true>(p, grid, stream)
+        : kind == KIND_I8 ? launch_one<KIND_I8, true>(p, grid, stream)
+                          : launch_one<KIND_F8, true>(p, grid, stream);
+  } else {
+    e = kind == KIND_F16 ? launch_one<KIND_F16, false>(p, grid, stream)
+        : kind == KIND_I8 ? launch_one<KIND_I8, false>(p, grid, stream)
+                          : launch_one<KIND_F8, false>(p, grid, stream);
+  }
+  if (e != cudaSuccess) {
+    set_error("kernel launch failed: %s", cudaGetErrorString(e));
+    return -1000 - static_cast<int>(e);
+  }
   return CATCOC_OK;
 }
 
 extern "C" int catcoc_fused_launch(const CatcocOpArgs* args, void* stream) {
   FusedParams p;
-  int kind = 0, grid = 0;
-  int rc = catcoc_build_params(args, &p, &kind, &grid);
+  int kind = 0, grid = 0, pair = 0;
+  int rc = catcoc_build_params(args, &p, &kind, &grid, &pair);
   if (rc != 0) return rc;
-  return catcoc_launch_params(p, kind, grid, static_cast<cudaStream_t>(stream));
+  return catcoc_launch_params(p, kind, grid, pair, static_cast<cudaStream_t>(stream));
 }

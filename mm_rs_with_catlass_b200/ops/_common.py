@@ -114,6 +114,7 @@ def fill_tiling(args: N.OpArgs, tiling: Optional[TilingConfig]) -> None:
     args.tiling.num_ctas = t.num_ctas
     args.tiling.seg_dim = t.seg_dim
     args.tiling.use_multicast = 1 if t.use_multicast else 0
+    args.tiling.cta_pair = t.cta_pair
 
 
 def default_timeout_ns() -> int:

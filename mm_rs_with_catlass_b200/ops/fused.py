@@ -97,8 +97,8 @@ def _base_args(ctx: ShmemContext, mode: int, a: torch.Tensor, trans_a: bool, b: 
 def _attach_stage(ctx: ShmemContext, args, m: int, n: int, seg_dim: int, t: TilingConfig, partial_fmt: int) -> None:
     lib = N.lib()
     bn = t.effective_bn
-    stage = _grow(ctx, "stage", int(lib.catcoc_stage_bytes(m, n, ctx.world, seg_dim, bn, partial_fmt)))
-    arrive = _grow(ctx, "arrive", 4 * int(lib.catcoc_arrive_words(m, n, ctx.world, seg_dim, bn)))
+    stage = _grow(ctx, "stage", int(lib.catcoc_stage_bytes(m, n, ctx.world, seg_dim, bn, t.cta_pair, partial_fmt)))
+    arrive = _grow(ctx, "arrive", 4 * int(lib.catcoc_arrive_words(m, n, ctx.world, seg_dim, bn, t.cta_pair)))
     args.partial_fmt = partial_fmt
     for p in range(ctx.world):
         args.stage[p] = stage.ptr(p)
@@ -187,7 +187,7 @@ def matmul_allreduce(a: torch.Tensor, b: torch.Tensor, *, trans_a: bool = False,
         args.tiling.seg_dim = seg_dim
         parity_bytes = (m * n * elt + 255) // 256 * 256
         obuf = _grow(ctx, "ar_out", 2 * parity_bytes)
-        done = _grow(ctx, "done", 4 * int(lib.catcoc_done_words(m, n, ctx.world, seg_dim, t.effective_bn)))
+        done = _grow(ctx, "done", 4 * int(lib.catcoc_done_words(m, n, ctx.world, seg_dim, t.effective_bn, t.cta_pair)))
         args.out, args.ldc, args.out_fmt = None, n, cm.out_fmt(a.dtype)
         args.ar_out_parity_bytes = parity_bytes
         for p in range(ctx.world):

@@ -13,6 +13,7 @@ constant, examples/dynamic_tiling/dynamic_tiling.cpp:219-227).
 from __future__ import annotations
 
 import math
+import os
 from typing import Optional
 
 import torch
@@ -35,7 +36,20 @@ def heuristic(op: str, m: int, n: int, k: int, world: int, dtype: torch.dtype) -
         bn = 128  # 8-bit [K, N] operands need a full 128-byte run of N per TMA box
     # column-group width: keep the concurrently running tiles roughly square in (rows, cols)
     swizzle = 8 if tiles_m >= 8 else max(1, min(16, _NUM_SMS // max(1, tiles_m)))
-    return TilingConfig(bn=bn, swizzle=swizzle)
+    # 2-CTA pairs halve the shared-memory traffic per FLOP; they pay off once every rank's
+    # row range splits into whole 256-row tiles and there is enough work to fill the pairs.
+    seg_rows = rows if (world <= 1 or op == "allgather_matmul" and False) else rows
+    if op in ("matmul_reduce_scatter", "quant_matmul_reduce_scatter", "matmul_allreduce", "allgather_matmul"):
+        seg_rows = rows // max(1, world) if world > 1 else rows
+    pair = 1
+    forced = os.environ.get("CATCOC_CTA_PAIR")
+    if forced in ("1", "2"):
+        pair = int(forced)
+    elif bn >= 128 and seg_rows >= 256 and seg_rows % 256 == 0 and (rows // 256) * math.ceil(n / bn) >= _NUM_SMS // 2:
+        pair = 2
+    if pair == 2 and bn < 128:
+        pair = 1
+    return TilingConfig(bn=bn, swizzle=swizzle, cta_pair=pair)
 
 
 def choose(op: str, m: int, n: int, k: int, world: int, dtype: torch.dtype,
