@@ -63,6 +63,7 @@ class OpArgs(C.Structure):
         ("epoch_ptr", C.c_void_p), ("cta_counter", C.c_void_p), ("status", C.c_void_p),
         ("timeout_ns", C.c_uint64),
         ("withhold_signals", C.c_int),
+        ("trace", C.c_void_p),
     ]
 
 

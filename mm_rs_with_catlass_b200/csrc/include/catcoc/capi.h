@@ -78,6 +78,7 @@ typedef struct CatcocOpArgs {
   uint32_t* epoch_ptr; uint32_t* cta_counter; uint32_t* status;
   uint64_t timeout_ns;
   int withhold_signals;
+  unsigned long long* trace;               /* optional 16 x u64 cycle counters (see params.h), or NULL */
 } CatcocOpArgs;
 
 const char* catcoc_last_error(void);

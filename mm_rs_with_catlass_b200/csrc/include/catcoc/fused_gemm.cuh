@@ -77,6 +77,16 @@ CATCOC_DEVICE void report_status(const FusedParams& p, uint32_t code, uint32_t w
   }
 }
 
+// Cycle accounting for the optional trace counters.
+struct Tick {
+  long long t;
+  bool on;
+  CATCOC_DEVICE explicit Tick(bool enabled) : t(enabled ? ptx::clock_cycles() : 0), on(enabled) {}
+  CATCOC_DEVICE void lap(unsigned long long& acc) {
+    if (on) { const long long n = ptx::clock_cycles(); acc += static_cast<unsigned long long>(n - t); t = n; }
+  }
+};
+
 // Polls a stamp until it reaches `epoch` (wrap-safe), the time budget ends or the CTA aborts.
 CATCOC_DEVICE bool wait_stamp(const uint32_t* flag, uint32_t epoch, uint64_t timeout_ns,
                               volatile uint32_t* abort_flag, uint32_t* seen) {
@@ -229,6 +239,7 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
   if (CTA2) ptx::cluster_sync_all();   // the peer's barriers exist before anyone signals them
   ptx::tcgen05_fence_after();
   const uint32_t tmem_base = tail->tmem_base;
+  const long long cta_t0 = (p.trace != nullptr) ? ptx::clock_cycles() : 0;
 
   // Epoch of this launch: completed launches + 1. Read before any CTA can finish.
   uint32_t epoch = 1;
@@ -241,6 +252,9 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
     uint32_t phase = 0;
     uint32_t issued_mask = 0, issued_parity = 0;
     bool ok = true;
+    const bool tr = (p.trace != nullptr) && lane == 0;
+    unsigned long long c_wait = 0, c_issue = 0;
+    Tick tick(tr);
     for (int t = worker; ok && t < sched.total_tiles; t += num_workers) {
       const TileInfo ti = get_tile(sched, t);
       const CUtensorMap* tma = &p.tm_a;
@@ -269,7 +283,10 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
         }
       }
       for (int kb = 0; kb < num_kb; ++kb) {
-        if (!ptx::mbar_wait(&tail->empty[stage], phase ^ 1u, p.timeout_ns, abort_flag)) {
+        tick.lap(c_issue);
+        const bool got = ptx::mbar_wait(&tail->empty[stage], phase ^ 1u, p.timeout_ns, abort_flag);
+        tick.lap(c_wait);
+        if (!got) {
           if (lane == 0) {
             report_status(p, STATUS_TIMEOUT_PIPELINE, 0u, static_cast<uint32_t>(t),
                           static_cast<uint32_t>(kb), 0u);
@@ -278,7 +295,7 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
           ok = false;
           break;
         }
-        if (lane == 0) {
+        if (ptx::elect_one()) {
           uint8_t* sa = smem + stage * kStageBytes;
           uint8_t* sb = sa + kABytes;
           const int k0 = kb * p.bk;
@@ -287,6 +304,8 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
             ptx::mbar_expect_tx(&tail->full[stage], kABytes + b_stage_bytes);
             if (!p.a_mn_major) {
               ptx::tma_load_2d(sa, tma, &tail->full[stage], k0, a_row);
+            } else if (p.a_3d) {
+              ptx::tma_load_3d(sa, tma, &tail->full[stage], 0, k0, a_row / per_box);
             } else {
               // storage [K, M]: boxes of 128 B along M x bk rows of K
               for (int j = 0; j < kBM / per_box; ++j)
@@ -295,6 +314,8 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
             }
             if (!p.b_mn_major) {
               ptx::tma_load_2d(sb, &p.tm_b, &tail->full[stage], k0, b_col);
+            } else if (p.b_3d) {
+              ptx::tma_load_3d(sb, &p.tm_b, &tail->full[stage], 0, k0, b_col / per_box);
             } else {
               for (int j = 0; j < b_cols_cta / per_box; ++j)
                 ptx::tma_load_2d(sb + j * (p.bk * 128), &p.tm_b, &tail->full[stage],
@@ -307,25 +328,30 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
             if (leader) ptx::mbar_expect_tx(&tail->full[stage], 2u * (kABytes + b_stage_bytes));
             if (!p.a_mn_major) {
               ptx::tma_load_2d_pair(sa, tma, bar, k0, a_row);
+            } else if (p.a_3d) {
+              ptx::tma_load_3d_pair(sa, tma, bar, 0, k0, a_row / per_box);
             } else {
               for (int j = 0; j < kBM / per_box; ++j)
                 ptx::tma_load_2d_pair(sa + j * (p.bk * 128), tma, bar, a_row + j * per_box, k0);
             }
             if (!p.b_mn_major) {
               ptx::tma_load_2d_pair(sb, &p.tm_b, bar, k0, b_col);
+            } else if (p.b_3d) {
+              ptx::tma_load_3d_pair(sb, &p.tm_b, bar, 0, k0, b_col / per_box);
             } else {
               for (int j = 0; j < b_cols_cta / per_box; ++j)
                 ptx::tma_load_2d_pair(sb + j * (p.bk * 128), &p.tm_b, bar, b_col + j * per_box,
                                       k0);
             }
           }
-          issued_mask |= 1u << stage;
-          issued_parity = (issued_parity & ~(1u << stage)) | (phase << stage);
         }
         __syncwarp();
+        issued_mask |= 1u << stage;
+        issued_parity = (issued_parity & ~(1u << stage)) | (phase << stage);
         if (++stage == kStages) { stage = 0; phase ^= 1u; }
       }
     }
+    if (tr) { atomicAdd(p.trace + 0, c_wait); atomicAdd(p.trace + 1, c_issue); }
     if (*abort_flag && lane == 0 && leader) {
       // let every bulk copy this thread started land before the CTA's smem goes away
       volatile uint32_t never = 0;
@@ -335,7 +361,9 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
     }
   } else if (warp == 1) {
     // =============================== MMA issuer ===============================
-    if (lane == 0 && leader) {
+    // The whole warp walks the loop converged (so addresses and descriptors stay warp-uniform
+    // and cheap); one elected lane issues the tcgen05 instructions.
+    if (leader) {
       int stage = 0;
       uint32_t phase = 0;
       int acc = 0;
@@ -343,58 +371,87 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
       bool ok = true;
       const uint32_t a_lbo = p.a_mn_major ? static_cast<uint32_t>(p.bk) * 128u : 16u;
       const uint32_t b_lbo = p.b_mn_major ? static_cast<uint32_t>(p.bk) * 128u : 16u;
-      const uint32_t a_kstep = p.a_mn_major ? static_cast<uint32_t>(p.umma_k) * 128u : 32u;
-      const uint32_t b_kstep = p.b_mn_major ? static_cast<uint32_t>(p.umma_k) * 128u : 32u;
-      const int k_per_stage = p.bk / p.umma_k;
+      // descriptor low-word increment per MMA along K (units of 16 bytes)
+      const uint32_t a_kinc = (p.a_mn_major ? static_cast<uint32_t>(p.umma_k) * 128u : 32u) >> 4;
+      const uint32_t b_kinc = (p.b_mn_major ? static_cast<uint32_t>(p.umma_k) * 128u : 32u) >> 4;
+      const uint32_t stage_inc = static_cast<uint32_t>(kStageBytes) >> 4;
+      const uint64_t da0 = ptx::make_smem_desc_sw128(ptx::smem_u32(smem), a_lbo, 1024u);
+      const uint64_t db0 = ptx::make_smem_desc_sw128(ptx::smem_u32(smem) + kABytes, b_lbo, 1024u);
+      const uint32_t idesc = p.idesc;
+      const int k_per_stage = p.bk / p.umma_k;   // 4
+      const int umma_k = p.umma_k;
+      const int bk = p.bk;
+      const int K = p.K;
+      const bool tr = (p.trace != nullptr) && lane == 0;
+      unsigned long long c_full = 0, c_acc = 0, c_issue = 0;
+      Tick tick(tr);
       for (int t = worker; ok && t < sched.total_tiles; t += num_workers) {
-        if (!ptx::mbar_wait(&tail->acc_empty[acc], acc_phase ^ 1u, p.timeout_ns, abort_flag)) {
-          report_status(p, STATUS_TIMEOUT_PIPELINE, 1u, static_cast<uint32_t>(t), 0u, 0u);
-          *abort_flag = 1;
+        tick.lap(c_issue);
+        const bool got_acc = ptx::mbar_wait(&tail->acc_empty[acc], acc_phase ^ 1u, p.timeout_ns, abort_flag);
+        tick.lap(c_acc);
+        if (!got_acc) {
+          if (lane == 0) {
+            report_status(p, STATUS_TIMEOUT_PIPELINE, 1u, static_cast<uint32_t>(t), 0u, 0u);
+            *abort_flag = 1;
+          }
           break;
         }
         ptx::tcgen05_fence_after();
         const uint32_t tmem_d = tmem_base + static_cast<uint32_t>(acc * kMaxBN);
         for (int kb = 0; kb < num_kb; ++kb) {
-          if (!ptx::mbar_wait(&tail->full[stage], phase, p.timeout_ns, abort_flag)) {
-            report_status(p, STATUS_TIMEOUT_PIPELINE, 2u, static_cast<uint32_t>(t),
-                          static_cast<uint32_t>(kb), 0u);
-            *abort_flag = 1;
+          tick.lap(c_issue);
+          const bool got_full = ptx::mbar_wait(&tail->full[stage], phase, p.timeout_ns, abort_flag);
+          tick.lap(c_full);
+          if (!got_full) {
+            if (lane == 0) {
+              report_status(p, STATUS_TIMEOUT_PIPELINE, 2u, static_cast<uint32_t>(t),
+                            static_cast<uint32_t>(kb), 0u);
+              *abort_flag = 1;
+            }
             ok = false;
             break;
           }
           ptx::tcgen05_fence_after();
-          const uint32_t sa = ptx::smem_u32(smem + stage * kStageBytes);
-          const uint32_t sb = sa + kABytes;
-          // K tail: the last stage may hold fewer than bk valid K elements; TMA zero-fills the
-          // rest, so the extra MMAs add zeros and are simply skipped when entirely out of range.
-          const int k_left = p.K - kb * p.bk;
-          const int nk = min(k_per_stage, ceil_div(k_left, p.umma_k));
-          for (int k = 0; k < nk; ++k) {
-            const uint64_t da = ptx::make_smem_desc_sw128(sa + k * a_kstep, a_lbo, 1024u);
-            const uint64_t db = ptx::make_smem_desc_sw128(sb + k * b_kstep, b_lbo, 1024u);
-            const uint32_t accum = (kb | k) != 0 ? 1u : 0u;
-            if (CTA2) {
-              if (KIND == KIND_F16) ptx::umma_f16_pair(tmem_d, da, db, p.idesc, accum);
-              else if (KIND == KIND_I8) ptx::umma_i8_pair(tmem_d, da, db, p.idesc, accum);
-              else ptx::umma_f8f6f4_pair(tmem_d, da, db, p.idesc, accum);
-            } else {
-              if (KIND == KIND_F16) ptx::umma_f16(tmem_d, da, db, p.idesc, accum);
-              else if (KIND == KIND_I8) ptx::umma_i8(tmem_d, da, db, p.idesc, accum);
-              else ptx::umma_f8f6f4(tmem_d, da, db, p.idesc, accum);
+          // K tail: TMA zero-fills beyond K, MMAs entirely out of range are skipped.
+          const int nk = min(k_per_stage, ceil_div(K - kb * bk, umma_k));
+          const uint64_t da = da0 + static_cast<uint64_t>(stage * stage_inc);
+          const uint64_t db = db0 + static_cast<uint64_t>(stage * stage_inc);
+          if (ptx::elect_one()) {
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              if (k < nk) {
+                const uint64_t dak = da + static_cast<uint64_t>(k * a_kinc);
+                const uint64_t dbk = db + static_cast<uint64_t>(k * b_kinc);
+                const uint32_t accum = (kb | k) != 0 ? 1u : 0u;
+                if (CTA2) {
+                  if (KIND == KIND_F16) ptx::umma_f16_pair(tmem_d, dak, dbk, idesc, accum);
+                  else if (KIND == KIND_I8) ptx::umma_i8_pair(tmem_d, dak, dbk, idesc, accum);
+                  else ptx::umma_f8f6f4_pair(tmem_d, dak, dbk, idesc, accum);
+                } else {
+                  if (KIND == KIND_F16) ptx::umma_f16(tmem_d, dak, dbk, idesc, accum);
+                  else if (KIND == KIND_I8) ptx::umma_i8(tmem_d, dak, dbk, idesc, accum);
+                  else ptx::umma_f8f6f4(tmem_d, dak, dbk, idesc, accum);
+                }
+              }
+            }
+            // frees this smem stage (in both CTAs of a pair) once the MMAs above retire
+            if (CTA2) ptx::tcgen05_commit_pair(&tail->empty[stage], 3);
+            else ptx::tcgen05_commit(&tail->empty[stage]);
+            if (kb == num_kb - 1) {
+              if (CTA2) ptx::tcgen05_commit_pair(&tail->acc_full[acc], 3);
+              else ptx::tcgen05_commit(&tail->acc_full[acc]);
             }
           }
-          // frees this smem stage (in both CTAs of a pair) once the MMAs above retire
-          if (CTA2) ptx::tcgen05_commit_pair(&tail->empty[stage], 3);
-          else ptx::tcgen05_commit(&tail->empty[stage]);
+          __syncwarp();
           if (++stage == kStages) { stage = 0; phase ^= 1u; }
         }
         if (!ok) break;
-        if (CTA2) ptx::tcgen05_commit_pair(&tail->acc_full[acc], 3);
-        else ptx::tcgen05_commit(&tail->acc_full[acc]);
         acc ^= 1;
         if (acc == 0) acc_phase ^= 1u;
       }
-      if (*abort_flag) {
+      tick.lap(c_issue);
+      if (tr) { atomicAdd(p.trace + 2, c_full); atomicAdd(p.trace + 3, c_acc); atomicAdd(p.trace + 4, c_issue); }
+      if (*abort_flag && lane == 0) {
         // wait (bounded) for the tensor core to retire what was issued before TMEM is freed
         volatile uint32_t never = 0;
         if (CTA2) ptx::tcgen05_commit_pair(&tail->acc_full[acc], 3);
@@ -419,6 +476,9 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
     int acc = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
+    const bool tr = (p.trace != nullptr) && lane == 0 && q == 0;
+    unsigned long long c_full = 0, c_work = 0, c_peer = 0;
+    Tick tick(tr);
 
     for (int t = worker; ok && t < sched.total_tiles; t += num_workers) {
       const TileInfo ti = get_tile(sched, t);
@@ -428,6 +488,7 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
       const int st_elt = fmt_bytes(st_fmt);
       const int rows_valid = max(0, min(32, ti.rows - row_base));
 
+      tick.lap(c_work);
       if (reduce_here) {
         // the peers' rows [32q, 32q+32) of this tile must have landed in my staging slabs
         if (lane < p.W && lane != p.rank) {
@@ -444,7 +505,10 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
         if (!ok) break;
       }
 
-      if (!ptx::mbar_wait(&tail->acc_full[acc], acc_phase, p.timeout_ns, abort_flag)) {
+      tick.lap(c_peer);
+      const bool got_tile = ptx::mbar_wait(&tail->acc_full[acc], acc_phase, p.timeout_ns, abort_flag);
+      tick.lap(c_full);
+      if (!got_tile) {
         if (lane == 0) {
           report_status(p, STATUS_TIMEOUT_PIPELINE, 3u, static_cast<uint32_t>(t), 0u, 0u);
           *abort_flag = 1;
@@ -649,6 +713,9 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
       if (acc == 0) acc_phase ^= 1u;
     }
 
+    tick.lap(c_work);
+    if (tr) { atomicAdd(p.trace + 5, c_full); atomicAdd(p.trace + 6, c_work); atomicAdd(p.trace + 7, c_peer); }
+
     // all-reduce tail: this rank's output is complete only when every owner's tiles landed
     if (fused && p.mode == MODE_AR && ok && !*abort_flag) {
       const int et = (warp - 2) * 32 + lane;
@@ -721,6 +788,8 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
     if (CTA2) ptx::tmem_dealloc_pair(tmem_base, kTmemCols);
     else ptx::tmem_dealloc(tmem_base, kTmemCols);
   }
+  if (p.trace != nullptr && threadIdx.x == 0)
+    atomicAdd(p.trace + 8, static_cast<unsigned long long>(ptx::clock_cycles() - cta_t0));
   if (fused && threadIdx.x == 0) {
     // the last CTA to finish publishes the new epoch for the next launch on this stream
     __threadfence();

@@ -56,6 +56,7 @@ struct alignas(64) FusedParams {
   // operand staging: K elements per pipeline stage and per MMA instruction; smem majors
   int bk, umma_k;
   int a_mn_major, b_mn_major;
+  int a_3d, b_3d;   // M/N-contiguous operand fetched through a 3-D map {128 B, K, blocks}: one TMA per stage
   uint32_t idesc;
 
   // output (MODE_LOCAL / MODE_AG / RS own tiles): row-major [rows, ldc]
@@ -97,6 +98,11 @@ struct alignas(64) FusedParams {
   uint32_t* status;          // kStatusWords words, host-visible
   uint64_t timeout_ns;
   int withhold_signals;      // test hook: this rank posts no arrival / done / chunk stamps
+  // Optional per-launch cycle counters (summed over CTAs), null = off:
+  // [0] producer waits on empty   [1] producer issue     [2] MMA waits on full
+  // [3] MMA waits on acc_empty    [4] MMA issue          [5] epilogue waits on acc_full
+  // [6] epilogue work             [7] epilogue waits on peers' stamps   [8] CTA lifetime
+  unsigned long long* trace;
 };
 
 }  // namespace catcoc

@@ -23,6 +23,12 @@ CATCOC_DEVICE uint64_t globaltimer_ns() {
   return t;
 }
 
+CATCOC_DEVICE long long clock_cycles() {
+  long long t;
+  asm volatile("mov.u64 %0, %%clock64;" : "=l"(t));
+  return t;
+}
+
 CATCOC_DEVICE bool elect_one() {
   uint32_t pred = 0;
   asm volatile(
@@ -111,6 +117,17 @@ CATCOC_DEVICE void tma_load_2d(void* smem_dst, const void* tmap, uint64_t* bar, 
       " [%0], [%1, {%3, %4}], [%2];"
       ::"r"(smem_u32(smem_dst)),
       "l"(reinterpret_cast<uint64_t>(tmap)), "r"(smem_u32(bar)), "r"(x), "r"(y)
+      : "memory");
+}
+
+// 3-D form: used to fetch an M/N-contiguous operand tile (several 128-byte-wide column blocks
+// x bk rows) with one instruction; x must again be a multiple of 16 bytes.
+CATCOC_DEVICE void tma_load_3d(void* smem_dst, const void* tmap, uint64_t* bar, int x, int y, int z) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(smem_u32(smem_dst)),
+      "l"(reinterpret_cast<uint64_t>(tmap)), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z)
       : "memory");
 }
 
@@ -259,6 +276,15 @@ CATCOC_DEVICE void tma_load_2d_pair(void* smem_dst, const void* tmap, uint32_t b
       " [%0], [%1, {%3, %4}], [%2];"
       ::"r"(smem_u32(smem_dst)),
       "l"(reinterpret_cast<uint64_t>(tmap)), "r"(bar_cluster_addr), "r"(x), "r"(y)
+      : "memory");
+}
+CATCOC_DEVICE void tma_load_3d_pair(void* smem_dst, const void* tmap, uint32_t bar_cluster_addr,
+                                    int x, int y, int z) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(smem_u32(smem_dst)),
+      "l"(reinterpret_cast<uint64_t>(tmap)), "r"(bar_cluster_addr), "r"(x), "r"(y), "r"(z)
       : "memory");
 }
 CATCOC_DEVICE void tmem_alloc_pair(uint32_t* smem_result, uint32_t ncols) {

@@ -90,6 +90,35 @@ static int sm_count(int device) {
   return cached[device];
 }
 
+// An M/N-contiguous matrix stored [K, MN] viewed as {128 B of MN, K, MN / (128 B)}: a box of
+// `nblk` column blocks x `box_rows` rows lands in shared memory block by block, which is
+// exactly the layout the MN-major UMMA descriptor walks. Needs MN to be a whole number of
+// 128-byte blocks (the ragged case uses one 2-D box per block instead).
+static int encode_3d_blocks(CUtensorMap* tm, const void* base, int elt_bytes, CUtensorMapDataType dt,
+                            int64_t k_rows, int64_t mn, int64_t ld, int box_rows, int nblk) {
+  static EncodeTiledFn fn = driver_fn<EncodeTiledFn>("cuTensorMapEncodeTiled");
+  if (fn == nullptr) return CATCOC_E_DRIVER;
+  const int per128 = 128 / elt_bytes;
+  if ((reinterpret_cast<uintptr_t>(base) & 15) != 0 || ((ld * elt_bytes) & 15) != 0 || (mn % per128) != 0) {
+    set_error("3-D TMA view needs aligned base/pitch and MN %% %d == 0", per128);
+    return CATCOC_E_ALIGNMENT;
+  }
+  cuuint64_t gdim[3] = {static_cast<cuuint64_t>(per128), static_cast<cuuint64_t>(k_rows),
+                        static_cast<cuuint64_t>(mn / per128)};
+  cuuint64_t gstride[2] = {static_cast<cuuint64_t>(ld) * elt_bytes, 128};
+  cuuint32_t box[3] = {static_cast<cuuint32_t>(per128), static_cast<cuuint32_t>(box_rows),
+                       static_cast<cuuint32_t>(nblk)};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(tm, dt, 3, const_cast<void*>(base), gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    set_error("cuTensorMapEncodeTiled (3-D) failed: CUresult %d", static_cast<int>(r));
+    return CATCOC_E_DRIVER;
+  }
+  return CATCOC_OK;
+}
+
 struct Resolved {
   int kind, elt, bk, umma_k, a_fmt, c_fmt;
   CUtensorMapDataType dt;
@@ -276,12 +305,19 @@ int catcoc_build_params(const CatcocOpArgs* args, FusedParams* p, int* kind_out,
   } else if (!a.trans_a) {
     rc = encode_2d(&p->tm_a, a.a, rf.elt, rf.dt, a.M, a.K, a.lda, rf.bk, kBM);
     if (rc != 0) return rc;
+  } else if (a.M % per128 == 0) {
+    rc = encode_3d_blocks(&p->tm_a, a.a, rf.elt, rf.dt, a.K, a.M, a.lda, rf.bk, kBM / per128);
+    if (rc != 0) return rc;
+    p->a_3d = 1;
   } else {
     rc = encode_2d(&p->tm_a, a.a, rf.elt, rf.dt, a.K, a.M, a.lda, per128, rf.bk);
     if (rc != 0) return rc;
   }
   if (a.trans_b) {
     rc = encode_2d(&p->tm_b, a.b, rf.elt, rf.dt, a.N, a.K, a.ldb, rf.bk, pair ? bn / 2 : bn);
+  } else if (a.N % per128 == 0) {
+    rc = encode_3d_blocks(&p->tm_b, a.b, rf.elt, rf.dt, a.K, a.N, a.ldb, rf.bk, (pair ? bn / 2 : bn) / per128);
+    p->b_3d = 1;
   } else {
     rc = encode_2d(&p->tm_b, a.b, rf.elt, rf.dt, a.K, a.N, a.ldb, per128, rf.bk);
   }
@@ -329,6 +365,7 @@ int catcoc_build_params(const CatcocOpArgs* args, FusedParams* p, int* kind_out,
   if (fused && (a.epoch_ptr == nullptr || a.cta_counter == nullptr)) { set_error("null epoch / counter"); return CATCOC_E_BAD_ARG; }
   p->timeout_ns = a.timeout_ns ? a.timeout_ns : 10000000000ull;
   p->withhold_signals = a.withhold_signals;
+  p->trace = a.trace;
 
   int device = 0;
   cudaGetDevice(&device);

@@ -21,7 +21,8 @@ from . import _common as cm
 def matmul(a: torch.Tensor, b: torch.Tensor, *, trans_a: bool = False, trans_b: bool = False,
            out: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None,
            scale_m: Optional[torch.Tensor] = None, scale_n: Optional[torch.Tensor] = None,
-           bias: Optional[torch.Tensor] = None, tiling: Optional[TilingConfig] = None) -> torch.Tensor:
+           bias: Optional[torch.Tensor] = None, tiling: Optional[TilingConfig] = None,
+           trace: Optional[torch.Tensor] = None) -> torch.Tensor:
     """``out = A @ B`` with fp32 (int32 for int8) accumulation.
 
     ``a`` is stored ``[M, K]`` (``[K, M]`` with ``trans_a``), ``b`` is stored ``[K, N]``
@@ -72,5 +73,7 @@ def matmul(a: torch.Tensor, b: torch.Tensor, *, trans_a: bool = False, trans_b: 
                     raise ValueError("%s must be a contiguous %s tensor of %d elements" % (name, dt, length))
                 setattr(args, name, t.data_ptr())
         args.status = cm.local_status(dev).data_ptr()
+        if trace is not None:  # int64[16] device tensor: per-role cycle counters (see params.h)
+            args.trace = trace.data_ptr()
         cm.launch(args, dev)
     return out
