@@ -4,8 +4,20 @@ A Blackwell-native library with the capabilities of the Ascend "CATCOC" template
 symmetric-heap SHMEM layer over NVLink / NVSwitch peer memory and four fused ops
 (matmul-allreduce, allgather-matmul, matmul-reduce-scatter, quantised matmul-reduce-scatter),
 each a single hand-written tcgen05 / TMA kernel that communicates from inside its tile loop.
+
+Typical use (one process per GPU, ``torch.distributed`` initialised):
+
+    import mm_rs_with_catlass_b200 as catcoc
+    ctx = catcoc.init()                                   # symmetric heap over the world group
+    y = catcoc.matmul_reduce_scatter(a, b)                # [M/W, N]
+    y, gathered = catcoc.allgather_matmul(a_shard, b)     # [W*m, N], [W*m, K]
+    ctx.finalize()
 """
 from . import _native  # noqa: F401
 from .tiling.config import TilingConfig  # noqa: F401
+from .parallel.shmem import init, default_context, ShmemContext, ShmemError  # noqa: F401
+from .ops.gemm import matmul  # noqa: F401
+from .ops.fused import (matmul_allreduce, allgather_matmul, matmul_reduce_scatter,  # noqa: F401
+                        quant_matmul_reduce_scatter)
 
 __version__ = "0.1.0"

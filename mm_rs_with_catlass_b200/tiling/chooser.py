@@ -47,6 +47,8 @@ def heuristic(op: str, m: int, n: int, k: int, world: int, dtype: torch.dtype) -
         pair = int(forced)
     elif bn >= 128 and seg_rows >= 256 and seg_rows % 256 == 0 and (rows // 256) * math.ceil(n / bn) >= _NUM_SMS // 2:
         pair = 2
+    if pair == 2 and dtype == torch.int8:
+        bn = 256  # each CTA of a pair loads bn / 2 columns, and 8-bit [K, N] needs 128 of them
     if pair == 2 and bn < 128:
         pair = 1
     return TilingConfig(bn=bn, swizzle=swizzle, cta_pair=pair)

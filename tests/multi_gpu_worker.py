@@ -1,0 +1,164 @@
+"""Worker of the multi-GPU tests; started by tests/test_fused_multi_gpu.py through
+``python -m torch.distributed.run``. Every rank uses different, seeded data. Prints one JSON
+line per case on rank 0 and exits non-zero if any rank saw a failure."""
+import json
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+REPO = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, REPO)
+
+import mm_rs_with_catlass_b200 as catcoc  # noqa: E402
+from mm_rs_with_catlass_b200.ops import reference as ref  # noqa: E402
+from mm_rs_with_catlass_b200.utils.data import matmul_inputs, quant_inputs  # noqa: E402
+from mm_rs_with_catlass_b200.utils.verify import verify  # noqa: E402
+
+rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
+torch.cuda.set_device(local)
+dev = torch.device("cuda", local)
+dist.init_process_group("nccl", device_id=dev)
+mode = sys.argv[1] if len(sys.argv) > 1 else "ops"
+failures = []
+
+
+def agree(ok: bool) -> bool:
+    t = torch.tensor([1 if ok else 0], device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MIN)
+    return bool(t.item())
+
+
+def report(name, ok, detail=""):
+    ok_all = agree(ok)
+    if not ok_all:
+        failures.append(name)
+    if rank == 0:
+        print(json.dumps({"case": name, "ok": ok_all, "detail": detail if not ok else ""}), flush=True)
+
+
+def check(name, out, gold, k, dtype):
+    r = verify(out, gold, k, dtype)
+    try:
+        ctx.check(name)
+        st = ""
+    except RuntimeError as e:
+        st = str(e)
+    report(name, r.ok and not st, "%s %s" % (r, st))
+
+
+TILINGS = [None, catcoc.TilingConfig(bn=128, cta_pair=1), catcoc.TilingConfig(bn=256, cta_pair=2, swizzle=4)]
+
+if mode == "ops":
+    ctx = catcoc.init(heap_bytes=2 << 30, multicast=(os.environ.get("CATCOC_TEST_NVLS", "1") == "1"))
+    W = world
+    for dtype in (torch.bfloat16, torch.float16):
+        for (M, N, K, ta, tb) in [(256 * W, 512, 384, False, False), (128 * W, 768, 256, False, True),
+                                  (256 * W, 512, 320, True, False), (2 * W * 23, 328, 136, False, False),
+                                  (W * 7, 72, 40, True, True)]:
+            for ti, tiling in enumerate(TILINGS):
+                a, b = matmul_inputs(M, N, K, rank, dtype, dev, trans_a=ta, trans_b=tb, seed=M + N)
+                gold_full = ref.matmul_allreduce(a, b, trans_a=ta, trans_b=tb, out_dtype=torch.float32)
+                rows = M // W
+                tag = "%s_%dx%dx%d_%d%d_t%d" % (str(dtype)[6:], M, N, K, ta, tb, ti)
+                o = catcoc.matmul_reduce_scatter(a, b, trans_a=ta, trans_b=tb, tiling=tiling)
+                check("rs_" + tag, o, gold_full[rank * rows:(rank + 1) * rows], K * W, dtype)
+                o = catcoc.matmul_allreduce(a, b, trans_a=ta, trans_b=tb, tiling=tiling)
+                check("ar_" + tag, o, gold_full, K * W, dtype)
+        # all-reduce with fewer rows than ranks * 128: ownership splits by columns
+        a, b = matmul_inputs(96, 1024, 256, rank, dtype, dev, seed=11)
+        gold = ref.matmul_allreduce(a, b, out_dtype=torch.float32)
+        check("ar_smallM_%s" % str(dtype)[6:], catcoc.matmul_allreduce(a, b), gold, 256 * W, dtype)
+        for seg in (0, 1):
+            check("ar_seg%d_%s" % (seg, str(dtype)[6:]),
+                  catcoc.matmul_allreduce(a, b, tiling=catcoc.TilingConfig(bn=64, seg_dim=seg)), gold, 256 * W, dtype)
+        if ctx.multicast:
+            a, b = matmul_inputs(256 * W, 512, 256, rank, dtype, dev, seed=12)
+            gold = ref.matmul_allreduce(a, b, out_dtype=torch.float32)
+            check("ar_nvls_%s" % str(dtype)[6:],
+                  catcoc.matmul_allreduce(a, b, tiling=catcoc.TilingConfig(use_multicast=True)), gold, 256 * W, dtype)
+        for (m, N, K, tb) in [(256, 512, 512, False), (384, 640, 1024, True), (100, 328, 136, False), (64, 256, 6148, False)]:
+            for ti, tiling in enumerate(TILINGS):
+                a, b = matmul_inputs(m, N, K, rank, dtype, dev, trans_b=tb, seed=m + K)
+                gold, gath = ref.allgather_matmul(a, b, trans_b=tb, out_dtype=torch.float32)
+                o, g = catcoc.allgather_matmul(a, b, trans_b=tb, tiling=tiling)
+                tag = "%s_%dx%dx%d_%d_t%d" % (str(dtype)[6:], m, N, K, tb, ti)
+                check("ag_" + tag, o, gold, K, dtype)
+                report("ag_gathered_" + tag, bool(torch.equal(g, gath)))
+    for (M, N, K, tb, with_bias) in [(128 * W, 512, 512, False, True), (256 * W, 768, 384, True, True),
+                                     (4 * W, 512, 128, False, False), (W * 23, 136, 72, True, True)]:
+        for out_dtype in (torch.bfloat16, torch.float16):
+            x1, x2, s1, s2, bias = quant_inputs(M, N, K, rank, dev, trans_b=tb, with_bias=with_bias, seed=K)
+            gold = ref.quant_matmul_reduce_scatter(x1, x2, s1, s2, bias, trans_b=tb, out_dtype=torch.float32)
+            o = catcoc.quant_matmul_reduce_scatter(x1, x2, s1, s2, bias, trans_b=tb, out_dtype=out_dtype)
+            check("qrs_%dx%dx%d_%d_%s" % (M, N, K, tb, str(out_dtype)[6:]), o, gold, 512, out_dtype)
+    # debug pattern (all-ones operands, arange bias) localises indexing errors
+    x1, x2, s1, s2, bias = quant_inputs(32 * W, 256, 128, rank, dev, debug=True)
+    o = catcoc.quant_matmul_reduce_scatter(x1, x2, s1, s2, bias, out_dtype=torch.float32)
+    exp = ((128.0 + torch.arange(1, 257, device=dev).float()) * W * 1e-4)[None, :].expand(32, 256)
+    report("qrs_debug_pattern", bool(torch.allclose(o, exp, rtol=1e-5)))
+    # many back-to-back launches of mixed ops on one context (epoch parity, stamp reuse)
+    a, b = matmul_inputs(128 * W, 256, 128, rank, torch.bfloat16, dev, seed=77)
+    gold = ref.matmul_allreduce(a, b, out_dtype=torch.float32)
+    rows = 128
+    ok = True
+    for it in range(60):
+        if it % 3 == 0:
+            o = catcoc.matmul_reduce_scatter(a, b)
+            ok &= verify(o, gold[rank * rows:(rank + 1) * rows], 128 * W, torch.bfloat16).ok
+        elif it % 3 == 1:
+            o = catcoc.matmul_allreduce(a, b).clone()
+            ok &= verify(o, gold, 128 * W, torch.bfloat16).ok
+        else:
+            o, _ = catcoc.allgather_matmul(a[:64], b[:128] if False else b)
+            ok &= bool(torch.isfinite(o.float()).all())
+    try:
+        ctx.check("repeat")
+    except RuntimeError as e:
+        ok = False
+        print("rank", rank, e, flush=True)
+    report("repeat_60_mixed_launches", ok)
+    # the flagship block
+    from mm_rs_with_catlass_b200.models.tp_mlp import TPMLP, TPMLPConfig
+    mlp = TPMLP(TPMLPConfig(hidden=512, ffn=256 * W), ctx, dev)
+    x = torch.randn(128, 512, device=dev).bfloat16()
+    check("tpmlp", mlp(x), mlp.reference_forward(x).float(), 256 * W, torch.bfloat16)
+    ctx.finalize()
+
+elif mode == "withhold":
+    # Failure detection without a GPU fault: the last rank posts no stamps, so its peers' waits
+    # run out of their (short) budget, return an error status and raise on the host. NVLS off.
+    from mm_rs_with_catlass_b200 import _native as N
+    from mm_rs_with_catlass_b200.ops import fused
+    os.environ["CATCOC_TIMEOUT_MS"] = "300"
+    ctx = catcoc.init(heap_bytes=256 << 20, multicast=False)
+    a, b = matmul_inputs(128 * world, 256, 128, rank, torch.bfloat16, dev)
+    orig = fused.cm.launch
+
+    def launch_withholding(args, device):
+        if rank == world - 1:
+            args.withhold_signals = 1
+        return orig(args, device)
+
+    fused.cm.launch = launch_withholding
+    catcoc.matmul_reduce_scatter(a, b)
+    torch.cuda.synchronize()
+    raised = False
+    try:
+        ctx.check("withheld signal")
+    except RuntimeError as e:
+        raised = "never arrived" in str(e)
+    fused.cm.launch = orig
+    expect_raise = rank != world - 1 or world == 1
+    # the withholding rank itself still receives everybody's tiles and finishes cleanly
+    report("withheld_signal_detected", raised == expect_raise)
+    ctx.reset_after_error()
+    gold = ref.matmul_reduce_scatter(a, b, out_dtype=torch.float32)
+    o = catcoc.matmul_reduce_scatter(a, b)
+    check("recovers_after_reset", o, gold, 128 * world, torch.bfloat16)
+    ctx.finalize()
+
+dist.barrier()
+dist.destroy_process_group()
+sys.exit(1 if failures else 0)

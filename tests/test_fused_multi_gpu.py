@@ -1,0 +1,60 @@
+"""Fused ops on 2 / 4 / 8 GPUs of one box: launches tests/multi_gpu_worker.py with one process
+per GPU and checks every case it reports. Skipped where fewer GPUs are visible."""
+import json
+import os
+import socket
+import subprocess
+import sys
+
+import pytest
+
+pytestmark = pytest.mark.gpu
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _run(world, mode, extra_env=None, timeout=900):
+    env = dict(os.environ)
+    env.setdefault("CATCOC_TIMEOUT_MS", "5000")
+    env.update(extra_env or {})
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", str(world),
+           "--master-addr", "127.0.0.1", "--master-port", str(_free_port()), os.path.join(HERE, "multi_gpu_worker.py"),
+           mode]
+    proc = subprocess.run(cmd, capture_output=True, text=True, timeout=timeout, env=env)
+    cases = []
+    for line in proc.stdout.splitlines():
+        if line.startswith("{"):
+            try:
+                cases.append(json.loads(line))
+            except ValueError:
+                pass
+    bad = [c for c in cases if not c["ok"]]
+    assert proc.returncode == 0 and not bad, "failed cases: %s\nstdout tail:\n%s\nstderr tail:\n%s" % (
+        bad[:10], proc.stdout[-2000:], proc.stderr[-3000:])
+    return cases
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_fused_ops_match_goldens(world, gpu_count):
+    if gpu_count < world:
+        pytest.skip("needs %d GPUs" % world)
+    cases = _run(world, "ops")
+    assert len(cases) > 100
+
+
+def test_fused_ops_on_plain_peer_stores_without_nvls(gpu_count):
+    if gpu_count < 2:
+        pytest.skip("needs 2 GPUs")
+    _run(2, "ops", {"CATCOC_TEST_NVLS": "0"})
+
+
+def test_withheld_signal_becomes_an_error_status(gpu_count):
+    if gpu_count < 2:
+        pytest.skip("needs 2 GPUs")
+    cases = _run(2, "withhold", {"NCCL_NVLS_ENABLE": "0"}, timeout=300)
+    assert {c["case"] for c in cases} >= {"withheld_signal_detected", "recovers_after_reset"}

@@ -1,0 +1,180 @@
+"""Numerics of the tcgen05 kernel on one GPU against a plain fp32 PyTorch reference: every
+operand layout, dtype, tile width, CTA pairing and ragged shape, plus the W = 1 path of the
+fused ops and the heap primitives in a single process."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _ref(a, b, ta, tb):
+    return (a.t() if ta else a).float() @ (b.t() if tb else b).float()
+
+
+@pytest.fixture(scope="module")
+def catcoc(device):
+    import mm_rs_with_catlass_b200 as c
+    return c
+
+
+def _check_status(device, what):
+    from mm_rs_with_catlass_b200.ops._common import local_status, raise_on_status
+    torch.cuda.synchronize()
+    raise_on_status(local_status(device), what)
+
+
+LAYOUTS = [(False, False), (False, True), (True, False), (True, True)]
+
+
+@pytest.mark.parametrize("ta,tb", LAYOUTS)
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("pair", [1, 2])
+def test_layouts_and_dtypes(catcoc, device, ta, tb, dtype, pair):
+    from mm_rs_with_catlass_b200.utils.data import matmul_inputs
+    from mm_rs_with_catlass_b200.utils.verify import assert_close
+    M, N, K = 512, 768, 320
+    a, b = matmul_inputs(M, N, K, 0, dtype, device, trans_a=ta, trans_b=tb)
+    out = catcoc.matmul(a, b, trans_a=ta, trans_b=tb, tiling=catcoc.TilingConfig(cta_pair=pair))
+    _check_status(device, "gemm")
+    assert_close(out, _ref(a, b, ta, tb), k=K, what="layout %s%s" % (ta, tb))
+
+
+@pytest.mark.parametrize("M,N,K", [(23, 45, 68), (4, 128, 129), (200, 328, 136), (129, 257, 65), (1024, 5120, 6148),
+                                   (1, 8, 8), (300, 8, 1000)])
+@pytest.mark.parametrize("bn,pair", [(0, 1), (64, 1), (128, 2)])
+def test_ragged_shapes(catcoc, device, M, N, K, bn, pair):
+    """Shapes the reference records as failing or hanging (23x45x68, 4x128x129) and its
+    unaligned-K all-gather shape (K = 6148) go through the pad / clip paths here."""
+    from mm_rs_with_catlass_b200.utils.data import matmul_inputs
+    from mm_rs_with_catlass_b200.utils.verify import assert_close
+    a, b = matmul_inputs(M, N, K, 0, torch.bfloat16, device)
+    out = catcoc.matmul(a, b, tiling=catcoc.TilingConfig(bn=bn, cta_pair=pair))
+    _check_status(device, "ragged gemm")
+    assert out.shape == (M, N)
+    assert_close(out, _ref(a, b, False, False), k=K)
+
+
+def test_strided_views_and_out_argument(catcoc, device):
+    from mm_rs_with_catlass_b200.utils.verify import assert_close
+    big = torch.randn(300, 700, device=device).bfloat16()
+    a = big[:256, 100:612]                    # row pitch 700: needs the pad copy
+    bt = (torch.randn(384, 512, device=device) * 0.05).bfloat16().t()   # column-major view -> folded into trans_b
+    out = torch.empty(256, 384, dtype=torch.bfloat16, device=device)
+    r = catcoc.matmul(a, bt, out=out)
+    assert r is out
+    _check_status(device, "views")
+    assert_close(out, a.float() @ bt.float(), k=512)
+    with pytest.raises(ValueError):
+        catcoc.matmul(a, bt, out=torch.empty(8, 8, dtype=torch.bfloat16, device=device))
+    with pytest.raises(TypeError):
+        catcoc.matmul(a, bt.float())
+
+
+@pytest.mark.parametrize("tb", [False, True])
+@pytest.mark.parametrize("pair", [1, 2])
+def test_int8_exact_and_dequant(catcoc, device, tb, pair):
+    from mm_rs_with_catlass_b200.utils.data import quant_inputs
+    M, N, K = 384, 512, 640
+    x1, x2, s1, s2, bias = quant_inputs(M, N, K, 0, device, trans_b=tb)
+    acc = catcoc.matmul(x1, x2, trans_b=tb, bias=bias, tiling=catcoc.TilingConfig(cta_pair=pair))
+    _check_status(device, "int8")
+    ref = x1.double() @ (x2.t() if tb else x2).double() + bias.double()[None, :]
+    assert acc.dtype == torch.int32 and torch.equal(acc.double(), ref)
+    deq = catcoc.matmul(x1, x2, trans_b=tb, bias=bias, scale_m=s1, scale_n=s2, out_dtype=torch.float32,
+                        tiling=catcoc.TilingConfig(cta_pair=pair))
+    _check_status(device, "int8 dequant")
+    exp = (ref * s2.double()[None, :] * s1.double()[:, None]).float()
+    assert torch.allclose(deq, exp, rtol=1e-5, atol=1e-6)
+
+
+@pytest.mark.skipif(not hasattr(torch, "float8_e4m3fn"), reason="no fp8 dtype in this torch")
+def test_fp8_operands(catcoc, device):
+    M, N, K = 256, 256, 512
+    a = (torch.randn(M, K, device=device) * 0.5).to(torch.float8_e4m3fn)
+    b = (torch.randn(N, K, device=device) * 0.5).to(torch.float8_e4m3fn)
+    out = catcoc.matmul(a, b, trans_b=True, out_dtype=torch.bfloat16)
+    _check_status(device, "fp8")
+    ref = a.float() @ b.float().t()
+    assert torch.allclose(out.float(), ref, rtol=2e-2, atol=2e-2 * ref.abs().max().item())
+
+
+def test_repeated_launches_alternating_shapes(catcoc, device):
+    """Back-to-back launches on one stream with changing shapes: stale barrier / TMEM state
+    from one launch must not leak into the next."""
+    from mm_rs_with_catlass_b200.utils.data import matmul_inputs
+    from mm_rs_with_catlass_b200.utils.verify import assert_close
+    shapes = [(256, 256, 128), (130, 520, 72), (512, 256, 256)]
+    data = [matmul_inputs(m, n, k, 0, torch.bfloat16, device, seed=i) for i, (m, n, k) in enumerate(shapes)]
+    outs = []
+    for it in range(34):
+        a, b = data[it % 3]
+        outs.append((it % 3, catcoc.matmul(a, b, tiling=catcoc.TilingConfig(cta_pair=1 + it % 2))))
+    _check_status(device, "repeat")
+    for idx, o in outs:
+        a, b = data[idx]
+        assert_close(o, a.float() @ b.float(), k=shapes[idx][2])
+
+
+def test_world1_fused_ops_and_heap(catcoc, device):
+    from mm_rs_with_catlass_b200.ops import reference
+    from mm_rs_with_catlass_b200.utils.data import matmul_inputs, quant_inputs
+    from mm_rs_with_catlass_b200.utils.verify import assert_close
+    ctx = catcoc.init(heap_bytes=64 << 20, make_default=False)
+    try:
+        assert ctx.world == 1 and ctx.heap_bytes >= 64 << 20
+        a, b = matmul_inputs(256, 384, 512, 0, torch.bfloat16, device)
+        gold = a.float() @ b.float()
+        assert_close(catcoc.matmul_reduce_scatter(a, b, ctx=ctx), gold, k=512)
+        assert_close(catcoc.matmul_allreduce(a, b, ctx=ctx), gold, k=512)
+        out, g = catcoc.allgather_matmul(a, b, ctx=ctx)
+        assert_close(out, gold, k=512)
+        assert g.data_ptr() == a.data_ptr()
+        x1, x2, s1, s2, bias = quant_inputs(256, 384, 512, 0, device)
+        q = catcoc.quant_matmul_reduce_scatter(x1, x2, s1, s2, bias, ctx=ctx)
+        assert_close(q, reference.quant_matmul_reduce_scatter(x1, x2, s1, s2, bias, out_dtype=torch.float32), k=512,
+                     dtype=torch.bfloat16)
+        # heap: allocation, views, put / get to self, signal + bounded wait, barrier
+        buf = ctx.malloc(1 << 16)
+        sig = ctx.malloc(64)
+        assert buf.offset % 256 == 0 and buf.ptr() == ctx.base(0) + buf.offset
+        src = torch.arange(1 << 14, dtype=torch.int32, device=device)
+        ctx.put(0, buf, src, signal=sig, signal_value=1)
+        ctx.wait_until(sig, ctx.put_blocks(), timeout_ms=2000)
+        ctx.barrier()
+        back = torch.empty_like(src)
+        ctx.get(0, back, buf)
+        ctx.check("heap primitives")
+        assert torch.equal(buf.tensor(torch.int32, (1 << 14,)), src) and torch.equal(back, src)
+        with pytest.raises(catcoc.ShmemError):
+            ctx.malloc(1 << 40)
+    finally:
+        ctx.finalize()
+        ctx.finalize()      # idempotent
+
+
+def test_bounded_wait_reports_a_status_instead_of_hanging(catcoc, device):
+    """A wait on a signal nothing ever sets gives up after its budget; the kernel returns, the
+    host reads an error status and the context stays usable."""
+    ctx = catcoc.init(heap_bytes=16 << 20, make_default=False)
+    try:
+        sig = ctx.malloc(64)
+        ctx.wait_until(sig, 1, timeout_ms=20)
+        with pytest.raises(RuntimeError, match="timed out"):
+            ctx.check("wait_until")
+        # still alive: the next kernel runs normally
+        a = torch.randn(128, 64, device=device).bfloat16()
+        b = torch.randn(64, 128, device=device).bfloat16()
+        o = catcoc.matmul(a, b)
+        ctx.check("after timeout")
+        assert torch.isfinite(o.float()).all()
+    finally:
+        ctx.finalize()
+
+
+def test_flagship_block_world1(catcoc, device):
+    from mm_rs_with_catlass_b200.models.tp_mlp import TPMLP, TPMLPConfig
+    from mm_rs_with_catlass_b200.utils.verify import assert_close
+    mlp = TPMLP(TPMLPConfig(hidden=512, ffn=1536), None, device)
+    x = torch.randn(384, 512, device=device).bfloat16()
+    assert_close(mlp(x), mlp.reference_forward(x).float(), k=1536)
+    _check_status(device, "tpmlp")

@@ -1,0 +1,95 @@
+"""Host-side replay of the device tile scheduler (the same C++ header, compiled for the host):
+coverage, uniqueness, visiting order and clipping for aligned and ragged shapes."""
+import ctypes as C
+import itertools
+
+import numpy as np
+import pytest
+
+from mm_rs_with_catlass_b200 import _native as N
+
+
+def tiles(M, Nn, bm, bn, W, seg_dim, first, swz):
+    lib = N.lib()
+    total = lib.catcoc_sched_total_tiles(M, Nn, bm, bn, W, seg_dim)
+    out = []
+    for t in range(total):
+        ti = N.Tile()
+        assert lib.catcoc_sched_get_tile(M, Nn, bm, bn, W, seg_dim, first, swz, t, C.byref(ti)) == 0
+        out.append(ti)
+    return out
+
+
+SHAPES = [(256, 512), (1024, 1024), (23, 45), (4, 129), (200, 328), (1030, 260), (129, 8), (8192, 256)]
+
+
+@pytest.mark.parametrize("M,Nn", SHAPES)
+@pytest.mark.parametrize("W", [1, 2, 3, 4, 8])
+@pytest.mark.parametrize("seg_dim", [0, 1])
+@pytest.mark.parametrize("bm,bn,swz", [(128, 256, 8), (128, 64, 3), (256, 128, 1), (128, 128, 16)])
+def test_every_element_is_covered_exactly_once(M, Nn, W, seg_dim, bm, bn, swz):
+    cover = np.zeros((M, Nn), dtype=np.int32)
+    seen_ids = set()
+    for ti in tiles(M, Nn, bm, bn, W, seg_dim, first=1 % W, swz=swz):
+        assert 0 <= ti.rows <= bm and 0 <= ti.cols <= bn
+        assert (ti.seg, ti.tile_in_seg) not in seen_ids
+        seen_ids.add((ti.seg, ti.tile_in_seg))
+        if ti.rows and ti.cols:
+            assert ti.m0 + ti.rows <= M and ti.n0 + ti.cols <= Nn
+            cover[ti.m0:ti.m0 + ti.rows, ti.n0:ti.n0 + ti.cols] += 1
+    assert (cover == 1).all()
+
+
+@pytest.mark.parametrize("W", [2, 4, 8])
+@pytest.mark.parametrize("seg_dim", [0, 1])
+def test_tiles_stay_inside_their_segment(W, seg_dim):
+    M, Nn = 1024 + 8 * W, 768 + 8 * W
+    seg_len = -(-(M if seg_dim == 0 else Nn) // W)
+    for ti in tiles(M, Nn, 128, 256, W, seg_dim, 0, 8):
+        if not (ti.rows and ti.cols):
+            continue
+        lo, n = (ti.m0, ti.rows) if seg_dim == 0 else (ti.n0, ti.cols)
+        assert ti.seg * seg_len <= lo and lo + n <= (ti.seg + 1) * seg_len
+
+
+@pytest.mark.parametrize("W", [2, 3, 8])
+def test_segments_are_visited_in_rotated_order_own_last(W):
+    for rank in range(W):
+        first = (rank + 1) % W           # reduce-scatter / all-reduce order
+        segs = [ti.seg for ti in tiles(1024, 512, 128, 256, W, 0, first, 8)]
+        order = list(dict.fromkeys(segs))
+        assert order == [(first + p) % W for p in range(W)]
+        assert order[-1] == rank
+        # segments are contiguous runs: a rank finishes one destination before the next
+        assert segs == sorted(segs, key=order.index)
+
+
+def test_tile_ids_do_not_depend_on_the_swizzle():
+    base = {(t.seg, t.mi, t.ni): t.tile_in_seg for t in tiles(2048, 2048, 128, 256, 4, 0, 0, 1)}
+    for swz in (2, 5, 8, 64):
+        for t in tiles(2048, 2048, 128, 256, 4, 0, 2, swz):
+            assert base[(t.seg, t.mi, t.ni)] == t.tile_in_seg
+
+
+def test_serpentine_groups_keep_neighbours_close():
+    ts = tiles(2048, 4096, 128, 256, 1, 0, 0, 4)
+    for a, b in zip(ts, ts[1:]):
+        assert abs(a.mi - b.mi) + abs(a.ni - b.ni) <= 4   # no jumps across the matrix
+
+
+def test_workspace_geometry_matches_the_schedule():
+    lib = N.lib()
+    for (M, Nn, W, bn, pair) in itertools.product((1024, 8192), (512, 8192), (2, 8), (64, 256), (1, 2)):
+        if pair == 2 and bn < 128:
+            continue
+        bm = 256 if pair == 2 else 128
+        per_seg = lib.catcoc_sched_total_tiles(M, Nn, bm, bn, W, 0) // W
+        assert lib.catcoc_stage_bytes(M, Nn, W, 0, bn, pair, N.FMT_BF16) == 2 * W * per_seg * bm * bn * 2
+        assert lib.catcoc_stage_bytes(M, Nn, W, 0, bn, pair, N.FMT_S32) == 2 * W * per_seg * bm * bn * 4
+        assert lib.catcoc_arrive_words(M, Nn, W, 0, bn, pair) == per_seg * W * (bm // 32)
+        assert lib.catcoc_done_words(M, Nn, W, 0, bn, pair) == per_seg * W * (bm // 32)
+
+
+def test_bad_tile_index_is_rejected():
+    ti = N.Tile()
+    assert N.lib().catcoc_sched_get_tile(256, 256, 128, 256, 1, 0, 0, 1, 99, C.byref(ti)) == N.E_BAD_ARG
