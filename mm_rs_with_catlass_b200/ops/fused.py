@@ -126,7 +126,10 @@ def matmul_reduce_scatter(a: torch.Tensor, b: torch.Tensor, *, trans_a: bool = F
 
     Per rank: ``a`` ``[M, K_r]`` and ``b`` ``[K_r, N]`` (transposed storage with the flags).
     Returns rows ``[rank*M/W, (rank+1)*M/W)`` of ``sum_r A_r @ B_r`` as ``[M/W, N]``.
-    Partials cross NVLink in the operand dtype and are summed in fp32 in a fixed rank order.
+    Partials cross NVLink in the operand dtype (as the reference's do, and as NCCL's payload
+    in the unfused pipeline is) and are summed in fp32 in a fixed rank order, so the result is
+    deterministic; the owner's own partial is never rounded. ``tiling.fp32_partials`` sends fp32
+    partials instead (twice the bytes, no intermediate rounding at all).
     """
     dev = cm.require_cuda(a, b, out)
     _check_pair(a, b)
@@ -147,7 +150,7 @@ def matmul_reduce_scatter(a: torch.Tensor, b: torch.Tensor, *, trans_a: bool = F
     with torch.cuda.device(dev):
         args, keep = _base_args(ctx, N.MODE_RS, a, trans_a, b, trans_b, m, n, k, t, seg_rows=rows)
         args.out, args.ldc, args.out_fmt = out.data_ptr(), out.stride(0), cm.out_fmt(out.dtype)
-        _attach_stage(ctx, args, m, n, _SEG_ROWS, t, cm.out_fmt(a.dtype))
+        _attach_stage(ctx, args, m, n, _SEG_ROWS, t, N.FMT_F32 if t.fp32_partials else cm.out_fmt(a.dtype))
         _launched(ctx, args)
     return out
 
@@ -195,7 +198,7 @@ def matmul_allreduce(a: torch.Tensor, b: torch.Tensor, *, trans_a: bool = False,
             args.done[p] = done.ptr(p)
         args.ar_out_mc = obuf.mc_ptr() or None
         args.done_mc = done.mc_ptr() or None
-        _attach_stage(ctx, args, m, n, seg_dim, t, cm.out_fmt(a.dtype))
+        _attach_stage(ctx, args, m, n, seg_dim, t, N.FMT_F32 if t.fp32_partials else cm.out_fmt(a.dtype))
         epoch = _launched(ctx, args)
         view = obuf.tensor(a.dtype, (m, n), byte_offset=(epoch & 1) * parity_bytes)
     if out is not None:

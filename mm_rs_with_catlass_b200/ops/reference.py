@@ -28,6 +28,15 @@ def local_matmul_f32(a: torch.Tensor, b: torch.Tensor, trans_a: bool = False, tr
     return _logical(a, trans_a).float() @ _logical(b, trans_b).float()
 
 
+def partial_magnitude(a, b, *, trans_a=False, trans_b=False, group=None) -> torch.Tensor:
+    """``sum_r |A_r @ B_r|``: the scale of the rounding error when partial results are rounded
+    before they are summed (see utils.verify.verify)."""
+    mag = local_matmul_f32(a, b, trans_a, trans_b).abs()
+    if _world(group)[1] > 1:
+        dist.all_reduce(mag, group=group)
+    return mag
+
+
 def matmul_allreduce(a, b, *, trans_a=False, trans_b=False, out_dtype=None, group=None) -> torch.Tensor:
     """fp32 ``sum_r A_r @ B_r`` on every rank, rounded once to ``out_dtype``."""
     full = local_matmul_f32(a, b, trans_a, trans_b)

@@ -65,7 +65,7 @@ def workspace_bytes(p: Problem, t: TilingConfig) -> int:
         tiles_per_seg = math.ceil(p.m / bm) * math.ceil(seg / bn)
     total = 0
     if p.op in ("matmul_allreduce", "matmul_reduce_scatter", "quant_matmul_reduce_scatter"):
-        pelt = 4 if p.op == "quant_matmul_reduce_scatter" else p.elt
+        pelt = 4 if (p.op == "quant_matmul_reduce_scatter" or t.fp32_partials) else p.elt
         total += 2 * p.world * tiles_per_seg * bm * bn * pelt            # staging, two parities
         total += 4 * tiles_per_seg * p.world * (bm // 32)                 # arrival stamps
     if p.op == "matmul_allreduce":

@@ -38,8 +38,8 @@ def report(name, ok, detail=""):
         print(json.dumps({"case": name, "ok": ok_all, "detail": detail if not ok else ""}), flush=True)
 
 
-def check(name, out, gold, k, dtype):
-    r = verify(out, gold, k, dtype)
+def check(name, out, gold, k, dtype, magnitude=None):
+    r = verify(out, gold, k, dtype, magnitude)
     try:
         ctx.check(name)
         st = ""
@@ -60,24 +60,36 @@ if mode == "ops":
             for ti, tiling in enumerate(TILINGS):
                 a, b = matmul_inputs(M, N, K, rank, dtype, dev, trans_a=ta, trans_b=tb, seed=M + N)
                 gold_full = ref.matmul_allreduce(a, b, trans_a=ta, trans_b=tb, out_dtype=torch.float32)
+                mag = ref.partial_magnitude(a, b, trans_a=ta, trans_b=tb)
                 rows = M // W
+                sl = slice(rank * rows, (rank + 1) * rows)
                 tag = "%s_%dx%dx%d_%d%d_t%d" % (str(dtype)[6:], M, N, K, ta, tb, ti)
+                # partial tiles cross the link rounded to the operand dtype: error scales with sum |partial|
                 o = catcoc.matmul_reduce_scatter(a, b, trans_a=ta, trans_b=tb, tiling=tiling)
-                check("rs_" + tag, o, gold_full[rank * rows:(rank + 1) * rows], K * W, dtype)
+                check("rs_" + tag, o, gold_full[sl], K * W, dtype, mag[sl])
                 o = catcoc.matmul_allreduce(a, b, trans_a=ta, trans_b=tb, tiling=tiling)
-                check("ar_" + tag, o, gold_full, K * W, dtype)
+                check("ar_" + tag, o, gold_full, K * W, dtype, mag)
+                # fp32 partials: the plain element-wise rule holds
+                t32 = (tiling or catcoc.TilingConfig()).with_(fp32_partials=True)
+                o = catcoc.matmul_reduce_scatter(a, b, trans_a=ta, trans_b=tb, tiling=t32)
+                check("rs32_" + tag, o, gold_full[sl], K * W, dtype)
+                o = catcoc.matmul_allreduce(a, b, trans_a=ta, trans_b=tb, tiling=t32)
+                check("ar32_" + tag, o, gold_full, K * W, dtype)
         # all-reduce with fewer rows than ranks * 128: ownership splits by columns
         a, b = matmul_inputs(96, 1024, 256, rank, dtype, dev, seed=11)
         gold = ref.matmul_allreduce(a, b, out_dtype=torch.float32)
-        check("ar_smallM_%s" % str(dtype)[6:], catcoc.matmul_allreduce(a, b), gold, 256 * W, dtype)
+        mag = ref.partial_magnitude(a, b)
+        check("ar_smallM_%s" % str(dtype)[6:], catcoc.matmul_allreduce(a, b), gold, 256 * W, dtype, mag)
         for seg in (0, 1):
             check("ar_seg%d_%s" % (seg, str(dtype)[6:]),
-                  catcoc.matmul_allreduce(a, b, tiling=catcoc.TilingConfig(bn=64, seg_dim=seg)), gold, 256 * W, dtype)
+                  catcoc.matmul_allreduce(a, b, tiling=catcoc.TilingConfig(bn=64, seg_dim=seg)), gold, 256 * W, dtype,
+                  mag)
         if ctx.multicast:
             a, b = matmul_inputs(256 * W, 512, 256, rank, dtype, dev, seed=12)
             gold = ref.matmul_allreduce(a, b, out_dtype=torch.float32)
             check("ar_nvls_%s" % str(dtype)[6:],
-                  catcoc.matmul_allreduce(a, b, tiling=catcoc.TilingConfig(use_multicast=True)), gold, 256 * W, dtype)
+                  catcoc.matmul_allreduce(a, b, tiling=catcoc.TilingConfig(use_multicast=True)), gold, 256 * W, dtype,
+                  ref.partial_magnitude(a, b))
         for (m, N, K, tb) in [(256, 512, 512, False), (384, 640, 1024, True), (100, 328, 136, False), (64, 256, 6148, False)]:
             for ti, tiling in enumerate(TILINGS):
                 a, b = matmul_inputs(m, N, K, rank, dtype, dev, trans_b=tb, seed=m + K)
@@ -101,15 +113,16 @@ if mode == "ops":
     # many back-to-back launches of mixed ops on one context (epoch parity, stamp reuse)
     a, b = matmul_inputs(128 * W, 256, 128, rank, torch.bfloat16, dev, seed=77)
     gold = ref.matmul_allreduce(a, b, out_dtype=torch.float32)
+    mag = ref.partial_magnitude(a, b)
     rows = 128
     ok = True
     for it in range(60):
         if it % 3 == 0:
             o = catcoc.matmul_reduce_scatter(a, b)
-            ok &= verify(o, gold[rank * rows:(rank + 1) * rows], 128 * W, torch.bfloat16).ok
+            ok &= verify(o, gold[rank * rows:(rank + 1) * rows], 128 * W, torch.bfloat16, mag[rank * rows:(rank + 1) * rows]).ok
         elif it % 3 == 1:
             o = catcoc.matmul_allreduce(a, b).clone()
-            ok &= verify(o, gold, 128 * W, torch.bfloat16).ok
+            ok &= verify(o, gold, 128 * W, torch.bfloat16, mag).ok
         else:
             o, _ = catcoc.allgather_matmul(a[:64], b[:128] if False else b)
             ok &= bool(torch.isfinite(o.float()).all())
@@ -123,7 +136,9 @@ if mode == "ops":
     from mm_rs_with_catlass_b200.models.tp_mlp import TPMLP, TPMLPConfig
     mlp = TPMLP(TPMLPConfig(hidden=512, ffn=256 * W), ctx, dev)
     x = torch.randn(128, 512, device=dev).bfloat16()
-    check("tpmlp", mlp(x), mlp.reference_forward(x).float(), 256 * W, torch.bfloat16)
+    h_ref, _ = ref.allgather_matmul(x, mlp.w_up, out_dtype=torch.bfloat16)
+    check("tpmlp", mlp(x), mlp.reference_forward(x).float(), 256 * W, torch.bfloat16,
+          ref.partial_magnitude(mlp._act(h_ref), mlp.w_down)[rank * 128:(rank + 1) * 128])
     ctx.finalize()
 
 elif mode == "withhold":
@@ -156,7 +171,9 @@ elif mode == "withhold":
     ctx.reset_after_error()
     gold = ref.matmul_reduce_scatter(a, b, out_dtype=torch.float32)
     o = catcoc.matmul_reduce_scatter(a, b)
-    check("recovers_after_reset", o, gold, 128 * world, torch.bfloat16)
+    rows = 128
+    check("recovers_after_reset", o, gold, 128 * world, torch.bfloat16,
+          ref.partial_magnitude(a, b)[rank * rows:(rank + 1) * rows])
     ctx.finalize()
 
 dist.barrier()
