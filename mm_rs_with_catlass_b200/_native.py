@@ -127,6 +127,8 @@ def _declare(lib) -> None:
         "catcoc_shmem_mc_reduce_bf16": (i32, [P(ShmemCtx), vp, i64, i64, vp]),
         "catcoc_shmem_put_blocks": (i32, []),
         "catcoc_pad2d": (i32, [vp, i64, vp, i64, i64, i64, vp]),
+        "catcoc_matmul_noalloc": (i32, [vp, i64, vp, i64, vp, i64, i32, i32, i32, i32, i32, i32, i32, vp]),
+        "catcoc_matmul_noalloc_status": (i32, [P(u32)]),
     }
     for name, (res, args) in sigs.items():
         fn = getattr(lib, name)
