@@ -34,7 +34,7 @@ STATUS_NAMES = {
 
 class Tiling(C.Structure):
     _fields_ = [("bn", C.c_int), ("swizzle", C.c_int), ("num_ctas", C.c_int), ("seg_dim", C.c_int),
-                ("use_multicast", C.c_int), ("cta_pair", C.c_int)]
+                ("use_multicast", C.c_int), ("rounds", C.c_int), ("cta_pair", C.c_int)]
 
 
 class OpArgs(C.Structure):
@@ -100,6 +100,7 @@ def _declare(lib) -> None:
         "catcoc_gather_flag_words": (i64, [i32, i32, i32, i32]),
         "catcoc_sched_total_tiles": (i32, [i32] * 6),
         "catcoc_sched_get_tile": (i32, [i32] * 9 + [P(Tile)]),
+        "catcoc_sched_get_tile_rounds": (i32, [i32] * 10 + [P(Tile)]),
         "catcoc_oracle_matmul_f32": (i32, [vp, vp, vp, i32, i32, i32, i32, i32]),
         "catcoc_oracle_quant_matmul": (i32, [vp, vp, vp, vp, i32, i32, i32, i32, i32]),
         "catcoc_oracle_dequant": (i32, [vp, vp, vp, vp, i32, i32]),

@@ -43,6 +43,7 @@ typedef struct CatcocTiling {
   int num_ctas;    /* persistent CTAs (0 = one per SM)                                   */
   int seg_dim;     /* all-reduce ownership split: 0 rows, 1 cols, -1 auto                */
   int use_multicast; /* all-reduce broadcast through the NVLS multicast alias if mapped  */
+  int rounds;      /* owner work is spread over this many rounds (0 = default); reduce-scatter / all-reduce */
   int cta_pair;    /* 2: 256-row tiles on 2-CTA clusters (tcgen05 cta_group::2); else 1 CTA */
 } CatcocTiling;
 
@@ -101,6 +102,8 @@ typedef struct CatcocTile {
 int catcoc_sched_total_tiles(int M, int N, int bm, int bn, int W, int seg_dim);
 int catcoc_sched_get_tile(int M, int N, int bm, int bn, int W, int seg_dim, int first_seg,
                           int swizzle, int t, CatcocTile* out);
+int catcoc_sched_get_tile_rounds(int M, int N, int bm, int bn, int W, int seg_dim, int first_seg,
+                                 int swizzle, int rounds, int t, CatcocTile* out);
 
 /* ---- CPU oracle (naive fp32 / int32 loops; see csrc/oracle/oracle.cpp) ---- */
 int catcoc_oracle_matmul_f32(const float* a, const float* b, float* c, int M, int N, int K,

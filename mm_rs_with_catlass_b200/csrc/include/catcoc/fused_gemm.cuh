@@ -477,7 +477,7 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
     uint32_t acc_phase = 0;
     bool ok = true;
     const bool tr = (p.trace != nullptr) && lane == 0 && q == 0;
-    unsigned long long c_full = 0, c_work = 0, c_peer = 0;
+    unsigned long long c_full = 0, c_work = 0, c_peer = 0, c_pub = 0, c_own = 0;
     Tick tick(tr);
 
     for (int t = worker; ok && t < sched.total_tiles; t += num_workers) {
@@ -583,38 +583,56 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
           }
 
           if (reduce_here && row_in_tile < ti.rows) {
-            // fold the peers' partials in a fixed source order => deterministic sum
-            for (int src = 0; src < p.W; ++src) {
-              if (src == p.rank) continue;
-              const uint8_t* sp = p.stage[p.rank] +
-                                  stage_slot_offset(sched, pelt, parity, src, ti.tile_in_seg) +
-                                  (static_cast<int64_t>(row_in_tile) * BN + col0) * pelt;
-              if (pelt == 2) {
+            // fold the peers' partials in a fixed source order => deterministic sum. The loads of
+            // two sources are issued back to back before their adds to keep more bytes in flight.
+            const uint8_t* sbase = p.stage[p.rank] + (static_cast<int64_t>(row_in_tile) * BN + col0) * pelt;
+            const int64_t slot_bytes = stage_tile_bytes(sched, pelt);
+            const int64_t src_stride = static_cast<int64_t>(sched.tiles_per_seg) * slot_bytes;
+            const int64_t base_off = (static_cast<int64_t>(parity) * p.W * sched.tiles_per_seg + ti.tile_in_seg) * slot_bytes;
+            if (pelt == 2) {
+              for (int s0 = 0; s0 < p.W; s0 += 2) {
+                uint4 w[2][4];
 #pragma unroll
-                for (int u = 0; u < 4; ++u) {
-                  const uint4 w = ptx::ld_global_v4(sp + u * 16);
-                  const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+                for (int j = 0; j < 2; ++j) {
+                  const int src = s0 + j;
+                  if (src < p.W && src != p.rank) {
 #pragma unroll
-                  for (int e = 0; e < 4; ++e) {
-                    const float2 f = unpack2(ww[e], pfmt);
-                    v[u * 8 + e * 2] = __float_as_uint(__uint_as_float(v[u * 8 + e * 2]) + f.x);
-                    v[u * 8 + e * 2 + 1] =
-                        __float_as_uint(__uint_as_float(v[u * 8 + e * 2 + 1]) + f.y);
+                    for (int u = 0; u < 4; ++u) w[j][u] = ptx::ld_global_v4(sbase + base_off + src * src_stride + u * 16);
                   }
                 }
-              } else {
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {
+                  const int src = s0 + j;
+                  if (src < p.W && src != p.rank) {
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                      const uint32_t ww[4] = {w[j][u].x, w[j][u].y, w[j][u].z, w[j][u].w};
+#pragma unroll
+                      for (int e = 0; e < 4; ++e) {
+                        const float2 f = unpack2(ww[e], pfmt);
+                        v[u * 8 + e * 2] = __float_as_uint(__uint_as_float(v[u * 8 + e * 2]) + f.x);
+                        v[u * 8 + e * 2 + 1] = __float_as_uint(__uint_as_float(v[u * 8 + e * 2 + 1]) + f.y);
+                      }
+                    }
+                  }
+                }
+              }
+            } else {
+              for (int src = 0; src < p.W; ++src) {
+                if (src == p.rank) continue;
+                const uint8_t* sp = sbase + base_off + src * src_stride;
+                uint4 w[8];
+#pragma unroll
+                for (int u = 0; u < 8; ++u) w[u] = ptx::ld_global_v4(sp + u * 16);
 #pragma unroll
                 for (int u = 0; u < 8; ++u) {
-                  const uint4 w = ptx::ld_global_v4(sp + u * 16);
-                  const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+                  const uint32_t ww[4] = {w[u].x, w[u].y, w[u].z, w[u].w};
 #pragma unroll
                   for (int e = 0; e < 4; ++e) {
                     if (pfmt == FMT_S32)
-                      v[u * 4 + e] = static_cast<uint32_t>(static_cast<int32_t>(v[u * 4 + e]) +
-                                                           static_cast<int32_t>(ww[e]));
+                      v[u * 4 + e] = static_cast<uint32_t>(static_cast<int32_t>(v[u * 4 + e]) + static_cast<int32_t>(ww[e]));
                     else
-                      v[u * 4 + e] = __float_as_uint(__uint_as_float(v[u * 4 + e]) +
-                                                     __uint_as_float(ww[e]));
+                      v[u * 4 + e] = __float_as_uint(__uint_as_float(v[u * 4 + e]) + __uint_as_float(ww[e]));
                   }
                 }
               }
@@ -677,6 +695,7 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
         }
         __syncwarp();
       }
+      if (reduce_here) tick.lap(c_own);
       if (!released) {
         // degenerate (empty) tile: nothing was read, still return the accumulator
         ptx::tcgen05_fence_before();
@@ -689,8 +708,10 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
 
       // ---- publish this warp's quarter of the tile ----
       if (fused && (p.mode == MODE_RS || p.mode == MODE_AR) && (!own || p.mode == MODE_AR)) {
-        ptx::fence_acq_rel_sys();   // every lane: my stores before the stamp, system-wide
+        // Data stores of all 32 lanes happen-before lane 0's release through the warp barrier;
+        // the release is cumulative, so one system-scope release by one lane publishes them all.
         __syncwarp();
+        tick.lap(c_work);
         if (!p.withhold_signals) {
           if (!own) {
             if (lane == 0)
@@ -709,12 +730,16 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
         }
       }
 
+      tick.lap(c_pub);
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1u;
     }
 
     tick.lap(c_work);
-    if (tr) { atomicAdd(p.trace + 5, c_full); atomicAdd(p.trace + 6, c_work); atomicAdd(p.trace + 7, c_peer); }
+    if (tr) {
+      atomicAdd(p.trace + 5, c_full); atomicAdd(p.trace + 6, c_work); atomicAdd(p.trace + 7, c_peer);
+      atomicAdd(p.trace + 9, c_pub); atomicAdd(p.trace + 10, c_own);
+    }
 
     // all-reduce tail: this rank's output is complete only when every owner's tiles landed
     if (fused && p.mode == MODE_AR && ok && !*abort_flag) {

@@ -42,6 +42,13 @@ struct TileSched {
   int seg_mt, seg_nt;    // tiles per segment along rows / cols
   int tiles_per_seg;     // seg_mt * seg_nt
   int total_tiles;       // W * tiles_per_seg
+  // Rounds: every segment's tiles are cut into `rounds` groups (along rows for a row split,
+  // along columns for a column split) and the W segments are visited once per round. The
+  // owner's tiles of round i are reduced / broadcast while round i+1 is being computed, so
+  // only the last round's owner work is exposed (the reference's "comm interval" idea,
+  // include/catcoc/dgemm/kernel/matmul_allreduce.hpp:116-133, without its global barriers).
+  int rounds;
+  int round_len;         // tiles along the cut dimension per round (last round may be shorter)
 };
 
 struct TileInfo {
@@ -53,7 +60,7 @@ struct TileInfo {
 };
 
 CATCOC_HD TileSched make_sched(int M, int N, int BM, int BN, int W, int seg_dim, int first_seg,
-                               int swizzle) {
+                               int swizzle, int rounds = 1) {
   TileSched s;
   s.M = M; s.N = N; s.BM = BM; s.BN = BN; s.W = W < 1 ? 1 : W;
   s.seg_dim = seg_dim;
@@ -70,20 +77,27 @@ CATCOC_HD TileSched make_sched(int M, int N, int BM, int BN, int W, int seg_dim,
   s.first_seg = ((first_seg % s.W) + s.W) % s.W;
   s.tiles_per_seg = s.seg_mt * s.seg_nt;
   s.total_tiles = s.tiles_per_seg * s.W;
+  const int cut = (seg_dim == SEG_ROWS) ? s.seg_mt : s.seg_nt;
+  s.rounds = rounds < 1 ? 1 : (rounds > cut ? cut : rounds);
+  s.round_len = ceil_div(cut, s.rounds);
+  s.rounds = ceil_div(cut, s.round_len);
   return s;
 }
 
-// Position of a tile inside its segment from its linear index (swizzled order).
-CATCOC_HD void seg_tile_coord(const TileSched& s, int i, int* mi, int* ni) {
-  const int group_tiles = s.swizzle * s.seg_mt;
+// Position of a tile inside an mt x nt grid from its linear index (swizzled order).
+CATCOC_HD void grid_tile_coord(int mt, int nt, int swizzle, int i, int* mi, int* ni) {
+  const int group_tiles = swizzle * mt;
   const int g = i / group_tiles;
   const int within = i - g * group_tiles;
-  const int gw = imin(s.swizzle, s.seg_nt - g * s.swizzle);
+  const int gw = imin(swizzle, nt - g * swizzle);
   int m = within / gw;
-  const int n = g * s.swizzle + (within - m * gw);
-  if (g & 1) m = s.seg_mt - 1 - m;  // serpentine: odd groups walk rows bottom-up
+  const int n = g * swizzle + (within - m * gw);
+  if (g & 1) m = mt - 1 - m;  // serpentine: odd groups walk rows bottom-up
   *mi = m;
   *ni = n;
+}
+CATCOC_HD void seg_tile_coord(const TileSched& s, int i, int* mi, int* ni) {
+  grid_tile_coord(s.seg_mt, s.seg_nt, s.swizzle, i, mi, ni);
 }
 
 // Inverse of seg_tile_coord: the canonical id used to address staging slots and flags.
@@ -93,10 +107,33 @@ CATCOC_HD int seg_tile_id(const TileSched& s, int mi, int ni) { return mi * s.se
 
 CATCOC_HD TileInfo get_tile(const TileSched& s, int t) {
   TileInfo ti;
-  const int phase = t / s.tiles_per_seg;
-  const int i = t - phase * s.tiles_per_seg;
-  ti.seg = (s.first_seg + phase) % s.W;
-  seg_tile_coord(s, i, &ti.mi, &ti.ni);
+  // t -> (round, phase, index inside the round's slice of the segment)
+  int round = 0, phase, i;
+  if (s.rounds <= 1) {
+    phase = t / s.tiles_per_seg;
+    i = t - phase * s.tiles_per_seg;
+    ti.seg = (s.first_seg + phase) % s.W;
+    seg_tile_coord(s, i, &ti.mi, &ti.ni);
+  } else {
+    const int other = (s.seg_dim == SEG_ROWS) ? s.seg_nt : s.seg_mt;   // tiles along the uncut dim
+    const int full_round_tiles = s.round_len * other * s.W;
+    round = t / full_round_tiles;
+    const int cut = (s.seg_dim == SEG_ROWS) ? s.seg_mt : s.seg_nt;
+    const int this_len = imin(s.round_len, cut - round * s.round_len);   // last round may be short
+    const int per_phase = this_len * other;
+    const int r = t - round * full_round_tiles;
+    phase = r / per_phase;
+    i = r - phase * per_phase;
+    ti.seg = (s.first_seg + phase) % s.W;
+    // swizzled walk inside the round's slice: a sub-grid of this_len x other tiles
+    if (s.seg_dim == SEG_ROWS) {
+      grid_tile_coord(this_len, s.seg_nt, s.swizzle, i, &ti.mi, &ti.ni);
+      ti.mi += round * s.round_len;
+    } else {
+      grid_tile_coord(s.seg_mt, this_len, s.swizzle, i, &ti.mi, &ti.ni);
+      ti.ni += round * s.round_len;
+    }
+  }
   ti.tile_in_seg = seg_tile_id(s, ti.mi, ti.ni);
   if (s.seg_dim == SEG_ROWS) {
     const int seg_begin = ti.seg * s.seg_len;

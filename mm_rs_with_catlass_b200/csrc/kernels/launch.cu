@@ -160,7 +160,9 @@ static TileSched build_sched(const CatcocOpArgs& a, int bm, int bn, int seg_dim)
   int first = 0;
   if (fused) first = (a.mode == CATCOC_MODE_AG) ? a.rank : (a.rank + 1) % W;
   const int swz = a.tiling.swizzle > 0 ? a.tiling.swizzle : 8;
-  return make_sched(a.M, a.N, bm, bn, W, seg_dim, first, swz);
+  int rounds = 1;
+  if (fused && (a.mode == CATCOC_MODE_RS || a.mode == CATCOC_MODE_AR)) rounds = a.tiling.rounds > 0 ? a.tiling.rounds : 4;
+  return make_sched(a.M, a.N, bm, bn, W, seg_dim, first, swz, rounds);
 }
 
 }  // namespace host
@@ -196,6 +198,15 @@ extern "C" int64_t catcoc_gather_flag_words(int m, int K, int W, int elt_bytes) 
 
 extern "C" int catcoc_sched_total_tiles(int M, int N, int bm, int bn, int W, int seg_dim) {
   return make_sched(M, N, bm, bn, W, seg_dim, 0, 1).total_tiles;
+}
+extern "C" int catcoc_sched_get_tile_rounds(int M, int N, int bm, int bn, int W, int seg_dim, int first_seg,
+                                            int swizzle, int rounds, int t, CatcocTile* out) {
+  TileSched s = make_sched(M, N, bm, bn, W, seg_dim, first_seg, swizzle, rounds);
+  if (t < 0 || t >= s.total_tiles || out == nullptr) return CATCOC_E_BAD_ARG;
+  TileInfo ti = get_tile(s, t);
+  out->seg = ti.seg; out->tile_in_seg = ti.tile_in_seg; out->mi = ti.mi; out->ni = ti.ni;
+  out->m0 = ti.m0; out->n0 = ti.n0; out->rows = ti.rows; out->cols = ti.cols;
+  return CATCOC_OK;
 }
 extern "C" int catcoc_sched_get_tile(int M, int N, int bm, int bn, int W, int seg_dim,
                                      int first_seg, int swizzle, int t, CatcocTile* out) {

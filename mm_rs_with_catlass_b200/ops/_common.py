@@ -115,6 +115,7 @@ def fill_tiling(args: N.OpArgs, tiling: Optional[TilingConfig]) -> None:
     args.tiling.seg_dim = t.seg_dim
     args.tiling.use_multicast = 1 if t.use_multicast else 0
     args.tiling.cta_pair = t.cta_pair
+    args.tiling.rounds = t.rounds
 
 
 def default_timeout_ns() -> int:

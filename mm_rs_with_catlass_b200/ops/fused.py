@@ -107,6 +107,9 @@ def _attach_stage(ctx: ShmemContext, args, m: int, n: int, seg_dim: int, t: Tili
 
 def _launched(ctx: ShmemContext, args) -> int:
     """Launch and advance the host mirror of the epoch; returns the epoch of this launch."""
+    trace = getattr(ctx, "trace", None)
+    if trace is not None:   # int64[16] device tensor of per-role cycle counters (params.h)
+        args.trace = trace.data_ptr()
     cm.launch(args, ctx.device)
     ctx.epoch += 1
     ctx.counters["launches"] += 1

@@ -34,6 +34,7 @@ class TilingConfig:
     num_ctas: int = 0      # persistent CTAs (0 = one per SM)
     seg_dim: int = -1      # all-reduce ownership split: 0 rows, 1 cols, -1 auto
     use_multicast: bool = False  # all-reduce broadcast through the NVLS alias
+    rounds: int = 0        # reduce-scatter / all-reduce: owner tiles are spread over this many rounds (0 = 4)
     fp32_partials: bool = False  # partial tiles cross NVLink in fp32 instead of the operand dtype (2x bytes, no rounding)
     cta_pair: int = 0      # 2: 256-row tiles on 2-CTA clusters (tcgen05 cta_group::2); 1: single CTA; 0 = 1
     # --- reference-compatible fields (carried, reported, not steering the kernel) ---
@@ -57,6 +58,8 @@ class TilingConfig:
             raise ValueError("cta_pair must be 0, 1 or 2")
         if self.cta_pair == 2 and self.bn not in (0, 128, 256):
             raise ValueError("cta_pair=2 needs bn of 128 or 256")
+        if self.rounds < 0 or self.rounds > 64:
+            raise ValueError("rounds must be in [0, 64]")
         if self.seg_dim not in (-1, 0, 1):
             raise ValueError("seg_dim must be -1, 0 or 1")
         return self

@@ -93,3 +93,39 @@ def test_workspace_geometry_matches_the_schedule():
 def test_bad_tile_index_is_rejected():
     ti = N.Tile()
     assert N.lib().catcoc_sched_get_tile(256, 256, 128, 256, 1, 0, 0, 1, 99, C.byref(ti)) == N.E_BAD_ARG
+
+
+def tiles_rounds(M, Nn, bm, bn, W, seg_dim, first, swz, rounds):
+    lib = N.lib()
+    total = lib.catcoc_sched_total_tiles(M, Nn, bm, bn, W, seg_dim)
+    out = []
+    for t in range(total):
+        ti = N.Tile()
+        assert lib.catcoc_sched_get_tile_rounds(M, Nn, bm, bn, W, seg_dim, first, swz, rounds, t, C.byref(ti)) == 0
+        out.append(ti)
+    return out
+
+
+@pytest.mark.parametrize("M,Nn", [(8192, 2048), (1024 + 136, 520), (200, 4096), (23, 45)])
+@pytest.mark.parametrize("W", [2, 3, 8])
+@pytest.mark.parametrize("seg_dim", [0, 1])
+@pytest.mark.parametrize("rounds", [1, 2, 4, 5, 64])
+def test_rounds_keep_coverage_and_ids(M, Nn, W, seg_dim, rounds):
+    base = {(t.seg, t.tile_in_seg): (t.m0, t.n0, t.rows, t.cols) for t in tiles(M, Nn, 128, 256, W, seg_dim, 1 % W, 8)}
+    got = tiles_rounds(M, Nn, 128, 256, W, seg_dim, 1 % W, 8, rounds)
+    assert len(got) == len(base)
+    seen = {}
+    for t in got:
+        seen[(t.seg, t.tile_in_seg)] = (t.m0, t.n0, t.rows, t.cols)
+    assert seen == base          # same tiles with the same ids and geometry, only the order differs
+
+
+def test_rounds_interleave_the_owner_segment():
+    W, rank = 8, 3
+    segs = [t.seg for t in tiles_rounds(8192, 8192, 128, 256, W, 0, (rank + 1) % W, 8, 4)]
+    # runs of equal segment: W per round, own segment closes every round
+    runs = [s for i, s in enumerate(segs) if i == 0 or segs[i - 1] != s]
+    assert len(runs) == 4 * W
+    assert runs[W - 1::W] == [rank] * 4
+    own_positions = [i for i, s in enumerate(segs) if s == rank]
+    assert own_positions[0] < len(segs) // 3        # owner work starts early instead of piling up at the end
