@@ -1,13 +1,16 @@
 // The one persistent, warp-specialised sm_100a kernel behind every op of this library.
 //
-//   warp 0      TMA producer   : cp.async.bulk.tensor A/B K-slices -> 128B-swizzled smem ring
-//   warp 1      MMA issuer     : one thread issues tcgen05.mma into a double-buffered TMEM
+//   warp 0      TMA producer A : cp.async.bulk.tensor K-slices of A -> 128B-swizzled smem ring
+//                                (all-gather: waits for the peers' chunk stamps first)
+//   warp 1      MMA issuer     : one elected lane issues tcgen05.mma into a double-buffered TMEM
 //                                accumulator, tcgen05.commit frees smem stages / publishes tiles
 //   warps 2..5  epilogue       : tcgen05.ld -> convert -> smem staging -> coalesced 16 B stores
 //                                to local memory, to a peer's staging slab (NVLink P2P) or to
 //                                every rank's output (P2P or multimem.st); owner tiles fold the
 //                                peers' partials into the fp32 / int32 accumulator first
-//   warps 6..7  communication  : all-gather only: push this rank's A shard to the peers
+//   warp 6      TMA producer B : K-slices of B into the same ring (one warp cannot issue both
+//                                operands' copies fast enough)
+//   warp 7      communication  : all-gather only: push this rank's A shard to the peers
 //
 // The collective is expressed inside the tile loop (see sched.h for the visiting order), so
 // transfers overlap the tensor-core work tile by tile and no NCCL call is involved.
@@ -213,7 +216,7 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
-      ptx::mbar_init(&tail->full[s], 1);
+      ptx::mbar_init(&tail->full[s], 2);   // A-producer warp + B-producer warp
       ptx::mbar_init(&tail->empty[s], 1);
     }
     for (int b = 0; b < 2; ++b) {
@@ -255,31 +258,57 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
     const bool tr = (p.trace != nullptr) && lane == 0;
     unsigned long long c_wait = 0, c_issue = 0;
     Tick tick(tr);
+    bool pre_ok = false, pre_valid = false;   // all-gather: stamps of the next tile sampled early
+    int pre_tile = -1;
     for (int t = worker; ok && t < sched.total_tiles; t += num_workers) {
       const TileInfo ti = get_tile(sched, t);
       const CUtensorMap* tma = &p.tm_a;
       int a_row = ti.m0 + sub * kBM;
-      const int b_col = ti.n0 + sub * b_cols_cta;
       if (p.mode == MODE_AG && p.W > 1) {
         if (ti.seg == p.rank) {
           a_row = ti.mi * sched.BM + sub * kBM;  // row inside the local shard
         } else {
-          // wait until every K-slice of this row chunk of source `seg` has landed here
+          // Every K-slice of this row chunk of source `seg` must have landed here. The stamps
+          // were sampled (relaxed, non-blocking) while the previous tile was streaming; only
+          // if that sample was too early does the warp fall back to a blocking poll.
           const uint32_t* fl = p.gflags[p.rank];
-          for (int s = lane; ok && s < p.gp.n_slices; s += 32) {
-            uint32_t seen = 0;
-            const int64_t idx = gather_flag_index(p.gp, ti.seg, ti.mi, s);
-            if (!wait_stamp(fl + idx, epoch, p.timeout_ns, abort_flag, &seen)) {
-              report_status(p, STATUS_TIMEOUT_GATHER, static_cast<uint32_t>(idx), epoch, seen,
-                            static_cast<uint32_t>(ti.seg));
-              *abort_flag = 1;
-              ok = false;
+          bool ready = pre_valid && pre_tile == t && __all_sync(0xffffffffu, pre_ok);
+          if (!ready) {
+            for (int s = lane; ok && s < p.gp.n_slices; s += 32) {
+              uint32_t seen = 0;
+              const int64_t idx = gather_flag_index(p.gp, ti.seg, ti.mi, s);
+              if (!wait_stamp(fl + idx, epoch, p.timeout_ns, abort_flag, &seen)) {
+                report_status(p, STATUS_TIMEOUT_GATHER, static_cast<uint32_t>(idx), epoch, seen,
+                              static_cast<uint32_t>(ti.seg));
+                *abort_flag = 1;
+                ok = false;
+              }
             }
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+          } else {
+            ptx::fence_acq_rel_sys();   // relaxed sample + fence = acquire
+            __syncwarp();
           }
-          ok = __all_sync(0xffffffffu, ok);
-          if (!ok) break;
           ptx::fence_proxy_async();  // peer-written rows are about to be read by TMA
           tma = &p.tm_a_gath[parity];
+        }
+        // sample the stamps of the next remote tile now; the answer is needed one tile later
+        pre_valid = false;
+        const int tn = t + num_workers;
+        if (tn < sched.total_tiles) {
+          const TileInfo tin = get_tile(sched, tn);
+          if (tin.seg != p.rank) {
+            const uint32_t* fl = p.gflags[p.rank];
+            bool okl = true;
+            for (int s = lane; s < p.gp.n_slices; s += 32) {
+              const uint32_t v = ptx::ld_relaxed_sys_u32(fl + gather_flag_index(p.gp, tin.seg, tin.mi, s));
+              okl = okl && (static_cast<int32_t>(v - epoch) >= 0);
+            }
+            pre_ok = okl;
+            pre_valid = true;
+            pre_tile = tn;
+          }
         }
       }
       for (int kb = 0; kb < num_kb; ++kb) {
@@ -297,11 +326,10 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
         }
         if (ptx::elect_one()) {
           uint8_t* sa = smem + stage * kStageBytes;
-          uint8_t* sb = sa + kABytes;
           const int k0 = kb * p.bk;
           const int per_box = 128 / p.elt_bytes_a;
           if (!CTA2) {
-            ptx::mbar_expect_tx(&tail->full[stage], kABytes + b_stage_bytes);
+            ptx::mbar_expect_tx(&tail->full[stage], kABytes);
             if (!p.a_mn_major) {
               ptx::tma_load_2d(sa, tma, &tail->full[stage], k0, a_row);
             } else if (p.a_3d) {
@@ -312,20 +340,11 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
                 ptx::tma_load_2d(sa + j * (p.bk * 128), tma, &tail->full[stage],
                                  a_row + j * per_box, k0);
             }
-            if (!p.b_mn_major) {
-              ptx::tma_load_2d(sb, &p.tm_b, &tail->full[stage], k0, b_col);
-            } else if (p.b_3d) {
-              ptx::tma_load_3d(sb, &p.tm_b, &tail->full[stage], 0, k0, b_col / per_box);
-            } else {
-              for (int j = 0; j < b_cols_cta / per_box; ++j)
-                ptx::tma_load_2d(sb + j * (p.bk * 128), &p.tm_b, &tail->full[stage],
-                                 b_col + j * per_box, k0);
-            }
           } else {
             // Both CTAs' copies are credited to the leader's barrier; only the leader arms it,
             // with the bytes of the whole pair.
             const uint32_t bar = ptx::map_to_cta(ptx::smem_u32(&tail->full[stage]), 0u);
-            if (leader) ptx::mbar_expect_tx(&tail->full[stage], 2u * (kABytes + b_stage_bytes));
+            if (leader) ptx::mbar_expect_tx(&tail->full[stage], 2u * kABytes);
             if (!p.a_mn_major) {
               ptx::tma_load_2d_pair(sa, tma, bar, k0, a_row);
             } else if (p.a_3d) {
@@ -333,15 +352,6 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
             } else {
               for (int j = 0; j < kBM / per_box; ++j)
                 ptx::tma_load_2d_pair(sa + j * (p.bk * 128), tma, bar, a_row + j * per_box, k0);
-            }
-            if (!p.b_mn_major) {
-              ptx::tma_load_2d_pair(sb, &p.tm_b, bar, k0, b_col);
-            } else if (p.b_3d) {
-              ptx::tma_load_3d_pair(sb, &p.tm_b, bar, 0, k0, b_col / per_box);
-            } else {
-              for (int j = 0; j < b_cols_cta / per_box; ++j)
-                ptx::tma_load_2d_pair(sb + j * (p.bk * 128), &p.tm_b, bar, b_col + j * per_box,
-                                      k0);
             }
           }
         }
@@ -755,13 +765,63 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
         }
       }
     }
+  } else if (warp == 2 + kEpiWarps) {
+    // =============================== TMA producer for B ===============================
+    // Operand loading is split over two warps (this one and warp 0) because one warp cannot
+    // issue both operands' copies fast enough to keep the tensor core fed.
+    int stage = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    for (int t = worker; ok && t < sched.total_tiles; t += num_workers) {
+      const TileInfo ti = get_tile(sched, t);
+      const int b_col = ti.n0 + sub * b_cols_cta;
+      for (int kb = 0; kb < num_kb; ++kb) {
+        if (!ptx::mbar_wait(&tail->empty[stage], phase ^ 1u, p.timeout_ns, abort_flag)) {
+          if (lane == 0) {
+            report_status(p, STATUS_TIMEOUT_PIPELINE, 4u, static_cast<uint32_t>(t), static_cast<uint32_t>(kb), 0u);
+            *abort_flag = 1;
+          }
+          ok = false;
+          break;
+        }
+        if (ptx::elect_one()) {
+          uint8_t* sb = smem + stage * kStageBytes + kABytes;
+          const int k0 = kb * p.bk;
+          const int per_box = 128 / p.elt_bytes_a;
+          if (!CTA2) {
+            ptx::mbar_expect_tx(&tail->full[stage], b_stage_bytes);
+            if (!p.b_mn_major) {
+              ptx::tma_load_2d(sb, &p.tm_b, &tail->full[stage], k0, b_col);
+            } else if (p.b_3d) {
+              ptx::tma_load_3d(sb, &p.tm_b, &tail->full[stage], 0, k0, b_col / per_box);
+            } else {
+              for (int j = 0; j < b_cols_cta / per_box; ++j)
+                ptx::tma_load_2d(sb + j * (p.bk * 128), &p.tm_b, &tail->full[stage], b_col + j * per_box, k0);
+            }
+          } else {
+            const uint32_t bar = ptx::map_to_cta(ptx::smem_u32(&tail->full[stage]), 0u);
+            if (leader) ptx::mbar_expect_tx(&tail->full[stage], 2u * b_stage_bytes);
+            if (!p.b_mn_major) {
+              ptx::tma_load_2d_pair(sb, &p.tm_b, bar, k0, b_col);
+            } else if (p.b_3d) {
+              ptx::tma_load_3d_pair(sb, &p.tm_b, bar, 0, k0, b_col / per_box);
+            } else {
+              for (int j = 0; j < b_cols_cta / per_box; ++j)
+                ptx::tma_load_2d_pair(sb + j * (p.bk * 128), &p.tm_b, bar, b_col + j * per_box, k0);
+            }
+          }
+        }
+        __syncwarp();
+        if (++stage == kStages) { stage = 0; phase ^= 1u; }
+      }
+    }
   } else {
-    // ======================= communication warps (all-gather) =======================
+    // ======================= communication warp (all-gather) =======================
     // Push this rank's A shard into every rank's gathered buffer in units of
     // chunk_rows x 512 B, peer-major: the peer that consumes the shard first is served first.
     if (fused && p.mode == MODE_AG) {
-      const int cw = warp - (2 + kEpiWarps);
-      const int ncw = (kThreads / 32) - (2 + kEpiWarps);
+      const int cw = 0;
+      const int ncw = 1;
       const GatherPlan& gp = p.gp;
       const int units_per_peer = gp.n_chunks * gp.n_slices;
       const int64_t total_units = static_cast<int64_t>(p.W) * units_per_peer;

@@ -43,10 +43,11 @@ struct TileSched {
   int tiles_per_seg;     // seg_mt * seg_nt
   int total_tiles;       // W * tiles_per_seg
   // Rounds: every segment's tiles are cut into `rounds` groups (along rows for a row split,
-  // along columns for a column split) and the W segments are visited once per round. The
-  // owner's tiles of round i are reduced / broadcast while round i+1 is being computed, so
-  // only the last round's owner work is exposed (the reference's "comm interval" idea,
-  // include/catcoc/dgemm/kernel/matmul_allreduce.hpp:116-133, without its global barriers).
+  // along columns for a column split). Per round the W-1 remote segments are visited first;
+  // the own segment follows one round late (see get_tile), so only the last round's owner
+  // work is exposed. This is the reference's "comm interval" idea
+  // (include/catcoc/dgemm/kernel/matmul_allreduce.hpp:116-133) without its global barriers.
+  // Rounds apply to schedules whose own segment comes last (first_seg = rank + 1).
   int rounds;
   int round_len;         // tiles along the cut dimension per round (last round may be shorter)
 };
@@ -115,17 +116,44 @@ CATCOC_HD TileInfo get_tile(const TileSched& s, int t) {
     ti.seg = (s.first_seg + phase) % s.W;
     seg_tile_coord(s, i, &ti.mi, &ti.ni);
   } else {
+    // Lagged rounds. Block order (W-1 "remote" segments per round, own segment one round late):
+    //   remote(0) | remote(1) own(0) | remote(2) own(1) | ... | remote(R-1) own(R-2) | own(R-1)
+    // The own segment is the LAST of the rotation (first_seg + W - 1): its partial tiles were
+    // pushed by the peers a whole round earlier, so the owner never waits for them, and its
+    // heavy epilogue (reduce, broadcast) overlaps the next round's tensor-core work.
     const int other = (s.seg_dim == SEG_ROWS) ? s.seg_nt : s.seg_mt;   // tiles along the uncut dim
-    const int full_round_tiles = s.round_len * other * s.W;
-    round = t / full_round_tiles;
     const int cut = (s.seg_dim == SEG_ROWS) ? s.seg_mt : s.seg_nt;
-    const int this_len = imin(s.round_len, cut - round * s.round_len);   // last round may be short
+    const int full = s.round_len * other;                               // tiles of one segment in a full round
+    const int last_len = cut - (s.rounds - 1) * s.round_len;
+    int rem = t;
+    bool own_block = false;
+    for (int blk = 0;; ++blk) {
+      // blk even: remote(blk/2) ; blk odd: own((blk-1)/2 ... lagging) ; final block own(R-1)
+      const bool is_remote = (blk < 2 * s.rounds - 1) ? ((blk == 0) || (blk & 1)) : false;
+      int rnd;
+      if (blk == 0) rnd = 0;
+      else if (blk < 2 * s.rounds - 1) rnd = (blk & 1) ? (blk + 1) / 2 : blk / 2 - 1;
+      else rnd = s.rounds - 1;
+      const int len = (rnd == s.rounds - 1) ? last_len : s.round_len;
+      const int n = (is_remote ? (s.W - 1) : 1) * len * other;
+      if (rem < n || blk >= 2 * s.rounds - 1) {
+        round = rnd;
+        own_block = !is_remote;
+        break;
+      }
+      rem -= n;
+      (void)full;
+    }
+    const int this_len = (round == s.rounds - 1) ? last_len : s.round_len;
     const int per_phase = this_len * other;
-    const int r = t - round * full_round_tiles;
-    phase = r / per_phase;
-    i = r - phase * per_phase;
+    if (own_block) {
+      phase = s.W - 1;
+      i = rem;
+    } else {
+      phase = rem / per_phase;
+      i = rem - phase * per_phase;
+    }
     ti.seg = (s.first_seg + phase) % s.W;
-    // swizzled walk inside the round's slice: a sub-grid of this_len x other tiles
     if (s.seg_dim == SEG_ROWS) {
       grid_tile_coord(this_len, s.seg_nt, s.swizzle, i, &ti.mi, &ti.ni);
       ti.mi += round * s.round_len;

@@ -120,12 +120,21 @@ def test_rounds_keep_coverage_and_ids(M, Nn, W, seg_dim, rounds):
     assert seen == base          # same tiles with the same ids and geometry, only the order differs
 
 
-def test_rounds_interleave_the_owner_segment():
-    W, rank = 8, 3
-    segs = [t.seg for t in tiles_rounds(8192, 8192, 128, 256, W, 0, (rank + 1) % W, 8, 4)]
-    # runs of equal segment: W per round, own segment closes every round
-    runs = [s for i, s in enumerate(segs) if i == 0 or segs[i - 1] != s]
-    assert len(runs) == 4 * W
-    assert runs[W - 1::W] == [rank] * 4
-    own_positions = [i for i, s in enumerate(segs) if s == rank]
-    assert own_positions[0] < len(segs) // 3        # owner work starts early instead of piling up at the end
+def test_owner_tiles_lag_one_round_behind_the_remote_tiles():
+    W, rank, R = 8, 3, 4
+    ts = tiles_rounds(8192, 8192, 128, 256, W, 0, (rank + 1) % W, 8, R)
+    round_len = (8192 // W // 128) // R
+    pos = {}
+    for i, t in enumerate(ts):
+        key = ("own" if t.seg == rank else "remote", t.mi // round_len)
+        lo, hi = pos.get(key, (i, i))
+        pos[key] = (min(lo, i), max(hi, i))
+    for r in range(R - 1):
+        assert pos[("remote", r + 1)][1] < pos[("own", r)][0]       # own(r) only after remote(r+1) is done
+        if r + 2 < R:
+            assert pos[("own", r)][1] < pos[("remote", r + 2)][0]   # ... and before remote(r+2) starts
+    assert pos[("own", R - 1)][1] == len(ts) - 1                     # the last round's owner tiles close the kernel
+    assert pos[("own", 0)][0] < len(ts) // 2                         # owner work starts early, not piled up at the end
+    # within a round the remote segments still rotate starting at rank + 1
+    first_round = [t.seg for t in ts[:pos[("remote", 0)][1] + 1]]
+    assert list(dict.fromkeys(first_round)) == [(rank + 1 + p) % W for p in range(W - 1)]
