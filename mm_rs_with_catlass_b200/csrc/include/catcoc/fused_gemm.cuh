@@ -395,6 +395,7 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
       const bool tr = (p.trace != nullptr) && lane == 0;
       unsigned long long c_full = 0, c_acc = 0, c_issue = 0;
       Tick tick(tr);
+      bool probed = false;
       for (int t = worker; ok && t < sched.total_tiles; t += num_workers) {
         tick.lap(c_issue);
         const bool got_acc = ptx::mbar_wait(&tail->acc_empty[acc], acc_phase ^ 1u, p.timeout_ns, abort_flag);
@@ -410,7 +411,9 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
         const uint32_t tmem_d = tmem_base + static_cast<uint32_t>(acc * kMaxBN);
         for (int kb = 0; kb < num_kb; ++kb) {
           tick.lap(c_issue);
-          const bool got_full = ptx::mbar_wait(&tail->full[stage], phase, p.timeout_ns, abort_flag);
+          // `probed` is the answer of a non-blocking probe issued before the previous stage's
+          // MMAs: its latency was hidden behind their issue, so a ready stage costs nothing here
+          const bool got_full = probed || ptx::mbar_wait(&tail->full[stage], phase, p.timeout_ns, abort_flag);
           tick.lap(c_full);
           if (!got_full) {
             if (lane == 0) {
@@ -426,6 +429,11 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
           const int nk = min(k_per_stage, ceil_div(K - kb * bk, umma_k));
           const uint64_t da = da0 + static_cast<uint64_t>(stage * stage_inc);
           const uint64_t db = db0 + static_cast<uint64_t>(stage * stage_inc);
+          {
+            const int ns = (stage + 1 == kStages) ? 0 : stage + 1;
+            const uint32_t np = (stage + 1 == kStages) ? (phase ^ 1u) : phase;
+            probed = ptx::mbar_test_wait(&tail->full[ns], np);
+          }
           if (ptx::elect_one()) {
 #pragma unroll
             for (int k = 0; k < 4; ++k) {

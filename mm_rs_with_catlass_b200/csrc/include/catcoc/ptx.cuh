@@ -72,6 +72,21 @@ CATCOC_DEVICE bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 
+// Non-blocking probe of a phase (never suspends the thread).
+CATCOC_DEVICE bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t"
+      "}\n"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
 // Bounded wait on an mbarrier phase. `abort_flag` is a shared-memory word any role may set to
 // make every other role give up quickly. Returns false on time-out or abort.
 CATCOC_DEVICE bool mbar_wait(uint64_t* bar, uint32_t parity, uint64_t timeout_ns,
