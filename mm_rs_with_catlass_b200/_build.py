@@ -36,6 +36,11 @@ NVCC_FLAGS = [
 ]
 
 
+def _extra_flags() -> list[str]:
+    """Extra nvcc flags for experiments (``CATCOC_NVCC_EXTRA="-DFOO=1 -DBAR"``); part of the digest."""
+    return os.environ.get("CATCOC_NVCC_EXTRA", "").split()
+
+
 def _nvcc() -> str:
     cand = os.environ.get("CATCOC_NVCC") or shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
     if not Path(cand).exists():
@@ -54,7 +59,7 @@ def source_digest() -> str:
     for f in files:
         h.update(str(f.relative_to(CSRC)).encode())
         h.update(f.read_bytes())
-    h.update(" ".join(NVCC_FLAGS).encode())
+    h.update(" ".join(NVCC_FLAGS + _extra_flags()).encode())
     return h.hexdigest()
 
 
@@ -67,7 +72,7 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     if not force and is_current():
         return LIB_PATH
     LIB_DIR.mkdir(exist_ok=True)
-    cmd = [_nvcc(), *NVCC_FLAGS, "-I", str(CSRC / "include")]
+    cmd = [_nvcc(), *NVCC_FLAGS, *_extra_flags(), "-I", str(CSRC / "include")]
     if verbose:
         cmd += ["-Xptxas", "-v"]
     cmd += [str(s) for s in _existing_sources()]

@@ -49,10 +49,22 @@ constexpr int kMaxStages = 6;
 //            128 rows of A and HALF of the B tile; the pair's leader issues one MMA that reads
 //            both halves, so operand traffic into shared memory per FLOP halves
 //                                                                     (32 KiB / stage, 6 stages)
+// A pipeline stage holds kKPS consecutive K-blocks (each: A block + B block). Handing a stage
+// from the producers to the MMA warp and back costs a few hundred cycles of barrier / commit
+// latency that does not depend on how many MMAs the stage feeds, so the pair flavour (32 KiB per
+// K-block) packs two K-blocks per stage: 8 MMAs per hand-off instead of 4, same bytes in flight.
+#ifndef CATCOC_KPS_PAIR
+#define CATCOC_KPS_PAIR 2
+#endif
+#ifndef CATCOC_KPS_SINGLE
+#define CATCOC_KPS_SINGLE 1
+#endif
 template <bool CTA2> struct Geo {
-  static constexpr int kStages = CTA2 ? 6 : 4;
+  static constexpr int kKPS = CTA2 ? CATCOC_KPS_PAIR : CATCOC_KPS_SINGLE;
   static constexpr int kBBytesMax = (CTA2 ? kMaxBN / 2 : kMaxBN) * 128;
-  static constexpr int kStageBytes = kABytes + kBBytesMax;
+  static constexpr int kSubBytes = kABytes + kBBytesMax;        // one K-block: A then B
+  static constexpr int kStageBytes = kKPS * kSubBytes;
+  static constexpr int kStages = (192 * 1024) / kStageBytes;
   static constexpr int kSmemBytes =
       kStages * kStageBytes + kEpiWarps * kEpiStageBytes + 256 /*barriers*/ + 1024 /*align slack*/;
 };
@@ -192,6 +204,8 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
   using G = Geo<CTA2>;
   constexpr int kStages = G::kStages;
   constexpr int kStageBytes = G::kStageBytes;
+  constexpr int kSubBytes = G::kSubBytes;
+  constexpr int kKPS = G::kKPS;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
@@ -203,7 +217,7 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
   const int lane = threadIdx.x & 31;
   const TileSched& sched = p.sched;
   const int BN = sched.BN;
-  const int num_kb = ceil_div(p.K, p.bk);
+  const int num_kb = ceil_div(p.K, p.bk * kKPS);   // pipeline stages per tile
   const bool fused = (p.mode != MODE_LOCAL) && (p.W > 1);
   // Pair flavour: `sub` is this CTA's half of the 256-row tile, work is dealt out per pair.
   const int sub = CTA2 ? static_cast<int>(ptx::cluster_ctarank()) : 0;
@@ -325,33 +339,36 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
           break;
         }
         if (ptx::elect_one()) {
-          uint8_t* sa = smem + stage * kStageBytes;
-          const int k0 = kb * p.bk;
           const int per_box = 128 / p.elt_bytes_a;
-          if (!CTA2) {
-            ptx::mbar_expect_tx(&tail->full[stage], kABytes);
-            if (!p.a_mn_major) {
-              ptx::tma_load_2d(sa, tma, &tail->full[stage], k0, a_row);
-            } else if (p.a_3d) {
-              ptx::tma_load_3d(sa, tma, &tail->full[stage], 0, k0, a_row / per_box);
+          const uint32_t bar = CTA2 ? ptx::map_to_cta(ptx::smem_u32(&tail->full[stage]), 0u) : 0u;
+          // Single flavour: this warp arms its own barrier with its bytes. Pair flavour: both
+          // CTAs' copies are credited to the leader's barrier and only the leader arms it, with
+          // the bytes of the whole pair. K-blocks past the end of K are fetched as zeros.
+          if (!CTA2) ptx::mbar_expect_tx(&tail->full[stage], kKPS * kABytes);
+          else if (leader) ptx::mbar_expect_tx(&tail->full[stage], 2u * kKPS * kABytes);
+#pragma unroll
+          for (int j = 0; j < kKPS; ++j) {
+            uint8_t* sa = smem + stage * kStageBytes + j * kSubBytes;
+            const int k0 = (kb * kKPS + j) * p.bk;
+            if (!CTA2) {
+              if (!p.a_mn_major) {
+                ptx::tma_load_2d(sa, tma, &tail->full[stage], k0, a_row);
+              } else if (p.a_3d) {
+                ptx::tma_load_3d(sa, tma, &tail->full[stage], 0, k0, a_row / per_box);
+              } else {
+                // storage [K, M]: boxes of 128 B along M x bk rows of K
+                for (int b = 0; b < kBM / per_box; ++b)
+                  ptx::tma_load_2d(sa + b * (p.bk * 128), tma, &tail->full[stage], a_row + b * per_box, k0);
+              }
             } else {
-              // storage [K, M]: boxes of 128 B along M x bk rows of K
-              for (int j = 0; j < kBM / per_box; ++j)
-                ptx::tma_load_2d(sa + j * (p.bk * 128), tma, &tail->full[stage],
-                                 a_row + j * per_box, k0);
-            }
-          } else {
-            // Both CTAs' copies are credited to the leader's barrier; only the leader arms it,
-            // with the bytes of the whole pair.
-            const uint32_t bar = ptx::map_to_cta(ptx::smem_u32(&tail->full[stage]), 0u);
-            if (leader) ptx::mbar_expect_tx(&tail->full[stage], 2u * kABytes);
-            if (!p.a_mn_major) {
-              ptx::tma_load_2d_pair(sa, tma, bar, k0, a_row);
-            } else if (p.a_3d) {
-              ptx::tma_load_3d_pair(sa, tma, bar, 0, k0, a_row / per_box);
-            } else {
-              for (int j = 0; j < kBM / per_box; ++j)
-                ptx::tma_load_2d_pair(sa + j * (p.bk * 128), tma, bar, a_row + j * per_box, k0);
+              if (!p.a_mn_major) {
+                ptx::tma_load_2d_pair(sa, tma, bar, k0, a_row);
+              } else if (p.a_3d) {
+                ptx::tma_load_3d_pair(sa, tma, bar, 0, k0, a_row / per_box);
+              } else {
+                for (int b = 0; b < kBM / per_box; ++b)
+                  ptx::tma_load_2d_pair(sa + b * (p.bk * 128), tma, bar, a_row + b * per_box, k0);
+              }
             }
           }
         }
@@ -390,7 +407,6 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
       const uint32_t idesc = p.idesc;
       const int k_per_stage = p.bk / p.umma_k;   // 4
       const int umma_k = p.umma_k;
-      const int bk = p.bk;
       const int K = p.K;
       const bool tr = (p.trace != nullptr) && lane == 0;
       unsigned long long c_full = 0, c_acc = 0, c_issue = 0;
@@ -426,7 +442,8 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
           }
           ptx::tcgen05_fence_after();
           // K tail: TMA zero-fills beyond K, MMAs entirely out of range are skipped.
-          const int nk = min(k_per_stage, ceil_div(K - kb * bk, umma_k));
+          const int k_mmas = ceil_div(K, umma_k);                    // MMAs along K for a whole tile
+          const int k_first = kb * kKPS * k_per_stage;               // index of this stage's first MMA
           const uint64_t da = da0 + static_cast<uint64_t>(stage * stage_inc);
           const uint64_t db = db0 + static_cast<uint64_t>(stage * stage_inc);
           {
@@ -436,11 +453,12 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
           }
           if (ptx::elect_one()) {
 #pragma unroll
-            for (int k = 0; k < 4; ++k) {
-              if (k < nk) {
-                const uint64_t dak = da + static_cast<uint64_t>(k * a_kinc);
-                const uint64_t dbk = db + static_cast<uint64_t>(k * b_kinc);
-                const uint32_t accum = (kb | k) != 0 ? 1u : 0u;
+            for (int kk = 0; kk < 4 * kKPS; ++kk) {
+              const int j = kk >> 2, k = kk & 3;
+              if (k_first + kk < k_mmas) {
+                const uint64_t dak = da + static_cast<uint64_t>(j * (kSubBytes >> 4) + k * a_kinc);
+                const uint64_t dbk = db + static_cast<uint64_t>(j * (kSubBytes >> 4) + k * b_kinc);
+                const uint32_t accum = (k_first + kk) != 0 ? 1u : 0u;
                 if (CTA2) {
                   if (KIND == KIND_F16) ptx::umma_f16_pair(tmem_d, dak, dbk, idesc, accum);
                   else if (KIND == KIND_I8) ptx::umma_i8_pair(tmem_d, dak, dbk, idesc, accum);
@@ -793,29 +811,32 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
           break;
         }
         if (ptx::elect_one()) {
-          uint8_t* sb = smem + stage * kStageBytes + kABytes;
-          const int k0 = kb * p.bk;
           const int per_box = 128 / p.elt_bytes_a;
-          if (!CTA2) {
-            ptx::mbar_expect_tx(&tail->full[stage], b_stage_bytes);
-            if (!p.b_mn_major) {
-              ptx::tma_load_2d(sb, &p.tm_b, &tail->full[stage], k0, b_col);
-            } else if (p.b_3d) {
-              ptx::tma_load_3d(sb, &p.tm_b, &tail->full[stage], 0, k0, b_col / per_box);
+          const uint32_t bar = CTA2 ? ptx::map_to_cta(ptx::smem_u32(&tail->full[stage]), 0u) : 0u;
+          if (!CTA2) ptx::mbar_expect_tx(&tail->full[stage], kKPS * b_stage_bytes);
+          else if (leader) ptx::mbar_expect_tx(&tail->full[stage], 2u * kKPS * b_stage_bytes);
+#pragma unroll
+          for (int j = 0; j < kKPS; ++j) {
+            uint8_t* sb = smem + stage * kStageBytes + j * kSubBytes + kABytes;
+            const int k0 = (kb * kKPS + j) * p.bk;
+            if (!CTA2) {
+              if (!p.b_mn_major) {
+                ptx::tma_load_2d(sb, &p.tm_b, &tail->full[stage], k0, b_col);
+              } else if (p.b_3d) {
+                ptx::tma_load_3d(sb, &p.tm_b, &tail->full[stage], 0, k0, b_col / per_box);
+              } else {
+                for (int b = 0; b < b_cols_cta / per_box; ++b)
+                  ptx::tma_load_2d(sb + b * (p.bk * 128), &p.tm_b, &tail->full[stage], b_col + b * per_box, k0);
+              }
             } else {
-              for (int j = 0; j < b_cols_cta / per_box; ++j)
-                ptx::tma_load_2d(sb + j * (p.bk * 128), &p.tm_b, &tail->full[stage], b_col + j * per_box, k0);
-            }
-          } else {
-            const uint32_t bar = ptx::map_to_cta(ptx::smem_u32(&tail->full[stage]), 0u);
-            if (leader) ptx::mbar_expect_tx(&tail->full[stage], 2u * b_stage_bytes);
-            if (!p.b_mn_major) {
-              ptx::tma_load_2d_pair(sb, &p.tm_b, bar, k0, b_col);
-            } else if (p.b_3d) {
-              ptx::tma_load_3d_pair(sb, &p.tm_b, bar, 0, k0, b_col / per_box);
-            } else {
-              for (int j = 0; j < b_cols_cta / per_box; ++j)
-                ptx::tma_load_2d_pair(sb + j * (p.bk * 128), &p.tm_b, bar, b_col + j * per_box, k0);
+              if (!p.b_mn_major) {
+                ptx::tma_load_2d_pair(sb, &p.tm_b, bar, k0, b_col);
+              } else if (p.b_3d) {
+                ptx::tma_load_3d_pair(sb, &p.tm_b, bar, 0, k0, b_col / per_box);
+              } else {
+                for (int b = 0; b < b_cols_cta / per_box; ++b)
+                  ptx::tma_load_2d_pair(sb + b * (p.bk * 128), &p.tm_b, bar, b_col + b * per_box, k0);
+              }
             }
           }
         }

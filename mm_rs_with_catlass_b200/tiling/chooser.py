@@ -45,9 +45,9 @@ def heuristic(op: str, m: int, n: int, k: int, world: int, dtype: torch.dtype) -
     forced = os.environ.get("CATCOC_CTA_PAIR")
     if forced in ("1", "2"):
         pair = int(forced)
-    elif (op in ("matmul", "matmul_reduce_scatter") and bn >= 128 and seg_rows >= 256 and seg_rows % 256 == 0
+    elif (bn >= 128 and seg_rows >= 256 and seg_rows % 256 == 0
           and (rows // 256) * math.ceil(n / bn) >= _NUM_SMS // 2):
-        pair = 2   # measured: pairs help the plain GEMM and the reduce-scatter, not all-gather / all-reduce
+        pair = 2   # measured: 2-CTA tiles with two K-blocks per stage run within a few % of cuBLAS
     if pair == 2 and dtype == torch.int8:
         bn = 256  # each CTA of a pair loads bn / 2 columns, and 8-bit [K, N] needs 128 of them
     if pair == 2 and bn < 128:
