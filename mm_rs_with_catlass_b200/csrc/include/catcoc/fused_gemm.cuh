@@ -872,19 +872,20 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
         uint8_t* dstp = p.gathered[peer] + static_cast<int64_t>(parity) * p.gathered_parity_bytes +
                         (static_cast<int64_t>(p.rank) * gp.m + r0) * p.gathered_pitch + cb;
         if (col_ok) {
-          for (int r = 0; r < nrows; r += 8) {
-            uint4 buf[8];
+          // 16 rows (8 KiB per warp) in flight per round trip: the copy is latency bound
+          for (int r = 0; r < nrows; r += 16) {
+            uint4 buf[16];
 #pragma unroll
-            for (int i = 0; i < 8; ++i)
+            for (int i = 0; i < 16; ++i)
               if (r + i < nrows)
                 buf[i] = ptx::ld_global_nc_v4(src + static_cast<int64_t>(r + i) * p.a_local_pitch);
 #pragma unroll
-            for (int i = 0; i < 8; ++i)
+            for (int i = 0; i < 16; ++i)
               if (r + i < nrows)
                 ptx::st_global_v4(dstp + static_cast<int64_t>(r + i) * p.gathered_pitch, buf[i]);
           }
         }
-        ptx::fence_acq_rel_sys();
+        // all lanes' stores happen-before lane 0's release through the warp barrier (cumulative)
         __syncwarp();
         if (lane == 0 && !p.withhold_signals)
           ptx::st_release_sys_u32(p.gflags[peer] + gather_flag_index(gp, p.rank, chunk, slice),

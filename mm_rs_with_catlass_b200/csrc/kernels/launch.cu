@@ -161,7 +161,7 @@ static TileSched build_sched(const CatcocOpArgs& a, int bm, int bn, int seg_dim)
   if (fused) first = (a.mode == CATCOC_MODE_AG) ? a.rank : (a.rank + 1) % W;
   const int swz = a.tiling.swizzle > 0 ? a.tiling.swizzle : 8;
   int rounds = 1;
-  if (fused && (a.mode == CATCOC_MODE_RS || a.mode == CATCOC_MODE_AR)) rounds = a.tiling.rounds > 0 ? a.tiling.rounds : 4;
+  if (fused && (a.mode == CATCOC_MODE_RS || a.mode == CATCOC_MODE_AR)) rounds = a.tiling.rounds > 0 ? a.tiling.rounds : 1;
   return make_sched(a.M, a.N, bm, bn, W, seg_dim, first, swz, rounds);
 }
 

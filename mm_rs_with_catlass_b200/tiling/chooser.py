@@ -52,7 +52,13 @@ def heuristic(op: str, m: int, n: int, k: int, world: int, dtype: torch.dtype) -
         bn = 256  # each CTA of a pair loads bn / 2 columns, and 8-bit [K, N] needs 128 of them
     if pair == 2 and bn < 128:
         pair = 1
-    return TilingConfig(bn=bn, swizzle=swizzle, cta_pair=pair)
+    # measured at W = 8: the int32 partials of the quantised op are link bound, lagged owner
+    # rounds overlap its owner-side reduce; the all-reduce gains from the NVLS broadcast (the op
+    # layer drops the flag when the heap has no multicast alias) and from column ownership
+    rounds = 4 if (op == "quant_matmul_reduce_scatter" and world > 1 and rows >= 2048) else 0
+    if op == "matmul_allreduce" and world > 1:
+        return TilingConfig(bn=bn, swizzle=swizzle, cta_pair=1, use_multicast=True, seg_dim=1 if n % (world * 8) == 0 else -1)
+    return TilingConfig(bn=bn, swizzle=swizzle, cta_pair=pair, rounds=rounds)
 
 
 def choose(op: str, m: int, n: int, k: int, world: int, dtype: torch.dtype,

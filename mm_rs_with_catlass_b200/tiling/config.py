@@ -34,7 +34,7 @@ class TilingConfig:
     num_ctas: int = 0      # persistent CTAs (0 = one per SM)
     seg_dim: int = -1      # all-reduce ownership split: 0 rows, 1 cols, -1 auto
     use_multicast: bool = False  # all-reduce broadcast through the NVLS alias
-    rounds: int = 0        # reduce-scatter / all-reduce: owner tiles are spread over this many rounds (0 = 4)
+    rounds: int = 0        # reduce-scatter / all-reduce: owner tiles are spread over this many lagged rounds (0 = 1)
     fp32_partials: bool = False  # partial tiles cross NVLink in fp32 instead of the operand dtype (2x bytes, no rounding)
     cta_pair: int = 0      # 2: 256-row tiles on 2-CTA clusters (tcgen05 cta_group::2); 1: single CTA; 0 = 1
     # --- reference-compatible fields (carried, reported, not steering the kernel) ---

@@ -26,6 +26,7 @@ BN_SPACE = (256, 128, 64)
 PAIR_SPACE = (1, 2)
 SWIZZLE_SPACE = (4, 8, 16)
 NUM_CTAS_SPACE = (0,)          # 0 = one CTA per SM
+ROUNDS_SPACE = (0,)            # 0 = the launcher's default
 NUM_SMS = 148
 
 
@@ -109,8 +110,8 @@ def infeasible_reason(p: Problem, t: TilingConfig) -> Optional[str]:
 
 
 def candidates(p: Problem, bn_space: Sequence[int] = BN_SPACE, pair_space: Sequence[int] = PAIR_SPACE,
-               swizzle_space: Sequence[int] = SWIZZLE_SPACE, num_ctas_space: Sequence[int] = NUM_CTAS_SPACE
-               ) -> List[TilingConfig]:
+               swizzle_space: Sequence[int] = SWIZZLE_SPACE, num_ctas_space: Sequence[int] = NUM_CTAS_SPACE,
+               rounds_space: Sequence[int] = ROUNDS_SPACE) -> List[TilingConfig]:
     """Every feasible tiling of the search space for this problem, widest tiles first."""
     seg_space: Iterable[int] = (-1,)
     mc_space: Iterable[bool] = (False,)
@@ -118,9 +119,12 @@ def candidates(p: Problem, bn_space: Sequence[int] = BN_SPACE, pair_space: Seque
         seg_space = (0, 1)
         mc_space = (False, True) if p.multicast_available else (False,)
     out: List[TilingConfig] = []
-    for bn, pair, swz, nctas, seg, mc in itertools.product(bn_space, pair_space, swizzle_space, num_ctas_space,
-                                                           seg_space, mc_space):
-        t = TilingConfig(bn=bn, cta_pair=pair, swizzle=swz, num_ctas=nctas, seg_dim=seg, use_multicast=mc)
+    if p.world <= 1 or p.op in ("matmul", "allgather_matmul"):
+        rounds_space = (0,)
+    for bn, pair, swz, nctas, seg, mc, rounds in itertools.product(bn_space, pair_space, swizzle_space,
+                                                                   num_ctas_space, seg_space, mc_space, rounds_space):
+        t = TilingConfig(bn=bn, cta_pair=pair, swizzle=swz, num_ctas=nctas, seg_dim=seg, use_multicast=mc,
+                         rounds=rounds)
         if infeasible_reason(p, t) is None:
             out.append(t)
     return out

@@ -82,6 +82,10 @@ def main(argv=None) -> int:
     ap.add_argument("--start-line", type=int, default=0)
     ap.add_argument("--collect-rows", type=int, default=0)
     ap.add_argument("--heap-gb", type=float, default=6.0)
+    ap.add_argument("--bns", default="256,128,64", help="tile widths to try")
+    ap.add_argument("--pairs", default="1,2", help="1 = single CTA tiles, 2 = 2-CTA tiles")
+    ap.add_argument("--swizzles", default="4,8,16")
+    ap.add_argument("--rounds", default="0", help="owner rounds to try (0 = default)")
     args = ap.parse_args(argv)
 
     from ..parallel import shmem
@@ -99,7 +103,9 @@ def main(argv=None) -> int:
     done = TilingTable.load(args.out) if os.path.exists(args.out) else TilingTable()
     for (m, k, n, ta, tb) in read_shapes(args.shapes, args.start_line, args.collect_rows):
         prob = search.Problem(op, m, n, k, world, args.dtype, bool(ta), bool(tb), bool(ctx.mc_base), ctx.heap_bytes)
-        for t in search.candidates(prob):
+        ints = lambda txt: tuple(int(x) for x in txt.split(",") if x != "")
+        for t in search.candidates(prob, ints(args.bns), ints(args.pairs), ints(args.swizzles),
+                                   rounds_space=ints(args.rounds)):
             row = Row(op, m, k, n, ta, tb, dtype_name(dtype), world, t, float("nan"))
             if done.has(row):
                 continue
