@@ -52,6 +52,9 @@ def matmul(a: torch.Tensor, b: torch.Tensor, *, trans_a: bool = False, trans_b: 
     if a.dtype != torch.int8 and out_dtype == torch.int32:
         raise ValueError("int32 output needs int8 operands")
 
+    if tiling is None:
+        from ..tiling.chooser import choose
+        tiling = choose("matmul", m, n, k, 1, a.dtype)
     with torch.cuda.device(dev):
         oa = cm.as_operand(a, trans_a)
         ob = cm.as_operand(b, trans_b)
