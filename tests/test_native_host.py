@@ -95,3 +95,27 @@ def test_data_generators_are_rank_dependent_and_seeded():
     assert s1.min() >= 0.001 and s1.max() <= 0.02 and bias.dtype == torch.int32
     d = quant_inputs(4, 8, 16, debug=True)
     assert d[0].unique().tolist() == [1] and d[4].tolist() == list(range(1, 9))
+
+
+def test_tensor_files_roundtrip_and_checker_exit_code(tmp_path):
+    from mm_rs_with_catlass_b200.utils import io
+    g = torch.randn(16, 24)
+    for dt in (torch.bfloat16, torch.float16, torch.float32, torch.int8):
+        t = (g * 10).to(dt)
+        io.tensor_to_file(t, str(tmp_path / "t.bin"))
+        assert torch.equal(io.tensor_from_file(str(tmp_path / "t.bin"), dt, (16, 24)), t)
+    io.tensor_to_file(g.to(torch.bfloat16), str(tmp_path / "out.bin"))
+    io.tensor_to_file(g, str(tmp_path / "gold.bin"))
+    assert io.main([str(tmp_path / "out.bin"), str(tmp_path / "gold.bin"), "bf16", "16", "24", "512"]) == 0
+    bad = g.clone()
+    bad[0, 0] += 5
+    io.tensor_to_file(bad.to(torch.bfloat16), str(tmp_path / "out.bin"))
+    assert io.main([str(tmp_path / "out.bin"), str(tmp_path / "gold.bin"), "bf16", "16", "24", "512"]) == 1
+
+
+def test_shape_lists_parse():
+    from mm_rs_with_catlass_b200.tiling.tune import read_shapes
+    d = os.path.join(REPO, "mm_rs_with_catlass_b200", "tiling", "shapes")
+    ref = read_shapes(os.path.join(d, "reference_shapes.csv"))
+    assert (16384, 27392, 4096, 0, 0) in ref and (8144, 5120, 1696, 0, 1) in ref and len(ref) == 9
+    assert read_shapes(os.path.join(d, "reference_shapes.csv"), start_line=1, rows=2) == ref[1:3]
