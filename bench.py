@@ -39,7 +39,7 @@ METRIC = "fused_tp_ops_tflops"
 def parse_args():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "baseline", "reference"])
     ap.add_argument("--m", type=int, default=M_DEFAULT)
@@ -125,11 +125,13 @@ def main():
     flops_step = 3.0 * flops_one
 
     # ---- headline: K steps, device-timed, max over ranks, clocks sampled during the region ----
-    for _ in range(args.warmup):
+    # the clock sampler starts before the warm-up so that nvidia-smi is already polling when the
+    # timed region begins; only samples taken under load enter the median
+    sampler = timing.ClockSampler(gpu_index=None, period_ms=100).start() if rank == 0 else None
+    for _ in range(max(args.warmup, 3)):
         step()
     timing.sync_all(dev)
     launches0 = ctx.counters["launches"] if ours else 0
-    sampler = timing.ClockSampler(gpu_index=None).start() if rank == 0 else None
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     t_host0 = time.perf_counter()
     start.record()

@@ -217,7 +217,11 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
   const int lane = threadIdx.x & 31;
   const TileSched& sched = p.sched;
   const int BN = sched.BN;
-  const int num_kb = ceil_div(p.K, p.bk * kKPS);   // pipeline stages per tile
+  // K-blocks per stage at run time: narrow single-CTA tiles (bn <= 64, the small-M configs) leave
+  // room for two 24 KiB K-blocks in a 48 KiB stage, which halves their barrier hand-offs too.
+  const int kps = (!CTA2 && BN <= 64) ? 2 : kKPS;
+  const int sub_bytes = (kps != kKPS) ? (kABytes + BN * 128) : kSubBytes;
+  const int num_kb = ceil_div(p.K, p.bk * kps);   // pipeline stages per tile
   const bool fused = (p.mode != MODE_LOCAL) && (p.W > 1);
   // Pair flavour: `sub` is this CTA's half of the 256-row tile, work is dealt out per pair.
   const int sub = CTA2 ? static_cast<int>(ptx::cluster_ctarank()) : 0;
@@ -344,12 +348,13 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
           // Single flavour: this warp arms its own barrier with its bytes. Pair flavour: both
           // CTAs' copies are credited to the leader's barrier and only the leader arms it, with
           // the bytes of the whole pair. K-blocks past the end of K are fetched as zeros.
-          if (!CTA2) ptx::mbar_expect_tx(&tail->full[stage], kKPS * kABytes);
-          else if (leader) ptx::mbar_expect_tx(&tail->full[stage], 2u * kKPS * kABytes);
+          if (!CTA2) ptx::mbar_expect_tx(&tail->full[stage], kps * kABytes);
+          else if (leader) ptx::mbar_expect_tx(&tail->full[stage], 2u * kps * kABytes);
 #pragma unroll
-          for (int j = 0; j < kKPS; ++j) {
-            uint8_t* sa = smem + stage * kStageBytes + j * kSubBytes;
-            const int k0 = (kb * kKPS + j) * p.bk;
+          for (int j = 0; j < 2; ++j) {
+            if (j >= kps) break;
+            uint8_t* sa = smem + stage * kStageBytes + j * sub_bytes;
+            const int k0 = (kb * kps + j) * p.bk;
             if (!CTA2) {
               if (!p.a_mn_major) {
                 ptx::tma_load_2d(sa, tma, &tail->full[stage], k0, a_row);
@@ -443,7 +448,7 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
           ptx::tcgen05_fence_after();
           // K tail: TMA zero-fills beyond K, MMAs entirely out of range are skipped.
           const int k_mmas = ceil_div(K, umma_k);                    // MMAs along K for a whole tile
-          const int k_first = kb * kKPS * k_per_stage;               // index of this stage's first MMA
+          const int k_first = kb * kps * k_per_stage;                // index of this stage's first MMA
           const uint64_t da = da0 + static_cast<uint64_t>(stage * stage_inc);
           const uint64_t db = db0 + static_cast<uint64_t>(stage * stage_inc);
           {
@@ -453,11 +458,11 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
           }
           if (ptx::elect_one()) {
 #pragma unroll
-            for (int kk = 0; kk < 4 * kKPS; ++kk) {
+            for (int kk = 0; kk < 8; ++kk) {
               const int j = kk >> 2, k = kk & 3;
-              if (k_first + kk < k_mmas) {
-                const uint64_t dak = da + static_cast<uint64_t>(j * (kSubBytes >> 4) + k * a_kinc);
-                const uint64_t dbk = db + static_cast<uint64_t>(j * (kSubBytes >> 4) + k * b_kinc);
+              if (j < kps && k_first + kk < k_mmas) {
+                const uint64_t dak = da + static_cast<uint64_t>(j * (sub_bytes >> 4) + k * a_kinc);
+                const uint64_t dbk = db + static_cast<uint64_t>(j * (sub_bytes >> 4) + k * b_kinc);
                 const uint32_t accum = (k_first + kk) != 0 ? 1u : 0u;
                 if (CTA2) {
                   if (KIND == KIND_F16) ptx::umma_f16_pair(tmem_d, dak, dbk, idesc, accum);
@@ -813,12 +818,13 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
         if (ptx::elect_one()) {
           const int per_box = 128 / p.elt_bytes_a;
           const uint32_t bar = CTA2 ? ptx::map_to_cta(ptx::smem_u32(&tail->full[stage]), 0u) : 0u;
-          if (!CTA2) ptx::mbar_expect_tx(&tail->full[stage], kKPS * b_stage_bytes);
-          else if (leader) ptx::mbar_expect_tx(&tail->full[stage], 2u * kKPS * b_stage_bytes);
+          if (!CTA2) ptx::mbar_expect_tx(&tail->full[stage], kps * b_stage_bytes);
+          else if (leader) ptx::mbar_expect_tx(&tail->full[stage], 2u * kps * b_stage_bytes);
 #pragma unroll
-          for (int j = 0; j < kKPS; ++j) {
-            uint8_t* sb = smem + stage * kStageBytes + j * kSubBytes + kABytes;
-            const int k0 = (kb * kKPS + j) * p.bk;
+          for (int j = 0; j < 2; ++j) {
+            if (j >= kps) break;
+            uint8_t* sb = smem + stage * kStageBytes + j * sub_bytes + kABytes;
+            const int k0 = (kb * kps + j) * p.bk;
             if (!CTA2) {
               if (!p.b_mn_major) {
                 ptx::tma_load_2d(sb, &p.tm_b, &tail->full[stage], k0, b_col);
