@@ -20,4 +20,7 @@ from .ops.gemm import matmul  # noqa: F401
 from .ops.fused import (matmul_allreduce, allgather_matmul, matmul_reduce_scatter,  # noqa: F401
                         quant_matmul_reduce_scatter)
 
+from .ops.mx import (mxf8_matmul, mxf8_matmul_reduce_scatter, quantize_mxf8, dequantize_mxf8,  # noqa: F401
+                     pack_scales)
+
 __version__ = "0.1.0"

@@ -15,7 +15,7 @@ from . import _build
 MAX_WORLD = 8
 
 # enums mirrored from capi.h
-IN_F16, IN_BF16, IN_S8, IN_E4M3, IN_E5M2 = range(5)
+IN_F16, IN_BF16, IN_S8, IN_E4M3, IN_E5M2, IN_MXE4M3, IN_MXE5M2 = range(7)
 FMT_F16, FMT_BF16, FMT_F32, FMT_S32 = range(4)
 MODE_LOCAL, MODE_RS, MODE_AR, MODE_AG = range(4)
 
@@ -59,6 +59,7 @@ class OpArgs(C.Structure):
         ("gathered_parity_bytes", C.c_int64),
         ("gflags", C.c_void_p * MAX_WORLD),
         ("ag_m", C.c_int), ("ag_ld", C.c_int),
+        ("sfa", C.c_void_p), ("sfb", C.c_void_p), ("sf_k_blocks", C.c_int),
         ("scale_m", C.c_void_p), ("scale_n", C.c_void_p), ("bias", C.c_void_p),
         ("epoch_ptr", C.c_void_p), ("cta_counter", C.c_void_p), ("status", C.c_void_p),
         ("timeout_ns", C.c_uint64),

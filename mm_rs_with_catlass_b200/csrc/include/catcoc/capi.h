@@ -29,7 +29,8 @@ enum {
 
 /* operand element formats */
 enum { CATCOC_IN_F16 = 0, CATCOC_IN_BF16 = 1, CATCOC_IN_S8 = 2, CATCOC_IN_E4M3 = 3,
-       CATCOC_IN_E5M2 = 4 };
+       CATCOC_IN_E5M2 = 4,
+       CATCOC_IN_MXE4M3 = 5, CATCOC_IN_MXE5M2 = 6 /* block-scaled: UE8M0 scale per 32 K-elements (sfa / sfb) */ };
 /* output / partial element formats (== catcoc::ElemFmt) */
 enum { CATCOC_FMT_F16 = 0, CATCOC_FMT_BF16 = 1, CATCOC_FMT_F32 = 2, CATCOC_FMT_S32 = 3 };
 /* op modes (== catcoc::FusedMode) */
@@ -72,6 +73,11 @@ typedef struct CatcocOpArgs {
   uint32_t* gflags[CATCOC_MAX_WORLD];
   int ag_m;                                /* all-gather: rows of one shard              */
   int ag_ld;                               /* all-gather: row pitch (elements) of the gathered buffer, >= K, 16-byte multiple */
+
+  /* block-scaled fp8 (CATCOC_IN_MX*): scale factors packed in 512-byte blocks of 128 rows x 4
+   * K-blocks (row r, K-block s at (r % 32) * 16 + (r / 32) * 4 + s), block (row_tile, k128) at
+   * (row_tile * sf_k_blocks + k128) * 512; A must be stored [M, K] and B [N, K] */
+  const void* sfa; const void* sfb; int sf_k_blocks;
 
   /* quantised epilogue */
   const float* scale_m; const float* scale_n; const int32_t* bias;

@@ -231,6 +231,11 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
   const int b_cols_cta = CTA2 ? BN / 2 : BN;   // columns of the B tile this CTA loads
   const uint32_t b_stage_bytes = static_cast<uint32_t>(b_cols_cta) * 128u;
   const int qpt = sched.BM / 32;               // 32-row quarters per tile: 4 (single) or 8 (pair)
+  // TMEM columns: two accumulators at 0 and acc_stride. The block-scaled kind runs 128-column
+  // tiles so that columns [256, 288) stay free for the scale factors of two stages in flight.
+  const uint32_t acc_stride = (KIND == KIND_MX) ? 128u : static_cast<uint32_t>(kMaxBN);
+  constexpr uint32_t kSfTmemCol = 256;         // + slot * 16: SFA 4 columns, SFB 4 columns per 128 of N
+  constexpr int kSfSmemOff = kABytes + 128 * 128;   // inside a 48 KiB stage, after A and a 128-column B
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
@@ -348,7 +353,14 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
           // Single flavour: this warp arms its own barrier with its bytes. Pair flavour: both
           // CTAs' copies are credited to the leader's barrier and only the leader arms it, with
           // the bytes of the whole pair. K-blocks past the end of K are fetched as zeros.
-          if (!CTA2) ptx::mbar_expect_tx(&tail->full[stage], kps * kABytes);
+          if (KIND == KIND_MX) {
+            // A block + the 512-byte scale-factor block of (this 128-row tile, this K-block)
+            ptx::mbar_expect_tx(&tail->full[stage], kABytes + 512);
+            const int row_tile = a_row / kBM;
+            ptx::bulk_load_1d(smem + stage * kStageBytes + kSfSmemOff,
+                              p.sfa + (static_cast<int64_t>(row_tile) * p.sf_k_blocks + kb) * 512, 512,
+                              &tail->full[stage]);
+          } else if (!CTA2) ptx::mbar_expect_tx(&tail->full[stage], kps * kABytes);
           else if (leader) ptx::mbar_expect_tx(&tail->full[stage], 2u * kps * kABytes);
 #pragma unroll
           for (int j = 0; j < 2; ++j) {
@@ -429,7 +441,7 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
           break;
         }
         ptx::tcgen05_fence_after();
-        const uint32_t tmem_d = tmem_base + static_cast<uint32_t>(acc * kMaxBN);
+        const uint32_t tmem_d = tmem_base + static_cast<uint32_t>(acc) * acc_stride;
         for (int kb = 0; kb < num_kb; ++kb) {
           tick.lap(c_issue);
           // `probed` is the answer of a non-blocking probe issued before the previous stage's
@@ -456,7 +468,34 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
             const uint32_t np = (stage + 1 == kStages) ? (phase ^ 1u) : phase;
             probed = ptx::mbar_test_wait(&tail->full[ns], np);
           }
-          if (ptx::elect_one()) {
+          if (KIND == KIND_MX) {
+            if (ptx::elect_one()) {
+              // scale factors of this stage: shared -> TMEM (slot alternates with the stage so a
+              // copy never overwrites columns an earlier, still running MMA may read)
+              const uint32_t sf_smem = ptx::smem_u32(smem + stage * kStageBytes + kSfSmemOff);
+              const uint32_t sf_tmem = tmem_base + kSfTmemCol + static_cast<uint32_t>(stage & 1) * 16u;
+              const int nblk = BN / 128;
+              ptx::tmem_cp_32x128b_warpx4(sf_tmem, ptx::make_smem_desc_noswizzle(sf_smem, 128u, 128u));
+              for (int j = 0; j < nblk; ++j)
+                ptx::tmem_cp_32x128b_warpx4(sf_tmem + 4u * (1 + j),
+                                            ptx::make_smem_desc_noswizzle(sf_smem + 512u * (1 + j), 128u, 128u));
+#pragma unroll
+              for (int k = 0; k < 4; ++k) {
+                if (k_first + k < k_mmas) {
+                  const uint64_t dak = da + static_cast<uint64_t>(k * a_kinc);
+                  const uint64_t dbk = db + static_cast<uint64_t>(k * b_kinc);
+                  const uint32_t accum = (k_first + k) != 0 ? 1u : 0u;
+                  // K-block k of the four in a scale word: byte k, passed both as the id in the
+                  // descriptor and in the top bits of the scale addresses
+                  const uint32_t sel = static_cast<uint32_t>(k) << 30;
+                  ptx::umma_mxf8(tmem_d, dak, dbk, ptx::with_sf_ids(idesc, k, k), (sf_tmem) | sel,
+                                 (sf_tmem + 4u) | sel, accum);
+                }
+              }
+              ptx::tcgen05_commit(&tail->empty[stage]);
+              if (kb == num_kb - 1) ptx::tcgen05_commit(&tail->acc_full[acc]);
+            }
+          } else if (ptx::elect_one()) {
 #pragma unroll
             for (int kk = 0; kk < 8; ++kk) {
               const int j = kk >> 2, k = kk & 3;
@@ -471,7 +510,7 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
                 } else {
                   if (KIND == KIND_F16) ptx::umma_f16(tmem_d, dak, dbk, idesc, accum);
                   else if (KIND == KIND_I8) ptx::umma_i8(tmem_d, dak, dbk, idesc, accum);
-                  else ptx::umma_f8f6f4(tmem_d, dak, dbk, idesc, accum);
+                  else if (KIND == KIND_F8) ptx::umma_f8f6f4(tmem_d, dak, dbk, idesc, accum);
                 }
               }
             }
@@ -558,7 +597,7 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
       }
       ptx::tcgen05_fence_after();
       const uint32_t taddr =
-          tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(acc * kMaxBN);
+          tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(acc) * acc_stride;
 
       // Where this warp's 32 rows of the tile go.
       uint8_t* base = nullptr;           // single destination
@@ -818,7 +857,14 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
         if (ptx::elect_one()) {
           const int per_box = 128 / p.elt_bytes_a;
           const uint32_t bar = CTA2 ? ptx::map_to_cta(ptx::smem_u32(&tail->full[stage]), 0u) : 0u;
-          if (!CTA2) ptx::mbar_expect_tx(&tail->full[stage], kps * b_stage_bytes);
+          if (KIND == KIND_MX) {
+            const int nblk = BN / 128;
+            ptx::mbar_expect_tx(&tail->full[stage], b_stage_bytes + nblk * 512);
+            for (int j = 0; j < nblk; ++j)
+              ptx::bulk_load_1d(smem + stage * kStageBytes + kSfSmemOff + 512 * (1 + j),
+                                p.sfb + (static_cast<int64_t>(b_col / 128 + j) * p.sf_k_blocks + kb) * 512, 512,
+                                &tail->full[stage]);
+          } else if (!CTA2) ptx::mbar_expect_tx(&tail->full[stage], kps * b_stage_bytes);
           else if (leader) ptx::mbar_expect_tx(&tail->full[stage], 2u * kps * b_stage_bytes);
 #pragma unroll
           for (int j = 0; j < 2; ++j) {

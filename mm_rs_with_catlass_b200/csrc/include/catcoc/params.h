@@ -21,6 +21,7 @@ enum MmaKind : int {
   KIND_F16 = 0,  // fp16 / bf16 operands, fp32 accumulate   (tcgen05 kind::f16)
   KIND_I8 = 1,   // int8 operands, int32 accumulate          (tcgen05 kind::i8)
   KIND_F8 = 2,   // e4m3 / e5m2 operands, fp32 accumulate    (tcgen05 kind::f8f6f4)
+  KIND_MX = 3,   // e4m3 / e5m2 with UE8M0 scales per 32 K    (tcgen05 kind::mxf8f6f4.block_scale)
 };
 
 // Element formats of outputs and of the partial tiles that cross NVLink.
@@ -91,6 +92,13 @@ struct alignas(64) FusedParams {
   const float* scale_m;   // per output row (token), indexed by the global row; may be null
   const float* scale_n;   // per output column (channel); may be null
   const int32_t* bias;    // int32 [N], added to every rank's accumulator; may be null
+
+  // block-scaled fp8: scale factors packed in 512-byte blocks of 128 rows x 4 K-blocks
+  // (row r, K-block s at (r % 32) * 16 + (r / 32) * 4 + s); block (row_tile, k128) at
+  // ((row_tile * sf_k_blocks) + k128) * 512
+  const uint8_t* sfa;
+  const uint8_t* sfb;
+  int sf_k_blocks;
 
   // launch bookkeeping
   uint32_t* epoch_ptr;       // completed launches on this workspace (local memory)

@@ -261,6 +261,62 @@ CATCOC_DEVICE void tmem_ld_32x32b_x32(uint32_t taddr, uint32_t (&r)[32]) {
 }
 
 // ---------------------------------------------------------------------------------------
+// Block-scaled fp8 (mxf8): scale factors live in TMEM
+// ---------------------------------------------------------------------------------------
+// 1-D bulk copy global -> shared (16-byte aligned, size a multiple of 16), credited to `bar`.
+CATCOC_DEVICE void bulk_load_1d(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+      ::"r"(smem_u32(smem_dst)), "l"(gsrc), "r"(bytes), "r"(smem_u32(bar))
+      : "memory");
+}
+// Descriptor of an unswizzled K-major block whose rows are 16 bytes: 8 rows form one contiguous
+// 128-byte core matrix, successive groups of 8 rows are `sbo_bytes` apart.
+CATCOC_DEVICE uint64_t make_smem_desc_noswizzle(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((smem_addr >> 4) & 0x3FFF);
+  d |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3FFF) << 16;
+  d |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3FFF) << 32;
+  d |= 1ull << 46;  // descriptor version for tcgen05; layout type 0 = no swizzle
+  return d;
+}
+// shared -> TMEM: 32 rows x 128 bits, replicated into all four 32-lane quarters. This is how a
+// 512-byte block of scale factors (128 rows x 4 K-blocks, row r at (r % 32) * 16 + (r / 32) * 4)
+// reaches the columns the block-scaled MMA reads.
+CATCOC_DEVICE void tmem_cp_32x128b_warpx4(uint32_t taddr, uint64_t sdesc) {
+  asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
+}
+// D[tmem] (+)= (A * 2^(sfa-127)) (B * 2^(sfb-127)) with one UE8M0 scale per 32 K-elements.
+CATCOC_DEVICE void umma_mxf8(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                             uint32_t tmem_sfa, uint32_t tmem_sfb, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %6, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%4], [%5], p;\n\t"
+      "}\n" ::"r"(tmem_d),
+      "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(tmem_sfa), "r"(tmem_sfb), "r"(accumulate)
+      : "memory");
+}
+// Instruction descriptor of the block-scaled kind (UE8M0 scales); the scale-factor ids select
+// which of the 4 bytes of a TMEM word (= which K-block of four) an MMA uses.
+__host__ __device__ inline uint32_t make_instr_desc_block_scaled(uint32_t a_fmt, uint32_t b_fmt, uint32_t a_mn_major,
+                                                                 uint32_t b_mn_major, uint32_t m, uint32_t n) {
+  uint32_t d = 0;
+  d |= (a_fmt & 7u) << 7;
+  d |= (b_fmt & 7u) << 10;
+  d |= (a_mn_major & 1u) << 15;
+  d |= (b_mn_major & 1u) << 16;
+  d |= ((n >> 3) & 0x3Fu) << 17;
+  d |= 1u << 23;                       // scale format UE8M0
+  d |= ((m >> 4) & 0x1Fu) << 24;
+  return d;
+}
+CATCOC_DEVICE uint32_t with_sf_ids(uint32_t idesc, uint32_t a_sf_id, uint32_t b_sf_id) {
+  return idesc | ((b_sf_id & 3u) << 4) | ((a_sf_id & 3u) << 29);
+}
+
+// ---------------------------------------------------------------------------------------
 // CTA pairs (thread-block clusters of 2) for tcgen05 cta_group::2
 // ---------------------------------------------------------------------------------------
 CATCOC_DEVICE uint32_t cluster_ctarank() {

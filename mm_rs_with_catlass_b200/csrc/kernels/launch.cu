@@ -141,6 +141,12 @@ static int resolve_format(int in_fmt, Resolved* r) {
     case CATCOC_IN_E5M2:
       *r = {KIND_F8, 1, 128, 32, 1, 1, CU_TENSOR_MAP_DATA_TYPE_UINT8};
       return 0;
+    case CATCOC_IN_MXE4M3:
+      *r = {KIND_MX, 1, 128, 32, 0, 1, CU_TENSOR_MAP_DATA_TYPE_UINT8};
+      return 0;
+    case CATCOC_IN_MXE5M2:
+      *r = {KIND_MX, 1, 128, 32, 1, 1, CU_TENSOR_MAP_DATA_TYPE_UINT8};
+      return 0;
     default:
       set_error("unknown operand format %d", in_fmt);
       return CATCOC_E_BAD_ARG;
@@ -240,9 +246,19 @@ int catcoc_build_params(const CatcocOpArgs* args, FusedParams* p, int* kind_out,
   Resolved rf;
   int rc = resolve_format(a.in_fmt, &rf);
   if (rc != 0) return rc;
-  const int bn = norm_bn(a.tiling.bn);
+  const bool mx = (rf.kind == KIND_MX);
+  const int bn = mx ? 128 : norm_bn(a.tiling.bn);   // block-scaled tiles are 128 wide (TMEM room for scales)
   const int seg_dim = pick_seg_dim(a);
-  const bool pair = (a.tiling.cta_pair == 2);
+  const bool pair = !mx && (a.tiling.cta_pair == 2);
+  if (mx) {
+    if (a.trans_a || !a.trans_b) { set_error("block-scaled fp8 needs A stored [M, K] and B stored [N, K]"); return CATCOC_E_UNSUPPORTED; }
+    if (a.sfa == nullptr || a.sfb == nullptr || a.sf_k_blocks < (a.K + 127) / 128) { set_error("block-scaled fp8 needs packed scale factors covering K"); return CATCOC_E_BAD_ARG; }
+    if (a.mode != CATCOC_MODE_LOCAL && a.W > 1 && (a.mode != CATCOC_MODE_RS || (a.M / a.W) % kBM != 0)) {
+      set_error("block-scaled fp8 is fused with reduce-scatter only, with M / W a multiple of 128");
+      return CATCOC_E_UNSUPPORTED;
+    }
+    if ((reinterpret_cast<uintptr_t>(a.sfa) & 15) || (reinterpret_cast<uintptr_t>(a.sfb) & 15)) { set_error("scale factor blocks must be 16-byte aligned"); return CATCOC_E_ALIGNMENT; }
+  }
   const int bm = pair ? 2 * kBM : kBM;
   if (pair && bn < 128) { set_error("cta_pair=2 needs bn >= 128"); return CATCOC_E_UNSUPPORTED; }
 
@@ -256,7 +272,11 @@ int catcoc_build_params(const CatcocOpArgs* args, FusedParams* p, int* kind_out,
   p->umma_k = rf.umma_k;
   p->a_mn_major = a.trans_a ? 1 : 0;     // stored [K, M]: M contiguous
   p->b_mn_major = a.trans_b ? 0 : 1;     // stored [K, N]: N contiguous
-  p->idesc = ptx::make_instr_desc(rf.c_fmt, rf.a_fmt, rf.a_fmt, p->a_mn_major, p->b_mn_major, bm, bn);
+  p->idesc = mx ? ptx::make_instr_desc_block_scaled(rf.a_fmt, rf.a_fmt, 0, 0, bm, bn)
+                : ptx::make_instr_desc(rf.c_fmt, rf.a_fmt, rf.a_fmt, p->a_mn_major, p->b_mn_major, bm, bn);
+  p->sfa = static_cast<const uint8_t*>(a.sfa);
+  p->sfb = static_cast<const uint8_t*>(a.sfb);
+  p->sf_k_blocks = a.sf_k_blocks;
   p->elt_bytes_a = rf.elt;
 
   if (fused && (a.mode == CATCOC_MODE_RS) && (a.M % a.W != 0)) {
@@ -415,6 +435,7 @@ static cudaError_t prepare_kernels() {
     if ((e = set_smem_attr<KIND_F16, true>()) != cudaSuccess) err = e;
     if ((e = set_smem_attr<KIND_I8, true>()) != cudaSuccess) err = e;
     if ((e = set_smem_attr<KIND_F8, true>()) != cudaSuccess) err = e;
+    if ((e = set_smem_attr<KIND_MX, false>()) != cudaSuccess) err = e;
   });
   return err;
 }
@@ -479,6 +500,7 @@ int catcoc_launch_params(const FusedParams& p, int kind, int grid, int pair, cud
     set_error("cudaFuncSetAttribute failed: %s", cudaGetErrorString(e));
     return -1000 - static_cast<int>(e);
   }
+  if (pair && kind == KIND_MX) { set_error("block-scaled fp8 has no 2-CTA flavour"); return CATCOC_E_UNSUPPORTED; }
   if (pair) {
     e = kind == KIND_F16 ? launch_one<KIND_F16, true>(p, grid, stream)
         : kind == KIND_I8 ? launch_one<KIND_I8, true>(p, grid, stream)
@@ -486,7 +508,8 @@ int catcoc_launch_params(const FusedParams& p, int kind, int grid, int pair, cud
   } else {
     e = kind == KIND_F16 ? launch_one<KIND_F16, false>(p, grid, stream)
         : kind == KIND_I8 ? launch_one<KIND_I8, false>(p, grid, stream)
-                          : launch_one<KIND_F8, false>(p, grid, stream);
+        : kind == KIND_F8 ? launch_one<KIND_F8, false>(p, grid, stream)
+                          : launch_one<KIND_MX, false>(p, grid, stream);
   }
   if (e != cudaSuccess) {
     set_error("kernel launch failed: %s", cudaGetErrorString(e));

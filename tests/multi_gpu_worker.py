@@ -105,6 +105,27 @@ if mode == "ops":
             gold = ref.quant_matmul_reduce_scatter(x1, x2, s1, s2, bias, trans_b=tb, out_dtype=torch.float32)
             o = catcoc.quant_matmul_reduce_scatter(x1, x2, s1, s2, bias, trans_b=tb, out_dtype=out_dtype)
             check("qrs_%dx%dx%d_%d_%s" % (M, N, K, tb, str(out_dtype)[6:]), o, gold, 512, out_dtype)
+    # block-scaled fp8 (mxf8) row-parallel linear with the fused reduce-scatter
+    if hasattr(torch, "float8_e4m3fn"):
+        for (M, N, K) in [(256 * W, 384, 512), (128 * W, 256, 1024), (128 * W, 136, 96)]:
+            g = torch.Generator(device=dev)
+            g.manual_seed(900 + rank)
+            a = torch.randn(M, K, device=dev, generator=g)
+            b = torch.randn(N, K, device=dev, generator=g) * 0.1
+            a = a * torch.exp2(torch.randint(-3, 3, (M, K // 32), device=dev, generator=g).float()).repeat_interleave(32, 1)
+            aq, sa = catcoc.quantize_mxf8(a)
+            bq, sb = catcoc.quantize_mxf8(b)
+            full = catcoc.dequantize_mxf8(aq, sa) @ catcoc.dequantize_mxf8(bq, sb).t()
+            mag = full.abs()
+            dist.all_reduce(full)
+            dist.all_reduce(mag)
+            rows = M // W
+            sl = slice(rank * rows, (rank + 1) * rows)
+            o = catcoc.mxf8_matmul_reduce_scatter(aq, catcoc.pack_scales(sa), bq, catcoc.pack_scales(sb))
+            check("mxf8_rs_%dx%dx%d" % (M, N, K), o, full[sl], K * W, torch.bfloat16, mag[sl])
+            o = catcoc.mxf8_matmul_reduce_scatter(aq, catcoc.pack_scales(sa), bq, catcoc.pack_scales(sb),
+                                                  tiling=catcoc.TilingConfig(fp32_partials=True))
+            check("mxf8_rs32_%dx%dx%d" % (M, N, K), o, full[sl], K * W, torch.bfloat16)
     # debug pattern (all-ones operands, arange bias) localises indexing errors
     x1, x2, s1, s2, bias = quant_inputs(32 * W, 256, 128, rank, dev, debug=True)
     o = catcoc.quant_matmul_reduce_scatter(x1, x2, s1, s2, bias, out_dtype=torch.float32)

@@ -98,6 +98,31 @@ def test_fp8_operands(catcoc, device):
     assert torch.allclose(out.float(), ref, rtol=2e-2, atol=2e-2 * ref.abs().max().item())
 
 
+@pytest.mark.skipif(not hasattr(torch, "float8_e4m3fn"), reason="no fp8 dtype in this torch")
+@pytest.mark.parametrize("M,N,K", [(128, 128, 128), (256, 384, 1024), (200, 328, 160), (1, 8, 32), (513, 130, 4096)])
+@pytest.mark.parametrize("fmt", ["e4m3", "e5m2"])
+def test_block_scaled_fp8(catcoc, device, M, N, K, fmt):
+    """mxf8: one UE8M0 scale per 32 K-elements, applied by the tensor core from TMEM. Scales are
+    spread over 12 binades across rows and K-blocks, so any mix-up of rows, blocks or operands
+    shows as an error of order one."""
+    g = torch.Generator(device=device)
+    g.manual_seed(M + N + K)
+    a = torch.randn(M, K, device=device, generator=g)
+    b = torch.randn(N, K, device=device, generator=g) * 0.1
+    a = a * torch.exp2(torch.randint(-6, 6, (M, K // 32), device=device, generator=g).float()).repeat_interleave(32, 1)
+    b = b * torch.exp2(torch.randint(-4, 4, (N, K // 32), device=device, generator=g).float()).repeat_interleave(32, 1)
+    aq, sa = catcoc.quantize_mxf8(a, fmt)
+    bq, sb = catcoc.quantize_mxf8(b, fmt)
+    ref = catcoc.dequantize_mxf8(aq, sa) @ catcoc.dequantize_mxf8(bq, sb).t()
+    out = catcoc.mxf8_matmul(aq, catcoc.pack_scales(sa), bq, catcoc.pack_scales(sb), out_dtype=torch.float32)
+    _check_status(device, "mxf8")
+    assert (out - ref).abs().max().item() <= 1e-4 * ref.abs().max().item()
+    out16 = catcoc.mxf8_matmul(aq, catcoc.pack_scales(sa), bq, catcoc.pack_scales(sb))
+    _check_status(device, "mxf8 bf16")
+    assert out16.dtype == torch.bfloat16
+    assert (out16.float() - ref).abs().max().item() <= 2 ** -7 * ref.abs().max().item()
+
+
 def test_repeated_launches_alternating_shapes(catcoc, device):
     """Back-to-back launches on one stream with changing shapes: stale barrier / TMEM state
     from one launch must not leak into the next."""

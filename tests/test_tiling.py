@@ -92,3 +92,20 @@ def test_heuristic_fills_the_machine_and_is_deterministic():
     assert chooser.heuristic("matmul_reduce_scatter", 8192, 8192, 3584, 8, torch.bfloat16) == big
     tbl = TilingTable([_row("matmul_reduce_scatter", 8192, 3584, 8192, 1.0, bn=128, swizzle=4)])
     assert chooser.choose("matmul_reduce_scatter", 8192, 8192, 3584, 8, torch.bfloat16, table=tbl).bn == 128
+
+
+def test_mx_scale_packing_matches_the_tensor_core_block_layout():
+    from mm_rs_with_catlass_b200.ops import mx
+    x = torch.randn(200, 160) * torch.exp2(torch.randint(-6, 6, (200, 5)).float()).repeat_interleave(32, 1)
+    q, s = mx.quantize_mxf8(x)
+    assert q.dtype == torch.float8_e4m3fn and s.shape == (200, 5) and s.dtype == torch.uint8
+    d = mx.dequantize_mxf8(q, s)
+    assert (d - x).abs().max() <= 2 ** -3 * x.abs().max()          # e4m3: 3 mantissa bits
+    assert q.float().abs().max() <= 448.0
+    p = mx.pack_scales(s)
+    assert p.shape == (2, 2, 512)
+    for r, kb in ((0, 0), (31, 4), (32, 1), (137, 3), (199, 2)):
+        assert int(p[r // 128, kb // 4, (r % 32) * 16 + ((r % 128) // 32) * 4 + kb % 4]) == int(s[r, kb])
+    assert int(p[1, 1, (10 % 32) * 16 + 3 * 4 + 3]) == 127          # padding is the neutral scale
+    with pytest.raises(ValueError):
+        mx.quantize_mxf8(torch.randn(4, 40))
