@@ -20,6 +20,9 @@ from .ops.gemm import matmul  # noqa: F401
 from .ops.fused import (matmul_allreduce, allgather_matmul, matmul_reduce_scatter,  # noqa: F401
                         quant_matmul_reduce_scatter)
 
+from .ops.blas import (gemm, matmul_bias, matmul_add, optimized_matmul, batched_matmul,  # noqa: F401
+                       grouped_matmul, grouped_quant_matmul, grouped_matmul_slice_k, group_gemm,
+                       splitk_matmul, gemv)
 from .ops.mx import (mxf8_matmul, mxf8_matmul_reduce_scatter, quantize_mxf8, dequantize_mxf8,  # noqa: F401
                      pack_scales)
 

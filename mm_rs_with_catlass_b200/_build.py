@@ -23,6 +23,7 @@ SOURCES = [
     "kernels/launch.cu",
     "kernels/shmem_prims.cu",
     "kernels/no_alloc.cu",
+    "kernels/blas_prims.cu",
     "shmem/host.cu",
     "oracle/oracle.cpp",
 ]

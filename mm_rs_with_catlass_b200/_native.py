@@ -61,6 +61,12 @@ class OpArgs(C.Structure):
         ("ag_m", C.c_int), ("ag_ld", C.c_int),
         ("sfa", C.c_void_p), ("sfb", C.c_void_p), ("sf_k_blocks", C.c_int),
         ("scale_m", C.c_void_p), ("scale_n", C.c_void_p), ("bias", C.c_void_p),
+        ("affine", C.c_int), ("alpha", C.c_float), ("beta", C.c_float),
+        ("c_src", C.c_void_p), ("ldc_src", C.c_int64), ("bias_f", C.c_void_p),
+        ("num_groups", C.c_int), ("group_ends", C.c_void_p), ("group_rows", C.c_int),
+        ("a_rows_total", C.c_int), ("a_k_total", C.c_int), ("b_n_total", C.c_int), ("b_k_total", C.c_int),
+        ("g_a_row_back", C.c_int), ("g_a_k", C.c_int), ("g_b_row", C.c_int), ("g_b_k", C.c_int),
+        ("g_nvec", C.c_int),
         ("epoch_ptr", C.c_void_p), ("cta_counter", C.c_void_p), ("status", C.c_void_p),
         ("timeout_ns", C.c_uint64),
         ("withhold_signals", C.c_int),
@@ -102,6 +108,7 @@ def _declare(lib) -> None:
         "catcoc_sched_total_tiles": (i32, [i32] * 6),
         "catcoc_sched_get_tile": (i32, [i32] * 9 + [P(Tile)]),
         "catcoc_sched_get_tile_rounds": (i32, [i32] * 10 + [P(Tile)]),
+        "catcoc_group_walk_replay": (i32, [i32, i32, i32, i32, i32, vp, i32, i32, P(Tile)]),
         "catcoc_oracle_matmul_f32": (i32, [vp, vp, vp, i32, i32, i32, i32, i32]),
         "catcoc_oracle_quant_matmul": (i32, [vp, vp, vp, vp, i32, i32, i32, i32, i32]),
         "catcoc_oracle_dequant": (i32, [vp, vp, vp, vp, i32, i32]),
@@ -129,6 +136,9 @@ def _declare(lib) -> None:
         "catcoc_shmem_mc_reduce_bf16": (i32, [P(ShmemCtx), vp, i64, i64, vp]),
         "catcoc_shmem_put_blocks": (i32, []),
         "catcoc_pad2d": (i32, [vp, i64, vp, i64, i64, i64, vp]),
+        "catcoc_splitk_reduce": (i32, [vp, i32, i64, i32, i32, vp, i64, i32, C.c_float, C.c_float, vp, i64, vp, vp]),
+        "catcoc_gemv_workspace_floats": (i64, [i32, i32, i32]),
+        "catcoc_gemv": (i32, [vp, i64, i32, i32, i32, i32, vp, vp, vp, C.c_float, C.c_float, vp, vp]),
         "catcoc_matmul_noalloc": (i32, [vp, i64, vp, i64, vp, i64, i32, i32, i32, i32, i32, i32, i32, vp]),
         "catcoc_matmul_noalloc_status": (i32, [P(u32)]),
     }

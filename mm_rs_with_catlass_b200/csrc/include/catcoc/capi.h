@@ -82,6 +82,22 @@ typedef struct CatcocOpArgs {
   /* quantised epilogue */
   const float* scale_m; const float* scale_n; const int32_t* bias;
 
+  /* affine epilogue (affine != 0): out = cast(alpha * acc + beta * c_src[row, col] + bias_f[col]);
+   * c_src has the format and row indexing of `out` (it may be `out` itself), bias_f is fp32 [N] */
+  int affine; float alpha; float beta;
+  const void* c_src; int64_t ldc_src; const float* bias_f;
+
+  /* Group walk (mode LOCAL only, num_groups > 0): one launch runs num_groups products that share
+   * N and K. M counts the rows of the whole output; group g owns rows [end_{g-1}, end_g), read from
+   * group_ends (device int32, cumulative) or, when that is NULL, g * group_rows. The stored
+   * operands may be larger than one product: a_rows_total x a_k_total and b_n_total x b_k_total
+   * (0 = M, K, N, K). Row r of group g reads A row r - g * g_a_row_back; K coordinates start at
+   * g * g_a_k (A) and g * g_b_k (B); a B stored [N, K] starts at row g * g_b_row; the per-column
+   * vectors (scale_n, bias, bias_f) of group g start at element g * g_nvec. */
+  int num_groups; const int32_t* group_ends; int group_rows;
+  int a_rows_total, a_k_total, b_n_total, b_k_total;
+  int g_a_row_back, g_a_k, g_b_row, g_b_k, g_nvec;
+
   uint32_t* epoch_ptr; uint32_t* cta_counter; uint32_t* status;
   uint64_t timeout_ns;
   int withhold_signals;
@@ -110,6 +126,11 @@ int catcoc_sched_get_tile(int M, int N, int bm, int bn, int W, int seg_dim, int 
                           int swizzle, int t, CatcocTile* out);
 int catcoc_sched_get_tile_rounds(int M, int N, int bm, int bn, int W, int seg_dim, int first_seg,
                                  int swizzle, int rounds, int t, CatcocTile* out);
+/* Host replay of the group walk of a grouped / batched / split-K launch: writes up to max_tiles
+ * tiles in launch order (seg = group) and returns the walk's tile count. `ends` is host memory
+ * here (cumulative rows per group) or NULL for uniform groups of group_rows rows. */
+int catcoc_group_walk_replay(int M, int N, int bm, int bn, int num_groups, const int32_t* ends,
+                             int group_rows, int max_tiles, CatcocTile* out);
 
 /* ---- CPU oracle (naive fp32 / int32 loops; see csrc/oracle/oracle.cpp) ---- */
 int catcoc_oracle_matmul_f32(const float* a, const float* b, float* c, int M, int N, int K,
@@ -167,6 +188,18 @@ int catcoc_shmem_put_blocks(void);  /* blocks a put launches: each adds signal_v
 /* copy rows into a buffer whose pitch is TMA-legal, zero-filling the padding */
 int catcoc_pad2d(void* dst, int64_t dst_pitch, const void* src, int64_t src_pitch, int64_t rows,
                  int64_t row_bytes, void* stream);
+
+/* out = cast(alpha * sum over `slices` fp32 partials [rows, cols] (slice s at parts + s * slice_elems)
+ *            + beta * c_src + bias[cols]); finishes a split-K product */
+int catcoc_splitk_reduce(const float* parts, int slices, int64_t slice_elems, int rows, int cols, void* out,
+                         int64_t ldc, int out_fmt, float alpha, float beta, const void* c_src,
+                         int64_t ldc_src, const float* bias, void* stream);
+/* y = alpha * op(A) x + beta * y_in, A row-major [rows, cols] of fp16 / bf16 / fp32 (CATCOC_FMT_*),
+ * op = transpose when `trans` (then x has `rows` and y `cols` elements and `workspace` must hold
+ * catcoc_gemv_workspace_floats(rows, cols, 1) floats) */
+int64_t catcoc_gemv_workspace_floats(int rows, int cols, int trans);
+int catcoc_gemv(const void* A, int64_t lda, int fmt, int rows, int cols, int trans, const void* x, void* y,
+                const void* y_in, float alpha, float beta, float* workspace, void* stream);
 
 #ifdef __cplusplus
 }

@@ -196,6 +196,36 @@ CATCOC_DEVICE void flush_staged(uint32_t stg, int lane, uint8_t* base, int64_t p
 }
 
 // ---------------------------------------------------------------------------------------
+// Group walk: one launch over several products that share N and K (grouped, batched, split-K).
+// The tile list is the concatenation of the groups' tile grids, rows fastest inside a group, so
+// that the CTAs working side by side share the group's B columns. Group extents live in device
+// memory (a routing result need not visit the host), so every warp derives the tile count and
+// walks the list with a cursor that only moves forward.
+// ---------------------------------------------------------------------------------------
+// called by a converged warp; every lane gets the sum
+CATCOC_DEVICE int grouped_total_tiles(const FusedParams& p, int lane) {
+  const int nt = ceil_div(p.sched.N, p.sched.BN);
+  int sum = 0;
+  for (int g = lane; g < p.num_groups; g += 32) {
+    const int b = (g == 0) ? 0 : group_end_row(p.group_ends, p.group_rows, p.sched.M, g - 1);
+    sum += ceil_div(max(0, group_end_row(p.group_ends, p.group_rows, p.sched.M, g) - b), p.sched.BM) * nt;
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+  return sum;
+}
+
+CATCOC_DEVICE GroupWalk group_walk_begin(const FusedParams& p) {
+  return group_walk_begin(p.num_groups, p.group_ends, p.group_rows, p.sched.M);
+}
+
+// `t` must be below the total and must not decrease between calls on the same cursor
+CATCOC_DEVICE TileInfo walk_tile(const FusedParams& p, int t, GroupWalk& w) {
+  if (p.num_groups == 0) return get_tile(p.sched, t);
+  return group_walk_tile(p.sched, p.num_groups, p.group_ends, p.group_rows, t, w);
+}
+
+// ---------------------------------------------------------------------------------------
 // The kernel
 // ---------------------------------------------------------------------------------------
 template <int KIND, bool CTA2>
@@ -236,6 +266,8 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
   const uint32_t acc_stride = (KIND == KIND_MX) ? 128u : static_cast<uint32_t>(kMaxBN);
   constexpr uint32_t kSfTmemCol = 256;         // + slot * 16: SFA 4 columns, SFB 4 columns per 128 of N
   constexpr int kSfSmemOff = kABytes + 128 * 128;   // inside a 48 KiB stage, after A and a 128-column B
+  const bool grouped = (p.num_groups > 0);
+  const int total_tiles = grouped ? grouped_total_tiles(p, lane) : sched.total_tiles;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
@@ -283,10 +315,16 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
     Tick tick(tr);
     bool pre_ok = false, pre_valid = false;   // all-gather: stamps of the next tile sampled early
     int pre_tile = -1;
-    for (int t = worker; ok && t < sched.total_tiles; t += num_workers) {
-      const TileInfo ti = get_tile(sched, t);
+    GroupWalk walk = group_walk_begin(p);
+    for (int t = worker; ok && t < total_tiles; t += num_workers) {
+      const TileInfo ti = walk_tile(p, t, walk);
       const CUtensorMap* tma = &p.tm_a;
       int a_row = ti.m0 + sub * kBM;
+      int a_k_off = 0;
+      if (grouped) {
+        a_row -= ti.seg * p.g_a_row_back;
+        a_k_off = ti.seg * p.g_a_k;
+      }
       if (p.mode == MODE_AG && p.W > 1) {
         if (ti.seg == p.rank) {
           a_row = ti.mi * sched.BM + sub * kBM;  // row inside the local shard
@@ -366,7 +404,7 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
           for (int j = 0; j < 2; ++j) {
             if (j >= kps) break;
             uint8_t* sa = smem + stage * kStageBytes + j * sub_bytes;
-            const int k0 = (kb * kps + j) * p.bk;
+            const int k0 = (kb * kps + j) * p.bk + a_k_off;
             if (!CTA2) {
               if (!p.a_mn_major) {
                 ptx::tma_load_2d(sa, tma, &tail->full[stage], k0, a_row);
@@ -429,7 +467,7 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
       unsigned long long c_full = 0, c_acc = 0, c_issue = 0;
       Tick tick(tr);
       bool probed = false;
-      for (int t = worker; ok && t < sched.total_tiles; t += num_workers) {
+      for (int t = worker; ok && t < total_tiles; t += num_workers) {
         tick.lap(c_issue);
         const bool got_acc = ptx::mbar_wait(&tail->acc_empty[acc], acc_phase ^ 1u, p.timeout_ns, abort_flag);
         tick.lap(c_acc);
@@ -560,13 +598,16 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
     unsigned long long c_full = 0, c_work = 0, c_peer = 0, c_pub = 0, c_own = 0;
     Tick tick(tr);
 
-    for (int t = worker; ok && t < sched.total_tiles; t += num_workers) {
-      const TileInfo ti = get_tile(sched, t);
+    GroupWalk walk = group_walk_begin(p);
+    for (int t = worker; ok && t < total_tiles; t += num_workers) {
+      const TileInfo ti = walk_tile(p, t, walk);
       const bool own = !fused || (p.mode == MODE_AG) || (ti.seg == p.rank);
       const bool reduce_here = fused && own && (p.mode == MODE_RS || p.mode == MODE_AR);
       const int st_fmt = own ? p.out_fmt : pfmt;   // format of what this tile's epilogue stores
       const int st_elt = fmt_bytes(st_fmt);
       const int rows_valid = max(0, min(32, ti.rows - row_base));
+      const int nvec_off = grouped ? ti.seg * p.g_nvec : 0;   // this group's per-column vectors
+      const bool affine = (p.affine != 0) && own;
 
       tick.lap(c_work);
       if (reduce_here) {
@@ -657,7 +698,7 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
 #pragma unroll
             for (int j = 0; j < 32; ++j) {
               const int c = ti.n0 + col0 + j;
-              const int32_t b = (c < sched.N) ? __ldg(p.bias + c) : 0;
+              const int32_t b = (c < sched.N) ? __ldg(p.bias + nvec_off + c) : 0;
               v[j] = static_cast<uint32_t>(static_cast<int32_t>(v[j]) + b);
             }
           }
@@ -720,7 +761,7 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
           }
 
           // convert this row's 32 values to the stored format and stage them
-          if (st_fmt == FMT_S32 || (st_fmt == FMT_F32 && !is_int && !(dequant && own))) {
+          if (st_fmt == FMT_S32 || (st_fmt == FMT_F32 && !is_int && !(dequant && own) && !affine)) {
 #pragma unroll
             for (int u = 0; u < 8; ++u)
               stage_write(stg, lane, u,
@@ -742,8 +783,63 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
               for (int j = 0; j < 32; ++j) {
                 const int c = ti.n0 + col0 + j;
                 const float sn =
-                    (p.scale_n != nullptr && c < sched.N) ? __ldg(p.scale_n + c) : 1.0f;
+                    (p.scale_n != nullptr && c < sched.N) ? __ldg(p.scale_n + nvec_off + c) : 1.0f;
                 f[j] = f[j] * sn * sm;
+              }
+            }
+            if (affine) {
+              // out = alpha * acc + beta * C + bias: each lane walks its own row of C
+              const float alpha = p.alpha, beta = p.beta;
+              const int cvalid = min(32, ti.cols - col0);
+#pragma unroll
+              for (int j = 0; j < 32; ++j) {
+                float x = alpha * f[j];
+                if (p.bias_f != nullptr && j < cvalid) x += __ldg(p.bias_f + nvec_off + ti.n0 + col0 + j);
+                f[j] = x;
+              }
+              if (p.c_src != nullptr && row_in_tile < ti.rows) {
+                const uint8_t* crow = static_cast<const uint8_t*>(p.c_src) +
+                    (static_cast<int64_t>(ti.m0 + row_in_tile - p.out_row_shift) * p.ldc_src + ti.n0 + col0) * st_elt;
+                if (cvalid == 32 && (reinterpret_cast<uintptr_t>(crow) & 15) == 0) {
+                  if (st_fmt == FMT_F32) {
+#pragma unroll
+                    for (int u = 0; u < 8; ++u) {
+                      const uint4 w = ptx::ld_global_v4(crow + u * 16);
+                      f[u * 4] += beta * __uint_as_float(w.x);
+                      f[u * 4 + 1] += beta * __uint_as_float(w.y);
+                      f[u * 4 + 2] += beta * __uint_as_float(w.z);
+                      f[u * 4 + 3] += beta * __uint_as_float(w.w);
+                    }
+                  } else {
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                      const uint4 w = ptx::ld_global_v4(crow + u * 16);
+                      const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+                      for (int e = 0; e < 4; ++e) {
+                        const float2 c2 = unpack2(ww[e], st_fmt);
+                        f[u * 8 + e * 2] += beta * c2.x;
+                        f[u * 8 + e * 2 + 1] += beta * c2.y;
+                      }
+                    }
+                  }
+                } else {
+                  // ragged or unaligned: element loads (the index stays a compile-time constant
+                  // so that f[] remains in registers)
+#pragma unroll
+                  for (int j = 0; j < 32; ++j) {
+                    if (j < cvalid) {
+                      float cv;
+                      if (st_fmt == FMT_F32) {
+                        cv = *reinterpret_cast<const float*>(crow + j * 4);
+                      } else {
+                        const uint32_t h = *reinterpret_cast<const uint16_t*>(crow + j * 2);
+                        cv = unpack2(h, st_fmt).x;
+                      }
+                      f[j] += beta * cv;
+                    }
+                  }
+                }
               }
             }
             if (st_fmt == FMT_F32) {
@@ -842,9 +938,15 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
     int stage = 0;
     uint32_t phase = 0;
     bool ok = true;
-    for (int t = worker; ok && t < sched.total_tiles; t += num_workers) {
-      const TileInfo ti = get_tile(sched, t);
-      const int b_col = ti.n0 + sub * b_cols_cta;
+    GroupWalk walk = group_walk_begin(p);
+    for (int t = worker; ok && t < total_tiles; t += num_workers) {
+      const TileInfo ti = walk_tile(p, t, walk);
+      int b_col = ti.n0 + sub * b_cols_cta;
+      int b_k_off = 0;
+      if (grouped) {
+        b_col += ti.seg * p.g_b_row;
+        b_k_off = ti.seg * p.g_b_k;
+      }
       for (int kb = 0; kb < num_kb; ++kb) {
         if (!ptx::mbar_wait(&tail->empty[stage], phase ^ 1u, p.timeout_ns, abort_flag)) {
           if (lane == 0) {
@@ -870,7 +972,7 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
           for (int j = 0; j < 2; ++j) {
             if (j >= kps) break;
             uint8_t* sb = smem + stage * kStageBytes + j * sub_bytes + kABytes;
-            const int k0 = (kb * kps + j) * p.bk;
+            const int k0 = (kb * kps + j) * p.bk + b_k_off;
             if (!CTA2) {
               if (!p.b_mn_major) {
                 ptx::tma_load_2d(sb, &p.tm_b, &tail->full[stage], k0, b_col);

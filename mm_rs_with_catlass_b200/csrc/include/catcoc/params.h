@@ -93,6 +93,26 @@ struct alignas(64) FusedParams {
   const float* scale_n;   // per output column (channel); may be null
   const int32_t* bias;    // int32 [N], added to every rank's accumulator; may be null
 
+  // affine epilogue on finished (owned) tiles, after the dequantisation above; off when
+  // `affine` is 0:  out = cast(alpha * acc + beta * c_src[row, col] + bias_f[col])
+  int affine;
+  float alpha, beta;
+  const void* c_src;      // same element format and row indexing as `out`; may be null
+  int64_t ldc_src;        // elements per row of c_src
+  const float* bias_f;    // fp32 [N]; may be null
+
+  // Group walk (MODE_LOCAL only; num_groups == 0: off). One launch covers several GEMMs that
+  // share N and K: the output's rows [begin_g, end_g) belong to group g. It serves grouped
+  // (ragged rows per group), batched (uniform rows) and split-K (group = K slice) products.
+  int num_groups;
+  const int32_t* group_ends;  // device: cumulative row count after each group; null = uniform
+  int group_rows;             // uniform groups: rows of every group
+  int g_a_row_back;           // A row of output row r of group g:  r - g * g_a_row_back
+  int g_a_k;                  // K coordinate of A starts at  g * g_a_k
+  int g_b_row;                // N coordinate of B (stored [N, K]) starts at  g * g_b_row
+  int g_b_k;                  // K coordinate of B starts at  g * g_b_k
+  int g_nvec;                 // scale_n / bias / bias_f of group g start at  g * g_nvec
+
   // block-scaled fp8: scale factors packed in 512-byte blocks of 128 rows x 4 K-blocks
   // (row r, K-block s at (r % 32) * 16 + (r / 32) * 4 + s); block (row_tile, k128) at
   // ((row_tile * sf_k_blocks) + k128) * 512

@@ -183,6 +183,76 @@ CATCOC_HD TileInfo get_tile(const TileSched& s, int t) {
   return ti;
 }
 
+// ---------------------------------------------------------------------------------------
+// Group walk: the tile list of one launch over several products that share N and K (grouped,
+// batched, split-K). It is the concatenation of the groups' tile grids, rows fastest inside a
+// group so that tiles running side by side share the group's B columns. Group g owns the
+// output rows [end(g-1), end(g)); `ends` (cumulative counts, possibly device memory) or, when it
+// is null, uniform groups of `group_rows` rows. Extents are clamped to [0, M] and to be
+// non-decreasing, so a malformed list can skip rows but never address outside the output.
+// ---------------------------------------------------------------------------------------
+struct GroupWalk {
+  int g;           // current group
+  int tile_base;   // tiles of the groups before g
+  int row_begin;   // first output row of g
+  int row_end;     // one past its last row
+};
+
+CATCOC_HD int group_end_row(const int32_t* ends, int group_rows, int M, int g) {
+  const int e = (ends != nullptr) ? ends[g] : (g + 1) * group_rows;
+  return e < 0 ? 0 : (e > M ? M : e);
+}
+
+CATCOC_HD GroupWalk group_walk_begin(int num_groups, const int32_t* ends, int group_rows, int M) {
+  GroupWalk w;
+  w.g = 0; w.tile_base = 0; w.row_begin = 0;
+  w.row_end = (num_groups > 0) ? group_end_row(ends, group_rows, M, 0) : 0;
+  return w;
+}
+
+CATCOC_HD int group_rows_of(const GroupWalk& w) { return w.row_end > w.row_begin ? w.row_end - w.row_begin : 0; }
+
+// `t` must be below the walk's total and must not decrease between calls on one cursor.
+CATCOC_HD TileInfo group_walk_tile(const TileSched& s, int num_groups, const int32_t* ends, int group_rows, int t,
+                                   GroupWalk& w) {
+  const int nt = (s.N + s.BN - 1) / s.BN;
+  int mt = (group_rows_of(w) + s.BM - 1) / s.BM;
+  while (t >= w.tile_base + mt * nt && w.g + 1 < num_groups) {
+    w.tile_base += mt * nt;
+    ++w.g;
+    if (w.row_end > w.row_begin) w.row_begin = w.row_end;
+    w.row_end = group_end_row(ends, group_rows, s.M, w.g);
+    mt = (group_rows_of(w) + s.BM - 1) / s.BM;
+  }
+  TileInfo ti;
+  const int local = t - w.tile_base;
+  if (mt < 1) mt = 1;
+  ti.seg = w.g;
+  ti.tile_in_seg = local;
+  ti.mi = local % mt;
+  ti.ni = local / mt;
+  ti.m0 = w.row_begin + ti.mi * s.BM;
+  ti.n0 = ti.ni * s.BN;
+  ti.rows = w.row_end - ti.m0;
+  if (ti.rows > s.BM) ti.rows = s.BM;
+  if (ti.rows < 0) ti.rows = 0;
+  ti.cols = s.N - ti.n0;
+  if (ti.cols > s.BN) ti.cols = s.BN;
+  if (ti.cols < 0) ti.cols = 0;
+  return ti;
+}
+
+// Serial count of the walk's tiles (the kernel computes the same sum with one warp).
+CATCOC_HD int group_walk_total(const TileSched& s, int num_groups, const int32_t* ends, int group_rows) {
+  const int nt = (s.N + s.BN - 1) / s.BN;
+  int total = 0, begin = 0;
+  for (int g = 0; g < num_groups; ++g) {
+    const int e = group_end_row(ends, group_rows, s.M, g);
+    if (e > begin) { total += ((e - begin + s.BM - 1) / s.BM) * nt; begin = e; }
+  }
+  return total;
+}
+
 // Order in which a pusher visits its peers: the peer that consumes this rank's data earliest
 // comes first. For source-major consumers (allgather_matmul) rank r reads source q in phase
 // (q - r) mod W, so q serves q-1, q-2, ... For destination-major producers the order is

@@ -214,6 +214,22 @@ extern "C" int catcoc_sched_get_tile_rounds(int M, int N, int bm, int bn, int W,
   out->m0 = ti.m0; out->n0 = ti.n0; out->rows = ti.rows; out->cols = ti.cols;
   return CATCOC_OK;
 }
+// Host replay of the group walk (ends = host memory or null for uniform groups): writes up to
+// max_tiles tiles in launch order and returns the walk's tile count.
+extern "C" int catcoc_group_walk_replay(int M, int N, int bm, int bn, int num_groups, const int32_t* ends,
+                                        int group_rows, int max_tiles, CatcocTile* out) {
+  if (M <= 0 || N <= 0 || bm <= 0 || bn <= 0 || num_groups <= 0) return CATCOC_E_BAD_ARG;
+  const TileSched s = make_sched(M, N, bm, bn, 1, SEG_ROWS, 0, 1);
+  const int total = group_walk_total(s, num_groups, ends, group_rows);
+  GroupWalk w = group_walk_begin(num_groups, ends, group_rows, M);
+  for (int t = 0; t < total && t < max_tiles && out != nullptr; ++t) {
+    const TileInfo ti = group_walk_tile(s, num_groups, ends, group_rows, t, w);
+    out[t].seg = ti.seg; out[t].tile_in_seg = ti.tile_in_seg; out[t].mi = ti.mi; out[t].ni = ti.ni;
+    out[t].m0 = ti.m0; out[t].n0 = ti.n0; out[t].rows = ti.rows; out[t].cols = ti.cols;
+  }
+  return total;
+}
+
 extern "C" int catcoc_sched_get_tile(int M, int N, int bm, int bn, int W, int seg_dim,
                                      int first_seg, int swizzle, int t, CatcocTile* out) {
   TileSched s = make_sched(M, N, bm, bn, W, seg_dim, first_seg, swizzle);
@@ -284,6 +300,49 @@ int catcoc_build_params(const CatcocOpArgs* args, FusedParams* p, int* kind_out,
     return CATCOC_E_BAD_ARG;
   }
 
+  // ---- group walk (grouped / batched / split-K in one launch) ----
+  const bool grouped = a.num_groups > 0;
+  const int a_rows = (grouped && a.a_rows_total > 0) ? a.a_rows_total : a.M;
+  const int a_k = (grouped && a.a_k_total > 0) ? a.a_k_total : a.K;
+  const int b_n = (grouped && a.b_n_total > 0) ? a.b_n_total : a.N;
+  const int b_k = (grouped && a.b_k_total > 0) ? a.b_k_total : a.K;
+  if (grouped) {
+    if (fused || a.mode != CATCOC_MODE_LOCAL || mx) { set_error("the group walk runs local, non block-scaled products only"); return CATCOC_E_UNSUPPORTED; }
+    if (a.group_ends == nullptr && (a.group_rows <= 0 || static_cast<int64_t>(a.group_rows) * a.num_groups != a.M)) {
+      set_error("uniform groups: M (%d) must be num_groups (%d) x group_rows (%d)", a.M, a.num_groups, a.group_rows);
+      return CATCOC_E_BAD_ARG;
+    }
+    if (a.g_a_row_back < 0 || a.g_a_k < 0 || a.g_b_row < 0 || a.g_b_k < 0 || a.g_nvec < 0) { set_error("negative group stride"); return CATCOC_E_BAD_ARG; }
+    if (a.group_ends != nullptr && a.trans_a) {
+      // a ragged group origin would be the innermost TMA coordinate of an A stored [K, M]
+      set_error("ragged groups need A stored [M, K]");
+      return CATCOC_E_UNSUPPORTED;
+    }
+    // K origins of a group are innermost TMA coordinates of K-contiguous operands
+    if (!a.trans_a && (a.g_a_k * rf.elt) % 16 != 0) { set_error("group K stride of A must be a multiple of 16 bytes"); return CATCOC_E_ALIGNMENT; }
+    if (a.trans_b && (a.g_b_k * rf.elt) % 16 != 0) { set_error("group K stride of B must be a multiple of 16 bytes"); return CATCOC_E_ALIGNMENT; }
+    if (a.trans_a && (a.g_a_row_back * rf.elt) % 16 != 0) { set_error("group row stride of a transposed A must be a multiple of 16 bytes"); return CATCOC_E_ALIGNMENT; }
+    // a group whose K range is followed by another group's data must end on an MMA boundary,
+    // or the last MMA would multiply into the neighbour's elements
+    if ((a.g_a_k > 0 || a.g_b_k > 0) && (a.K % rf.umma_k) != 0) {
+      set_error("K per group (%d) must be a multiple of %d when groups are stacked along K", a.K, rf.umma_k);
+      return CATCOC_E_ALIGNMENT;
+    }
+    if (static_cast<int64_t>(a.num_groups - 1) * a.g_a_k >= a_k ||
+        static_cast<int64_t>(a.num_groups - 1) * a.g_b_k >= b_k) {
+      set_error("the last group's K origin lies outside the stored operands");
+      return CATCOC_E_BAD_ARG;
+    }
+    p->num_groups = a.num_groups;
+    p->group_ends = a.group_ends;
+    p->group_rows = a.group_rows;
+    p->g_a_row_back = a.g_a_row_back;
+    p->g_a_k = a.g_a_k;
+    p->g_b_row = a.g_b_row;
+    p->g_b_k = a.g_b_k;
+    p->g_nvec = a.g_nvec;
+  }
+
   // ---- operands ----
   // TMA alignment of tile origins: the innermost TMA coordinate must be a multiple of 16 bytes.
   // It is the tile's first row for an A stored [K, M] and its first column for a B stored
@@ -334,23 +393,23 @@ int catcoc_build_params(const CatcocOpArgs* args, FusedParams* p, int* kind_out,
       if (p->gathered[r] == nullptr || p->gflags[r] == nullptr) { set_error("allgather: missing peer buffers"); return CATCOC_E_BAD_ARG; }
     }
   } else if (!a.trans_a) {
-    rc = encode_2d(&p->tm_a, a.a, rf.elt, rf.dt, a.M, a.K, a.lda, rf.bk, kBM);
+    rc = encode_2d(&p->tm_a, a.a, rf.elt, rf.dt, a_rows, a_k, a.lda, rf.bk, kBM);
     if (rc != 0) return rc;
-  } else if (a.M % per128 == 0) {
-    rc = encode_3d_blocks(&p->tm_a, a.a, rf.elt, rf.dt, a.K, a.M, a.lda, rf.bk, kBM / per128);
+  } else if (a_rows % per128 == 0) {
+    rc = encode_3d_blocks(&p->tm_a, a.a, rf.elt, rf.dt, a_k, a_rows, a.lda, rf.bk, kBM / per128);
     if (rc != 0) return rc;
     p->a_3d = 1;
   } else {
-    rc = encode_2d(&p->tm_a, a.a, rf.elt, rf.dt, a.K, a.M, a.lda, per128, rf.bk);
+    rc = encode_2d(&p->tm_a, a.a, rf.elt, rf.dt, a_k, a_rows, a.lda, per128, rf.bk);
     if (rc != 0) return rc;
   }
   if (a.trans_b) {
-    rc = encode_2d(&p->tm_b, a.b, rf.elt, rf.dt, a.N, a.K, a.ldb, rf.bk, pair ? bn / 2 : bn);
-  } else if (a.N % per128 == 0) {
-    rc = encode_3d_blocks(&p->tm_b, a.b, rf.elt, rf.dt, a.K, a.N, a.ldb, rf.bk, (pair ? bn / 2 : bn) / per128);
+    rc = encode_2d(&p->tm_b, a.b, rf.elt, rf.dt, b_n, b_k, a.ldb, rf.bk, pair ? bn / 2 : bn);
+  } else if (b_n % per128 == 0) {
+    rc = encode_3d_blocks(&p->tm_b, a.b, rf.elt, rf.dt, b_k, b_n, a.ldb, rf.bk, (pair ? bn / 2 : bn) / per128);
     p->b_3d = 1;
   } else {
-    rc = encode_2d(&p->tm_b, a.b, rf.elt, rf.dt, a.K, a.N, a.ldb, per128, rf.bk);
+    rc = encode_2d(&p->tm_b, a.b, rf.elt, rf.dt, b_k, b_n, a.ldb, per128, rf.bk);
   }
   if (rc != 0) return rc;
 
@@ -387,7 +446,17 @@ int catcoc_build_params(const CatcocOpArgs* args, FusedParams* p, int* kind_out,
   p->scale_m = a.scale_m;
   p->scale_n = a.scale_n;
   p->bias = a.bias;
-  if (a.bias != nullptr && rf.kind != KIND_I8) { set_error("bias is only supported for int8 operands"); return CATCOC_E_UNSUPPORTED; }
+  if (a.bias != nullptr && rf.kind != KIND_I8) { set_error("the int32 bias is only supported for int8 operands"); return CATCOC_E_UNSUPPORTED; }
+  if (a.affine) {
+    if (a.out_fmt == CATCOC_FMT_S32) { set_error("alpha / beta / fp32 bias need a floating-point output"); return CATCOC_E_UNSUPPORTED; }
+    if (a.c_src != nullptr && a.ldc_src < a.N) { set_error("ldc_src (%lld) < N (%d)", static_cast<long long>(a.ldc_src), a.N); return CATCOC_E_BAD_ARG; }
+    p->affine = 1;
+    p->alpha = a.alpha;
+    p->beta = a.beta;
+    p->c_src = (a.beta != 0.0f) ? a.c_src : nullptr;
+    p->ldc_src = a.ldc_src;
+    p->bias_f = a.bias_f;
+  }
 
   p->epoch_ptr = a.epoch_ptr;
   p->cta_counter = a.cta_counter;
@@ -405,7 +474,14 @@ int catcoc_build_params(const CatcocOpArgs* args, FusedParams* p, int* kind_out,
   grid = imin(grid, sms);
   const int per_tile = pair ? 2 : 1;
   // All-gather needs every CTA's communication warps; otherwise never launch idle CTAs.
-  if (!(fused && a.mode == CATCOC_MODE_AG)) grid = imin(grid, p->sched.total_tiles * per_tile);
+  int tiles_bound = p->sched.total_tiles;
+  if (grouped) {
+    // group extents are device data: bound the tile count by full tiles + one ragged tile per group
+    const int64_t mt = static_cast<int64_t>(a.M / bm) + a.num_groups;
+    const int64_t nt = (a.N + bn - 1) / bn;
+    tiles_bound = static_cast<int>(mt * nt > (1 << 30) ? (1 << 30) : mt * nt);
+  }
+  if (!(fused && a.mode == CATCOC_MODE_AG)) grid = imin(grid, tiles_bound * per_tile);
   if (pair) {
     grid = imin(grid, 2 * max_active_pairs(rf.kind));
     grid &= ~1;

@@ -5,7 +5,9 @@ building block for unit tests and the probe used to measure the GEMM-only gap to
 It covers the plain kernels of the reference's GEMM template library that the fused ops
 rely on: basic matmul, matmul with int32 bias and int8 matmul with per-token / per-channel
 dequantisation (3rdparty/catlass/include/catlass/gemm/kernel/basic_matmul.hpp:105-137,
-matmul_bias.hpp, quant_matmul.hpp).
+matmul_bias.hpp, quant_matmul.hpp), and carries the affine epilogue
+``alpha * A @ B + beta * C + bias`` (3rdparty/catlass/include/catlass/epilogue/block/
+block_epilogue_gemm.hpp) that :mod:`.blas` builds the rest of that catalogue on.
 """
 from __future__ import annotations
 
@@ -22,18 +24,30 @@ def matmul(a: torch.Tensor, b: torch.Tensor, *, trans_a: bool = False, trans_b: 
            out: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None,
            scale_m: Optional[torch.Tensor] = None, scale_n: Optional[torch.Tensor] = None,
            bias: Optional[torch.Tensor] = None, tiling: Optional[TilingConfig] = None,
-           trace: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """``out = A @ B`` with fp32 (int32 for int8) accumulation.
+           trace: Optional[torch.Tensor] = None, alpha: float = 1.0, beta: float = 0.0,
+           c: Optional[torch.Tensor] = None, bias_f32: Optional[torch.Tensor] = None,
+           _group: Optional[dict] = None) -> torch.Tensor:
+    """``out = alpha * (A @ B) + beta * C + bias_f32`` with fp32 (int32 for int8) accumulation.
 
     ``a`` is stored ``[M, K]`` (``[K, M]`` with ``trans_a``), ``b`` is stored ``[K, N]``
     (``[N, K]`` with ``trans_b``). For int8 / fp8 operands ``scale_m`` (fp32 ``[M]``) and
     ``scale_n`` (fp32 ``[N]``) dequantise in the epilogue, ``bias`` (int32 ``[N]``, int8 only)
-    is added to the accumulator first.
+    is added to the accumulator first. ``c`` (same dtype and shape as the output; it may be the
+    output itself) and ``bias_f32`` (fp32 ``[N]``) enter after the dequantisation, in fp32,
+    before the single rounding to the output dtype.
+
+    ``_group`` is the group walk used by :mod:`.blas` (grouped, batched and split-K products in
+    one launch): a dict with the logical ``m, n, k`` of the launch and the ``OpArgs`` group
+    fields; ``a`` and ``b`` are then the stacked 2-D storages.
     """
-    dev = cm.require_cuda(a, b, out, scale_m, scale_n, bias)
+    dev = cm.require_cuda(a, b, out, scale_m, scale_n, bias, c, bias_f32)
     if a.dtype != b.dtype:
         raise TypeError("A and B must share a dtype (got %s, %s)" % (a.dtype, b.dtype))
-    m, n, k = cm.logical_shape(a, trans_a, b, trans_b)
+    if _group is not None:
+        m, n, k = _group["m"], _group["n"], _group["k"]
+    else:
+        m, n, k = cm.logical_shape(a, trans_a, b, trans_b)
+    n_vec = n * (_group["num_groups"] if _group is not None and _group.get("g_nvec") else 1)
     if out_dtype is None:
         if out is not None:
             out_dtype = out.dtype
@@ -52,6 +66,12 @@ def matmul(a: torch.Tensor, b: torch.Tensor, *, trans_a: bool = False, trans_b: 
     if a.dtype != torch.int8 and out_dtype == torch.int32:
         raise ValueError("int32 output needs int8 operands")
 
+    affine = (alpha != 1.0) or (beta != 0.0 and c is not None) or (bias_f32 is not None)
+    if affine and out_dtype == torch.int32:
+        raise ValueError("alpha / beta / bias_f32 need a floating-point output")
+    if c is not None and beta != 0.0:
+        if c.shape != (m, n) or c.dtype != out_dtype or c.stride(-1) != 1:
+            raise ValueError("c must be a row-major [%d, %d] %s tensor" % (m, n, out_dtype))
     if tiling is None:
         from ..tiling.chooser import choose
         tiling = choose("matmul", m, n, k, 1, a.dtype)
@@ -69,12 +89,26 @@ def matmul(a: torch.Tensor, b: torch.Tensor, *, trans_a: bool = False, trans_b: 
         args.partial_fmt = args.out_fmt
         cm.fill_tiling(args, tiling)
         args.rank, args.W = 0, 1
-        for name, t, length, dt in (("scale_m", scale_m, m, torch.float32), ("scale_n", scale_n, n, torch.float32),
-                                    ("bias", bias, n, torch.int32)):
+        for name, t, length, dt in (("scale_m", scale_m, m, torch.float32), ("scale_n", scale_n, n_vec, torch.float32),
+                                    ("bias", bias, n_vec, torch.int32), ("bias_f", bias_f32, n_vec, torch.float32)):
             if t is not None:
                 if t.dtype != dt or t.numel() != length or not t.is_contiguous():
                     raise ValueError("%s must be a contiguous %s tensor of %d elements" % (name, dt, length))
                 setattr(args, name, t.data_ptr())
+        if affine:
+            args.affine = 1
+            args.alpha, args.beta = float(alpha), float(beta)
+            if c is not None and beta != 0.0:
+                args.c_src, args.ldc_src = c.data_ptr(), c.stride(0)
+        if _group is not None:
+            for key in ("num_groups", "group_rows", "a_rows_total", "a_k_total", "b_n_total", "b_k_total",
+                        "g_a_row_back", "g_a_k", "g_b_row", "g_b_k", "g_nvec"):
+                setattr(args, key, int(_group.get(key, 0)))
+            ends = _group.get("group_ends")
+            if ends is not None:
+                if ends.dtype != torch.int32 or not ends.is_contiguous() or ends.numel() != args.num_groups or ends.device != dev:
+                    raise ValueError("group_ends must be a contiguous int32 device tensor of num_groups elements")
+                args.group_ends = ends.data_ptr()
         args.status = cm.local_status(dev).data_ptr()
         if trace is not None:  # int64[16] device tensor: per-role cycle counters (see params.h)
             args.trace = trace.data_ptr()
