@@ -11,6 +11,7 @@ import os
 import shutil
 import subprocess
 import sys
+from concurrent.futures import ThreadPoolExecutor
 from pathlib import Path
 
 PKG_DIR = Path(__file__).resolve().parent
@@ -21,6 +22,13 @@ STAMP_PATH = LIB_DIR / "build.stamp"
 
 SOURCES = [
     "kernels/launch.cu",
+    "kernels/inst/f16_single.cu",
+    "kernels/inst/f16_pair.cu",
+    "kernels/inst/i8_single.cu",
+    "kernels/inst/i8_pair.cu",
+    "kernels/inst/f8_single.cu",
+    "kernels/inst/f8_pair.cu",
+    "kernels/inst/mx_single.cu",
     "kernels/shmem_prims.cu",
     "kernels/no_alloc.cu",
     "kernels/blas_prims.cu",
@@ -33,7 +41,6 @@ NVCC_FLAGS = [
     "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=default",
     "--expt-relaxed-constexpr",
-    "-shared",
 ]
 
 
@@ -68,24 +75,42 @@ def is_current() -> bool:
     return LIB_PATH.exists() and STAMP_PATH.exists() and STAMP_PATH.read_text().strip() == source_digest()
 
 
+def _compile_one(src: Path, obj: Path, verbose: bool) -> str:
+    cmd = [_nvcc(), *NVCC_FLAGS, *_extra_flags(), "-I", str(CSRC / "include"), "-c", str(src), "-o", str(obj)]
+    if verbose:
+        cmd += ["-Xptxas", "-v"]
+    proc = subprocess.run(cmd, capture_output=True, text=True)
+    if proc.returncode != 0:
+        raise RuntimeError("nvcc failed:\n%s\n%s" % (" ".join(cmd), proc.stderr[-8000:]))
+    return proc.stderr
+
+
 def build(force: bool = False, verbose: bool = False) -> Path:
-    """Compile every CUDA source of the package into one shared library (sm_100a)."""
+    """Compile every CUDA source of the package for sm_100a and link one shared library. The
+    translation units (one per kernel flavour) compile in parallel."""
     if not force and is_current():
         return LIB_PATH
     LIB_DIR.mkdir(exist_ok=True)
-    cmd = [_nvcc(), *NVCC_FLAGS, *_extra_flags(), "-I", str(CSRC / "include")]
-    if verbose:
-        cmd += ["-Xptxas", "-v"]
-    cmd += [str(s) for s in _existing_sources()]
+    obj_dir = LIB_DIR / ("obj%d" % os.getpid())
+    obj_dir.mkdir(exist_ok=True)
+    sources = _existing_sources()
+    objs = [obj_dir / (s.relative_to(CSRC).as_posix().replace("/", "_") + ".o") for s in sources]
     tmp = LIB_PATH.with_suffix(".so.tmp%d" % os.getpid())
-    cmd += ["-o", str(tmp)]
-    proc = subprocess.run(cmd, capture_output=True, text=True)
-    if proc.returncode != 0:
+    try:
+        workers = max(1, min(len(sources), os.cpu_count() or 1, int(os.environ.get("CATCOC_BUILD_JOBS", "8"))))
+        with ThreadPoolExecutor(max_workers=workers) as pool:
+            logs = list(pool.map(lambda so: _compile_one(so[0], so[1], verbose), zip(sources, objs)))
+        if verbose:
+            sys.stderr.write("".join(logs))
+        link = [_nvcc(), "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-Xcompiler", "-fPIC",
+                *[str(o) for o in objs], "-o", str(tmp)]
+        proc = subprocess.run(link, capture_output=True, text=True)
+        if proc.returncode != 0:
+            raise RuntimeError("link failed:\n%s\n%s" % (" ".join(link), proc.stderr[-8000:]))
+        os.replace(tmp, LIB_PATH)
+    finally:
         tmp.unlink(missing_ok=True)
-        raise RuntimeError("nvcc failed:\n%s\n%s" % (" ".join(cmd), proc.stderr[-8000:]))
-    if verbose:
-        sys.stderr.write(proc.stderr)
-    os.replace(tmp, LIB_PATH)
+        shutil.rmtree(obj_dir, ignore_errors=True)
     STAMP_PATH.write_text(source_digest())
     return LIB_PATH
 

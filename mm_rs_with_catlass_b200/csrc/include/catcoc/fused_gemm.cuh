@@ -38,7 +38,8 @@ constexpr int kBM = 128;               // rows per CTA == TMEM lanes
 constexpr int kMaxBN = 256;            // tile cols upper bound == TMEM columns per accumulator
 constexpr int kABytes = kBM * 128;     // A stage: 128 rows x 128 B (K-major) or the MN-major equal
 constexpr int kEpiWarps = 4;
-constexpr int kEpiStageBytes = 32 * 128;           // per epilogue warp: 32 rows x 128 B
+constexpr int kEpiWinBytes = 32 * 128;             // one staged window: 32 rows x 128 B
+constexpr int kEpiStageBytes = 2 * kEpiWinBytes;   // per epilogue warp: two windows (one may still feed a TMA store)
 constexpr int kThreads = 256;
 constexpr int kTmemCols = 512;
 constexpr int kMaxStages = 6;
@@ -228,9 +229,12 @@ CATCOC_DEVICE TileInfo walk_tile(const FusedParams& p, int t, GroupWalk& w) {
 // ---------------------------------------------------------------------------------------
 // The kernel
 // ---------------------------------------------------------------------------------------
-template <int KIND, bool CTA2>
+template <int KIND, bool CTA2, int EPI>
 __global__ void __launch_bounds__(kThreads, 1)
 fused_gemm_kernel(const __grid_constant__ FusedParams p) {
+  // Epilogue variant (see EpiVariant in params.h): stages a launch cannot need are compiled out.
+  constexpr bool kReduce = (EPI >= EPI_REDUCE);   // reduce-scatter / all-reduce: peers' partials, pushes, stamps
+  constexpr bool kScale = (EPI == EPI_FULL);      // int32 bias, dequantisation, alpha / beta / C / fp32 bias
   using G = Geo<CTA2>;
   constexpr int kStages = G::kStages;
   constexpr int kStageBytes = G::kStageBytes;
@@ -282,6 +286,7 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
     ptx::mbar_fence_init();
     ptx::prefetch_tmap(&p.tm_a);
     ptx::prefetch_tmap(&p.tm_b);
+    if (p.out_tma) ptx::prefetch_tmap(&p.tm_out);
   }
   if (warp == 1) {
     if (CTA2) {
@@ -583,12 +588,13 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
     // [32q, 32q+32) end to end, including their stamps, so a warp that gives up on a wait
     // cannot strand the others at a barrier.
     const int q = warp & 3;                 // TMEM lane quarter this warp may read
-    const uint32_t stg = ptx::smem_u32(epi_stage + (warp - 2) * kEpiStageBytes);
+    const uint32_t stg_base = ptx::smem_u32(epi_stage + (warp - 2) * kEpiStageBytes);
+    uint32_t win_count = 0;   // windows staged so far: picks the staging buffer
     const int row_base = sub * kBM + q * 32;   // first tile row of this warp
     const int row_in_tile = row_base + lane;
     const int qid = sub * 4 + q;               // quarter index inside the tile
     const bool is_int = (KIND == KIND_I8);
-    const bool dequant = (p.scale_m != nullptr) || (p.scale_n != nullptr);
+    const bool dequant = kScale && ((p.scale_m != nullptr) || (p.scale_n != nullptr));
     const int pfmt = p.partial_fmt;
     const int pelt = fmt_bytes(pfmt);
     int acc = 0;
@@ -596,18 +602,19 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
     bool ok = true;
     const bool tr = (p.trace != nullptr) && lane == 0 && q == 0;
     unsigned long long c_full = 0, c_work = 0, c_peer = 0, c_pub = 0, c_own = 0;
+    unsigned long long c_tld = 0, c_cvt = 0, c_flush = 0;
     Tick tick(tr);
 
     GroupWalk walk = group_walk_begin(p);
     for (int t = worker; ok && t < total_tiles; t += num_workers) {
       const TileInfo ti = walk_tile(p, t, walk);
-      const bool own = !fused || (p.mode == MODE_AG) || (ti.seg == p.rank);
-      const bool reduce_here = fused && own && (p.mode == MODE_RS || p.mode == MODE_AR);
+      const bool own = !kReduce || !fused || (p.mode == MODE_AG) || (ti.seg == p.rank);
+      const bool reduce_here = kReduce && fused && own && (p.mode == MODE_RS || p.mode == MODE_AR);
       const int st_fmt = own ? p.out_fmt : pfmt;   // format of what this tile's epilogue stores
       const int st_elt = fmt_bytes(st_fmt);
       const int rows_valid = max(0, min(32, ti.rows - row_base));
       const int nvec_off = grouped ? ti.seg * p.g_nvec : 0;   // this group's per-column vectors
-      const bool affine = (p.affine != 0) && own;
+      const bool affine = kScale && (p.affine != 0) && own;
 
       tick.lap(c_work);
       if (reduce_here) {
@@ -651,7 +658,7 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
         pitch = static_cast<int64_t>(BN) * st_elt;
         base = p.stage[ti.seg] + stage_slot_offset(sched, st_elt, parity, p.rank, ti.tile_in_seg) +
                static_cast<int64_t>(row_base) * pitch;
-      } else if (fused && p.mode == MODE_AR) {
+      } else if (kReduce && fused && p.mode == MODE_AR) {
         pitch = p.ldc * st_elt;
         off = static_cast<int64_t>(parity) * p.ar_out_parity_bytes +
               (static_cast<int64_t>(ti.m0 + row_base) * p.ldc + ti.n0) * st_elt;
@@ -674,15 +681,35 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
       const int last_group = min(groups, ceil_div(ti.cols, 32)) - 1;
       bool released = false;
 
+      // Finished windows of a local output leave through the TMA store unit (one instruction
+      // per 4 KiB, the warp moves on at once). TMA clips at the tensor's edges only, so a short
+      // row range that ends inside the output (a group or segment boundary) takes the plain stores.
+      const bool tma_out = (p.out_tma != 0) && own && base != nullptr &&
+                           (rows_valid == 32 || (!grouped && !fused));
+
       for (int win = 0; win < nwin; ++win) {
         if (win * groups_per_win * 32 >= ti.cols) break;
+        // the store that read this staging buffer two windows ago must be done with it
+        const uint32_t stg = stg_base + (win_count & 1u) * kEpiWinBytes;
+        ++win_count;
+        if (p.out_tma) {
+          if (lane == 0) {
+            // a window sent by TMA leaves one younger store in flight; a window sent by plain
+            // stores adds no group, so everything older has to be drained
+            if (tma_out) ptx::bulk_wait_group_read<1>();
+            else ptx::bulk_wait_group_read<0>();
+          }
+          __syncwarp();
+        }
         for (int h = 0; h < groups_per_win; ++h) {
           const int g = win * groups_per_win + h;
           const int col0 = g * 32;
           if (col0 >= ti.cols) break;
           uint32_t v[32];
+          tick.lap(c_pub);
           ptx::tmem_ld_32x32b_x32(taddr + static_cast<uint32_t>(col0), v);
           ptx::tcgen05_wait_ld();
+          tick.lap(c_tld);
           if (g == last_group) {
             // every TMEM read of this tile is done: hand the accumulator back to the MMA warp
             ptx::tcgen05_fence_before();
@@ -694,7 +721,7 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
             released = true;
           }
 
-          if (is_int && p.bias != nullptr) {
+          if (kScale && is_int && p.bias != nullptr) {
 #pragma unroll
             for (int j = 0; j < 32; ++j) {
               const int c = ti.n0 + col0 + j;
@@ -703,7 +730,7 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
             }
           }
 
-          if (reduce_here && row_in_tile < ti.rows) {
+          if (kReduce && reduce_here && row_in_tile < ti.rows) {
             // fold the peers' partials in a fixed source order => deterministic sum. The loads of
             // two sources are issued back to back before their adds to keep more bytes in flight.
             const uint8_t* sbase = p.stage[p.rank] + (static_cast<int64_t>(row_in_tile) * BN + col0) * pelt;
@@ -775,7 +802,7 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
 #pragma unroll
               for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
             }
-            if (dequant && own) {
+            if (kScale && dequant && own) {
               const int grow = ti.m0 + row_in_tile;
               const float sm =
                   (p.scale_m != nullptr && grow < sched.M) ? __ldg(p.scale_m + grow) : 1.0f;
@@ -787,7 +814,7 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
                 f[j] = f[j] * sn * sm;
               }
             }
-            if (affine) {
+            if (kScale && affine) {
               // out = alpha * acc + beta * C + bias: each lane walks its own row of C
               const float alpha = p.alpha, beta = p.beta;
               const int cvalid = min(32, ti.cols - col0);
@@ -861,15 +888,29 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
           }
         }
         __syncwarp();
+        tick.lap(c_cvt);
         {
           const int per_win = 128 / st_elt;
           const int cols_valid = min(per_win, ti.cols - win * per_win);
           const int64_t wb = static_cast<int64_t>(win) * 128;
-          flush_staged(stg, lane, base != nullptr ? base + wb : nullptr, pitch, rows_valid,
-                       cols_valid, st_elt, vec_ok, mc != nullptr ? mc + wb : nullptr, peer_bases,
-                       off + wb, p.rank, p.W);
+          if (tma_out) {
+            if (rows_valid > 0) {
+              ptx::fence_proxy_async_smem();   // the staged bytes become visible to the TMA unit
+              __syncwarp();
+              if (lane == 0) {
+                ptx::tma_store_2d(&p.tm_out, stg, ti.n0 + win * per_win,
+                                  static_cast<int>(ti.m0 + row_base - p.out_row_shift));
+                ptx::bulk_commit_group();
+              }
+            }
+          } else {
+            flush_staged(stg, lane, base != nullptr ? base + wb : nullptr, pitch, rows_valid,
+                         cols_valid, st_elt, vec_ok, mc != nullptr ? mc + wb : nullptr, peer_bases,
+                         off + wb, p.rank, p.W);
+          }
         }
         __syncwarp();
+        tick.lap(c_flush);
       }
       if (reduce_here) tick.lap(c_own);
       if (!released) {
@@ -883,7 +924,7 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
       }
 
       // ---- publish this warp's quarter of the tile ----
-      if (fused && (p.mode == MODE_RS || p.mode == MODE_AR) && (!own || p.mode == MODE_AR)) {
+      if (kReduce && fused && (p.mode == MODE_RS || p.mode == MODE_AR) && (!own || p.mode == MODE_AR)) {
         // Data stores of all 32 lanes happen-before lane 0's release through the warp barrier;
         // the release is cumulative, so one system-scope release by one lane publishes them all.
         __syncwarp();
@@ -911,14 +952,18 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
       if (acc == 0) acc_phase ^= 1u;
     }
 
+    // every TMA store of this warp has to be performed before the kernel ends
+    if (p.out_tma && lane == 0) ptx::bulk_wait_group_all();
+    __syncwarp();
     tick.lap(c_work);
     if (tr) {
       atomicAdd(p.trace + 5, c_full); atomicAdd(p.trace + 6, c_work); atomicAdd(p.trace + 7, c_peer);
       atomicAdd(p.trace + 9, c_pub); atomicAdd(p.trace + 10, c_own);
+      atomicAdd(p.trace + 11, c_tld); atomicAdd(p.trace + 12, c_cvt); atomicAdd(p.trace + 13, c_flush);
     }
 
     // all-reduce tail: this rank's output is complete only when every owner's tiles landed
-    if (fused && p.mode == MODE_AR && ok && !*abort_flag) {
+    if (kReduce && fused && p.mode == MODE_AR && ok && !*abort_flag) {
       const int et = (warp - 2) * 32 + lane;
       const int nstamps = sched.total_tiles * qpt;
       for (int j = blockIdx.x + et * gridDim.x; j < nstamps; j += gridDim.x * kEpiWarps * 32) {

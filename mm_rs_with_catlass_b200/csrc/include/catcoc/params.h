@@ -29,6 +29,13 @@ enum ElemFmt : int { FMT_F16 = 0, FMT_BF16 = 1, FMT_F32 = 2, FMT_S32 = 3 };
 
 CATCOC_HD int fmt_bytes(int fmt) { return (fmt == FMT_F16 || fmt == FMT_BF16) ? 2 : 4; }
 
+// Compile-time epilogue variants of the kernel; a launch picks the leanest one that covers it.
+enum EpiVariant {
+  EPI_PLAIN = 0,    // convert and store (local GEMM, all-gather GEMM)
+  EPI_REDUCE = 1,   // + owner-side fold of the peers' partial tiles, pushes and stamps (RS / AR)
+  EPI_FULL = 2,     // + int32 bias, per-row / per-column scales, alpha / beta / C / fp32 bias
+};
+
 // Error codes written to status[0] by a kernel that gave up on a wait.
 enum StatusCode : uint32_t {
   STATUS_OK = 0,
@@ -48,6 +55,7 @@ struct alignas(64) FusedParams {
   CUtensorMap tm_a;          // A operand (AG: this rank's shard)
   CUtensorMap tm_a_gath[2];  // AG: gathered A, one map per parity buffer
   CUtensorMap tm_b;
+  CUtensorMap tm_out;  // `out` as [rows, N] with a 32-row x 128-byte box (valid when out_tma)
 
   TileSched sched;
   int K;
@@ -65,6 +73,7 @@ struct alignas(64) FusedParams {
   int64_t ldc;
   int out_fmt;      // ElemFmt of `out`
   int out_vec_ok;   // 1 when 16-byte vector stores to `out` are aligned
+  int out_tma;      // 1 when tm_out describes `out`: finished 32-row x 128-byte windows leave by TMA store
   int64_t out_row_shift;  // subtracted from the tile's global row to index `out` (RS: seg begin)
 
   // partial tiles that cross NVLink
@@ -130,6 +139,8 @@ struct alignas(64) FusedParams {
   // [0] producer waits on empty   [1] producer issue     [2] MMA waits on full
   // [3] MMA waits on acc_empty    [4] MMA issue          [5] epilogue waits on acc_full
   // [6] epilogue work             [7] epilogue waits on peers' stamps   [8] CTA lifetime
+  // [9] epilogue publish / rest   [10] owner-side reduce
+  // [11] epilogue TMEM loads      [12] convert + stage to shared         [13] flush to global / peers
   unsigned long long* trace;
 };
 

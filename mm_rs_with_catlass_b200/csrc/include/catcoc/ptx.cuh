@@ -135,6 +135,23 @@ CATCOC_DEVICE void tma_load_2d(void* smem_dst, const void* tmap, uint64_t* bar, 
       : "memory");
 }
 
+// Tiled store shared -> global of one box (bulk-group completion). x (elements) times the element
+// size must be a multiple of 16 bytes and no coordinate may be negative; the part of the box
+// that lies outside the tensor is not written. The issuing thread owns the bulk group.
+CATCOC_DEVICE void tma_store_2d(const void* tmap, uint32_t smem_src, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+               ::"l"(reinterpret_cast<uint64_t>(tmap)), "r"(smem_src), "r"(x), "r"(y)
+               : "memory");
+}
+CATCOC_DEVICE void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// Waits until at most N of this thread's bulk groups still READ their shared-memory source.
+template <int N>
+CATCOC_DEVICE void bulk_wait_group_read() {
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+// Waits until every bulk group of this thread has completed (its writes are performed).
+CATCOC_DEVICE void bulk_wait_group_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+
 // 3-D form: used to fetch an M/N-contiguous operand tile (several 128-byte-wide column blocks
 // x bk rows) with one instruction; x must again be a multiple of 16 bytes.
 CATCOC_DEVICE void tma_load_3d(void* smem_dst, const void* tmap, uint64_t* bar, int x, int y, int z) {

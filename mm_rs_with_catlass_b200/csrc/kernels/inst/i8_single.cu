@@ -1,0 +1,4 @@
+// Instantiates the fused kernel for one operand kind and CTA flavour (see kernel_inst.cuh).
+#include "catcoc/kernel_inst.cuh"
+
+CATCOC_DEFINE_UNIT_2(i8_single, catcoc::KIND_I8, false)

@@ -8,6 +8,7 @@
 #include <mutex>
 #include "catcoc/capi.h"
 #include "catcoc/fused_gemm.cuh"
+#include "catcoc/kernel_inst.cuh"
 #include "catcoc/host_util.h"
 
 namespace catcoc {
@@ -72,6 +73,15 @@ static int encode_2d(CUtensorMap* tm, const void* base, int elt_bytes, CUtensorM
     return CATCOC_E_DRIVER;
   }
   return CATCOC_OK;
+}
+
+// CATCOC_OUT_TMA=0 keeps every output on plain vector stores (for A/B measurements).
+static bool out_tma_enabled() {
+  static const bool on = [] {
+    const char* e = getenv("CATCOC_OUT_TMA");
+    return !(e != nullptr && e[0] == '0');
+  }();
+  return on;
 }
 
 static int sm_count(int device) {
@@ -436,6 +446,16 @@ int catcoc_build_params(const CatcocOpArgs* args, FusedParams* p, int* kind_out,
     if (a.out == nullptr) { set_error("null output"); return CATCOC_E_BAD_ARG; }
     p->out_vec_ok = (((a.ldc * oelt) & 15) == 0 && (reinterpret_cast<uintptr_t>(a.out) & 15) == 0) ? 1 : 0;
   }
+  // A local output leaves by TMA stores (32-row x 128-byte boxes, same swizzle as the staging
+  // buffer) when its base and pitch allow a tensor map; the plain-store path covers the rest.
+  if (!(fused && a.mode == CATCOC_MODE_AR) && p->out_vec_ok && out_tma_enabled()) {
+    const int64_t rows_out = (fused && a.mode == CATCOC_MODE_RS) ? p->sched.seg_len : a.M;
+    const CUtensorMapDataType odt = a.out_fmt == CATCOC_FMT_F16    ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
+                                    : a.out_fmt == CATCOC_FMT_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                    : a.out_fmt == CATCOC_FMT_F32  ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                                                                   : CU_TENSOR_MAP_DATA_TYPE_INT32;
+    if (encode_2d(&p->tm_out, a.out, oelt, odt, rows_out, a.N, a.ldc, 128 / oelt, 32) == CATCOC_OK) p->out_tma = 1;
+  }
   if (fused && (a.mode == CATCOC_MODE_RS || a.mode == CATCOC_MODE_AR)) {
     for (int r = 0; r < a.W; ++r) {
       p->stage[r] = static_cast<uint8_t*>(a.stage[r]);
@@ -494,46 +514,29 @@ int catcoc_build_params(const CatcocOpArgs* args, FusedParams* p, int* kind_out,
   return CATCOC_OK;
 }
 
-template <int KIND, bool CTA2>
-static cudaError_t set_smem_attr() {
-  return cudaFuncSetAttribute(fused_gemm_kernel<KIND, CTA2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                              Geo<CTA2>::kSmemBytes);
+static const inst::Unit* unit_for(int kind, bool pair) {
+  switch (kind) {
+    case KIND_F16: return pair ? &inst::unit_f16_pair() : &inst::unit_f16_single();
+    case KIND_I8: return pair ? &inst::unit_i8_pair() : &inst::unit_i8_single();
+    case KIND_F8: return pair ? &inst::unit_f8_pair() : &inst::unit_f8_single();
+    case KIND_MX: return pair ? nullptr : &inst::unit_mx_single();
+    default: return nullptr;
+  }
 }
 
 static cudaError_t prepare_kernels() {
   static std::once_flag once;
   static cudaError_t err = cudaSuccess;
   std::call_once(once, [] {
-    cudaError_t e;
-    if ((e = set_smem_attr<KIND_F16, false>()) != cudaSuccess) err = e;
-    if ((e = set_smem_attr<KIND_I8, false>()) != cudaSuccess) err = e;
-    if ((e = set_smem_attr<KIND_F8, false>()) != cudaSuccess) err = e;
-    if ((e = set_smem_attr<KIND_F16, true>()) != cudaSuccess) err = e;
-    if ((e = set_smem_attr<KIND_I8, true>()) != cudaSuccess) err = e;
-    if ((e = set_smem_attr<KIND_F8, true>()) != cudaSuccess) err = e;
-    if ((e = set_smem_attr<KIND_MX, false>()) != cudaSuccess) err = e;
+    for (int kind = KIND_F16; kind <= KIND_MX; ++kind)
+      for (int pair = 0; pair < 2; ++pair) {
+        const inst::Unit* u = unit_for(kind, pair != 0);
+        if (u == nullptr) continue;
+        const cudaError_t e = u->prepare();
+        if (e != cudaSuccess) err = e;
+      }
   });
   return err;
-}
-
-template <int KIND>
-static int query_pairs() {
-  cudaLaunchConfig_t cfg;
-  memset(&cfg, 0, sizeof(cfg));
-  cfg.gridDim = dim3(2, 1, 1);
-  cfg.blockDim = dim3(kThreads, 1, 1);
-  cfg.dynamicSmemBytes = Geo<true>::kSmemBytes;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = 1;
-  int n = 0;
-  if (cudaOccupancyMaxActiveClusters(&n, fused_gemm_kernel<KIND, true>, &cfg) != cudaSuccess || n <= 0) {
-    cudaGetLastError();
-    n = 0;
-  }
-  return n;
 }
 
 // How many 2-CTA clusters of the pair kernel can be resident at once (the persistent grid must
@@ -543,7 +546,7 @@ int max_active_pairs(int kind) {
   if (kind < 0 || kind > 2) return 1;
   if (cached[kind] < 0) {
     if (prepare_kernels() != cudaSuccess) return 1;
-    int n = kind == KIND_F16 ? query_pairs<KIND_F16>() : kind == KIND_I8 ? query_pairs<KIND_I8>() : query_pairs<KIND_F8>();
+    int n = unit_for(kind, true)->max_clusters();
     int device = 0;
     cudaGetDevice(&device);
     if (n <= 0) n = sm_count(device) / 2;
@@ -552,22 +555,11 @@ int max_active_pairs(int kind) {
   return cached[kind];
 }
 
-template <int KIND, bool CTA2>
-static cudaError_t launch_one(const FusedParams& p, int grid, cudaStream_t stream) {
-  cudaLaunchConfig_t cfg;
-  memset(&cfg, 0, sizeof(cfg));
-  cfg.gridDim = dim3(grid, 1, 1);
-  cfg.blockDim = dim3(kThreads, 1, 1);
-  cfg.dynamicSmemBytes = Geo<CTA2>::kSmemBytes;
-  cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
-  if (CTA2) {
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-  }
-  return cudaLaunchKernelEx(&cfg, fused_gemm_kernel<KIND, CTA2>, p);
+// The leanest epilogue variant that covers this launch.
+static int pick_epi(const FusedParams& p) {
+  if (p.scale_m != nullptr || p.scale_n != nullptr || p.bias != nullptr || p.affine != 0) return EPI_FULL;
+  if (p.W > 1 && (p.mode == MODE_RS || p.mode == MODE_AR)) return EPI_REDUCE;
+  return EPI_PLAIN;
 }
 
 int catcoc_launch_params(const FusedParams& p, int kind, int grid, int pair, cudaStream_t stream) {
@@ -576,17 +568,9 @@ int catcoc_launch_params(const FusedParams& p, int kind, int grid, int pair, cud
     set_error("cudaFuncSetAttribute failed: %s", cudaGetErrorString(e));
     return -1000 - static_cast<int>(e);
   }
-  if (pair && kind == KIND_MX) { set_error("block-scaled fp8 has no 2-CTA flavour"); return CATCOC_E_UNSUPPORTED; }
-  if (pair) {
-    e = kind == KIND_F16 ? launch_one<KIND_F16, true>(p, grid, stream)
-        : kind == KIND_I8 ? launch_one<KIND_I8, true>(p, grid, stream)
-                          : launch_one<KIND_F8, true>(p, grid, stream);
-  } else {
-    e = kind == KIND_F16 ? launch_one<KIND_F16, false>(p, grid, stream)
-        : kind == KIND_I8 ? launch_one<KIND_I8, false>(p, grid, stream)
-        : kind == KIND_F8 ? launch_one<KIND_F8, false>(p, grid, stream)
-                          : launch_one<KIND_MX, false>(p, grid, stream);
-  }
+  const inst::Unit* u = unit_for(kind, pair != 0);
+  if (u == nullptr) { set_error("no kernel for kind %d with cta_pair=%d", kind, pair ? 2 : 1); return CATCOC_E_UNSUPPORTED; }
+  e = u->launch(pick_epi(p), p, grid, stream);
   if (e != cudaSuccess) {
     set_error("kernel launch failed: %s", cudaGetErrorString(e));
     return -1000 - static_cast<int>(e);
