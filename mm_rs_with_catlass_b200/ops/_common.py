@@ -66,6 +66,7 @@ class Operand:
     ptr: int
     ld: int
     trans: bool
+    copied: bool = False  # the storage is a fresh padded copy of the caller's data (not reusable)
 
 
 def _tma_legal(t: torch.Tensor) -> bool:
@@ -102,9 +103,23 @@ def as_operand(x: torch.Tensor, trans: bool) -> Operand:
     if x.stride(-1) != 1 and x.stride(0) == 1 and x.shape[0] > 1 and x.shape[1] > 1:
         x = x.t()
         trans = not trans
+    copied = False
     if not _tma_legal(x):
         x = pad_rows(x)
-    return Operand(x, x.data_ptr(), x.stride(0), trans)
+        copied = True
+    return Operand(x, x.data_ptr(), x.stride(0), trans, copied)
+
+
+def tkey(t: Optional[torch.Tensor]):
+    """Identity of a tensor as far as a launch plan is concerned: where it lives and how it is
+    laid out. Two tensors with equal keys give byte-identical kernel arguments."""
+    if t is None:
+        return None
+    return (t.data_ptr(), t.shape, t.stride(), t.dtype)
+
+
+def on_device(device: torch.device) -> bool:
+    return torch.cuda.current_device() == (device.index if device.index is not None else 0)
 
 
 def fill_tiling(args: N.OpArgs, tiling: Optional[TilingConfig]) -> None:
@@ -123,11 +138,21 @@ def default_timeout_ns() -> int:
     return int(float(os.environ.get("CATCOC_TIMEOUT_MS", "10000")) * 1e6)
 
 
-def launch(args: N.OpArgs, device: torch.device) -> None:
-    if not args.timeout_ns:
-        args.timeout_ns = default_timeout_ns()
-    stream = torch.cuda.current_stream(device).cuda_stream
-    N.check(N.lib().catcoc_fused_launch(C.byref(args), C.c_void_p(stream)))
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
+def launch(args: N.OpArgs, device: torch.device, timeout_ns: Optional[int] = None) -> None:
+    """Queues the kernel on the current stream of ``device`` (which must be the current device).
+    The wait budget is re-read on every launch so that a cached argument block follows
+    ``CATCOC_TIMEOUT_MS``."""
+    args.timeout_ns = timeout_ns if timeout_ns is not None else default_timeout_ns()
+    if _raw_stream is not None and device.index is not None:
+        stream = _raw_stream(device.index)
+    else:
+        stream = torch.cuda.current_stream(device).cuda_stream
+    code = N.lib().catcoc_fused_launch(C.byref(args), C.c_void_p(stream))
+    if code < 0:
+        N.check(code)
 
 
 _status_cache = {}

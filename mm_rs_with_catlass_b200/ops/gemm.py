@@ -20,6 +20,14 @@ from ..tiling.config import TilingConfig
 from . import _common as cm
 
 
+# Launch plans of :func:`matmul`: argument blocks keyed by where the operands live and how they
+# are laid out. A plan holds addresses, never tensors, so it keeps no memory alive; an entry can
+# only be hit again by tensors at the same addresses with the same layout, for which the block is
+# exactly what a rebuild would produce. Operands that needed a padded copy are never planned.
+_plans: dict = {}
+_MAX_PLANS = 4096
+
+
 def matmul(a: torch.Tensor, b: torch.Tensor, *, trans_a: bool = False, trans_b: bool = False,
            out: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None,
            scale_m: Optional[torch.Tensor] = None, scale_n: Optional[torch.Tensor] = None,
@@ -40,6 +48,22 @@ def matmul(a: torch.Tensor, b: torch.Tensor, *, trans_a: bool = False, trans_b: 
     one launch): a dict with the logical ``m, n, k`` of the launch and the ``OpArgs`` group
     fields; ``a`` and ``b`` are then the stacked 2-D storages.
     """
+    # Steady state: the same call on the same buffers reuses the argument block built the first
+    # time (a launch plan) and goes straight to the native launch.
+    key = None
+    if _group is None:
+        key = (a.device, cm.tkey(a), cm.tkey(b), trans_a, trans_b, cm.tkey(out), out_dtype, cm.tkey(scale_m),
+               cm.tkey(scale_n), cm.tkey(bias), tiling, None if trace is None else trace.data_ptr(), alpha, beta,
+               cm.tkey(c), cm.tkey(bias_f32))
+        plan = _plans.get(key)
+        if plan is not None and cm.on_device(a.device):
+            args, out_shape, plan_dtype = plan
+            if out is None:
+                out = torch.empty(out_shape, dtype=plan_dtype, device=a.device)
+                args = N.OpArgs.from_buffer_copy(args)   # private copy: the plan itself stays immutable
+                args.out = out.data_ptr()
+            cm.launch(args, a.device)
+            return out
     dev = cm.require_cuda(a, b, out, scale_m, scale_n, bias, c, bias_f32)
     if a.dtype != b.dtype:
         raise TypeError("A and B must share a dtype (got %s, %s)" % (a.dtype, b.dtype))
@@ -113,4 +137,8 @@ def matmul(a: torch.Tensor, b: torch.Tensor, *, trans_a: bool = False, trans_b: 
         if trace is not None:  # int64[16] device tensor: per-role cycle counters (see params.h)
             args.trace = trace.data_ptr()
         cm.launch(args, dev)
+        if key is not None and not oa.copied and not ob.copied:
+            if len(_plans) >= _MAX_PLANS:
+                _plans.clear()
+            _plans[key] = (args, tuple(out.shape), out.dtype)
     return out

@@ -102,6 +102,7 @@ class ShmemContext:
         self._barrier_buf = self.malloc(4 * N.MAX_WORLD)
         self._barrier_epoch = 0
         self.workspaces: Dict[str, object] = {}
+        self.plans: Dict[object, object] = {}   # launch plans of the fused ops (ops/fused.py)
         self.epoch = 0  # host mirror of launch_state[0]: fused launches completed on this context
         self.counters: Dict[str, int] = {"launches": 0, "bytes_pushed": 0, "pad_copies": 0}
 
@@ -247,6 +248,7 @@ class ShmemContext:
         except Exception:
             pass
         self.workspaces.clear()
+        self.plans.clear()
         self._local_bytes = None
         N.lib().catcoc_heap_destroy(self._h)
         self._h = None
