@@ -602,8 +602,22 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
     bool ok = true;
     const bool tr = (p.trace != nullptr) && lane == 0 && q == 0;
     unsigned long long c_full = 0, c_work = 0, c_peer = 0, c_pub = 0, c_own = 0;
-    unsigned long long c_tld = 0, c_cvt = 0, c_flush = 0;
+    unsigned long long c_tld = 0, c_cvt = 0, c_flush = 0, c_tile_own = 0, c_tile_push = 0;
     Tick tick(tr);
+    // A partial tile pushed by TMA store is announced one tile late: the arrival stamp may only
+    // follow the completion of the tile's bulk stores, and waiting for that right away would
+    // stall the warp for a link round trip. `pending_stamp` is the stamp still owed (lane 0).
+    const bool any_tma = (p.out_tma != 0) || (kReduce && p.stage_tma != 0);
+    uint32_t* pending_stamp = nullptr;
+    auto settle_pending = [&]() {
+      // every bulk store of this warp is complete; its stamp can go out
+      if (lane == 0 && pending_stamp != nullptr) {
+        ptx::bulk_wait_group_all();
+        ptx::fence_proxy_async();
+        ptx::st_release_sys_u32(pending_stamp, epoch);
+      }
+      pending_stamp = nullptr;
+    };
 
     GroupWalk walk = group_walk_begin(p);
     for (int t = worker; ok && t < total_tiles; t += num_workers) {
@@ -618,6 +632,8 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
 
       tick.lap(c_work);
       if (reduce_here) {
+        // never wait on a peer while owing one a stamp
+        if (kReduce) settle_pending();
         // the peers' rows [32q, 32q+32) of this tile must have landed in my staging slabs
         if (lane < p.W && lane != p.rank) {
           uint32_t seen = 0;
@@ -644,6 +660,7 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
         break;
       }
       ptx::tcgen05_fence_after();
+      const long long tile_t0 = tr ? ptx::clock_cycles() : 0;
       const uint32_t taddr =
           tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(acc) * acc_stride;
 
@@ -686,17 +703,25 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
       // row range that ends inside the output (a group or segment boundary) takes the plain stores.
       const bool tma_out = (p.out_tma != 0) && own && base != nullptr &&
                            (rows_valid == 32 || (!grouped && !fused));
+      // A partial tile goes to its owner's slab the same way. Slabs are BM x BN whatever the
+      // tile's valid extent, so whole windows are pushed and nothing needs clipping.
+      const bool tma_push = kReduce && !own && (p.stage_tma != 0);
+      const int push_row0 = tma_push
+          ? static_cast<int>(stage_slot_offset(sched, st_elt, parity, p.rank, ti.tile_in_seg) /
+                             (static_cast<int64_t>(BN) * st_elt)) + row_base
+          : 0;
+      int groups_sent = 0;
 
       for (int win = 0; win < nwin; ++win) {
         if (win * groups_per_win * 32 >= ti.cols) break;
         // the store that read this staging buffer two windows ago must be done with it
         const uint32_t stg = stg_base + (win_count & 1u) * kEpiWinBytes;
         ++win_count;
-        if (p.out_tma) {
+        if (any_tma) {
           if (lane == 0) {
             // a window sent by TMA leaves one younger store in flight; a window sent by plain
             // stores adds no group, so everything older has to be drained
-            if (tma_out) ptx::bulk_wait_group_read<1>();
+            if (tma_out || tma_push) ptx::bulk_wait_group_read<1>();
             else ptx::bulk_wait_group_read<0>();
           }
           __syncwarp();
@@ -893,7 +918,15 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
           const int per_win = 128 / st_elt;
           const int cols_valid = min(per_win, ti.cols - win * per_win);
           const int64_t wb = static_cast<int64_t>(win) * 128;
-          if (tma_out) {
+          if (tma_push) {
+            ptx::fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              ptx::tma_store_2d(&p.tm_stage[ti.seg], stg, win * per_win, push_row0);
+              ptx::bulk_commit_group();
+            }
+            ++groups_sent;
+          } else if (tma_out) {
             if (rows_valid > 0) {
               ptx::fence_proxy_async_smem();   // the staged bytes become visible to the TMA unit
               __syncwarp();
@@ -931,10 +964,24 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
         tick.lap(c_work);
         if (!p.withhold_signals) {
           if (!own) {
-            if (lane == 0)
-              ptx::st_release_sys_u32(
-                  p.arrive[ti.seg] + arrive_flag_index(sched, ti.tile_in_seg, p.rank) * qpt + qid,
-                  epoch);
+            uint32_t* stamp = p.arrive[ti.seg] + arrive_flag_index(sched, ti.tile_in_seg, p.rank) * qpt + qid;
+            if (tma_push) {
+              // the stores of the tile before this one are complete once at most this tile's
+              // groups are in flight: announce that tile now, this one a tile later
+              if (lane == 0 && pending_stamp != nullptr) {
+                // (the count is an immediate: take the largest one not above this tile's groups)
+                if (groups_sent >= 8) ptx::bulk_wait_group<8>();
+                else if (groups_sent >= 4) ptx::bulk_wait_group<4>();
+                else if (groups_sent >= 2) ptx::bulk_wait_group<2>();
+                else if (groups_sent == 1) ptx::bulk_wait_group<1>();
+                else ptx::bulk_wait_group_all();
+                ptx::fence_proxy_async();
+                ptx::st_release_sys_u32(pending_stamp, epoch);
+              }
+              pending_stamp = stamp;
+            } else if (lane == 0) {
+              ptx::st_release_sys_u32(stamp, epoch);
+            }
           } else {
             // the reduced rows are in every rank's output: stamp them everywhere
             const int gid = (ti.seg * sched.tiles_per_seg + ti.tile_in_seg) * qpt + qid;
@@ -948,18 +995,25 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
       }
 
       tick.lap(c_pub);
+      if (tr) {
+        const unsigned long long dt = static_cast<unsigned long long>(ptx::clock_cycles() - tile_t0);
+        if (own) c_tile_own += dt; else c_tile_push += dt;
+      }
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1u;
     }
 
-    // every TMA store of this warp has to be performed before the kernel ends
-    if (p.out_tma && lane == 0) ptx::bulk_wait_group_all();
+    // every TMA store of this warp has to be performed before the kernel ends, and the last
+    // pushed tile is still unannounced
+    if (kReduce) settle_pending();
+    if (any_tma && lane == 0) ptx::bulk_wait_group_all();
     __syncwarp();
     tick.lap(c_work);
     if (tr) {
       atomicAdd(p.trace + 5, c_full); atomicAdd(p.trace + 6, c_work); atomicAdd(p.trace + 7, c_peer);
       atomicAdd(p.trace + 9, c_pub); atomicAdd(p.trace + 10, c_own);
       atomicAdd(p.trace + 11, c_tld); atomicAdd(p.trace + 12, c_cvt); atomicAdd(p.trace + 13, c_flush);
+      atomicAdd(p.trace + 14, c_tile_own); atomicAdd(p.trace + 15, c_tile_push);
     }
 
     // all-reduce tail: this rank's output is complete only when every owner's tiles landed

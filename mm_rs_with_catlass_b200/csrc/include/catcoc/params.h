@@ -56,6 +56,9 @@ struct alignas(64) FusedParams {
   CUtensorMap tm_a_gath[2];  // AG: gathered A, one map per parity buffer
   CUtensorMap tm_b;
   CUtensorMap tm_out;  // `out` as [rows, N] with a 32-row x 128-byte box (valid when out_tma)
+  // Rank r's staging region as one matrix [slots * BM rows, BN] of partial elements (slots are
+  // contiguous and BN wide), same box; valid when stage_tma
+  CUtensorMap tm_stage[kMaxWorld];
 
   TileSched sched;
   int K;
@@ -74,6 +77,7 @@ struct alignas(64) FusedParams {
   int out_fmt;      // ElemFmt of `out`
   int out_vec_ok;   // 1 when 16-byte vector stores to `out` are aligned
   int out_tma;      // 1 when tm_out describes `out`: finished 32-row x 128-byte windows leave by TMA store
+  int stage_tma;    // 1 when tm_stage[r] describes rank r's staging slabs: partial tiles are pushed by TMA store
   int64_t out_row_shift;  // subtracted from the tile's global row to index `out` (RS: seg begin)
 
   // partial tiles that cross NVLink
@@ -141,6 +145,7 @@ struct alignas(64) FusedParams {
   // [6] epilogue work             [7] epilogue waits on peers' stamps   [8] CTA lifetime
   // [9] epilogue publish / rest   [10] owner-side reduce
   // [11] epilogue TMEM loads      [12] convert + stage to shared         [13] flush to global / peers
+  // [14] epilogue time on owned tiles (accumulator ready -> tile done)   [15] the same on pushed tiles
   unsigned long long* trace;
 };
 

@@ -149,6 +149,11 @@ template <int N>
 CATCOC_DEVICE void bulk_wait_group_read() {
   asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
 }
+// Waits until at most N of this thread's bulk groups are incomplete (older ones: writes performed).
+template <int N>
+CATCOC_DEVICE void bulk_wait_group() {
+  asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory");
+}
 // Waits until every bulk group of this thread has completed (its writes are performed).
 CATCOC_DEVICE void bulk_wait_group_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 

@@ -84,6 +84,18 @@ static bool out_tma_enabled() {
   return on;
 }
 
+// CATCOC_PUSH_TMA=1 pushes partial tiles to their owners with TMA stores instead of plain vector
+// stores. Off by default: the pushes are bound by the link either way (measured on 2 GPUs: the
+// same end-to-end time, about 500 GB/s per direction), and the plain stores announce a tile
+// without the one-tile lag the bulk stores need.
+static bool push_tma_enabled() {
+  static const bool on = [] {
+    const char* e = getenv("CATCOC_PUSH_TMA");
+    return e != nullptr && e[0] == '1';
+  }();
+  return on;
+}
+
 static int sm_count(int device) {
   static int cached[64];
   static std::once_flag once;
@@ -462,6 +474,22 @@ int catcoc_build_params(const CatcocOpArgs* args, FusedParams* p, int* kind_out,
       p->arrive[r] = a.arrive[r];
       if (p->stage[r] == nullptr || p->arrive[r] == nullptr) { set_error("missing staging buffers for rank %d", r); return CATCOC_E_BAD_ARG; }
     }
+  }
+  // Partial tiles are pushed into the owners' slabs by TMA stores when every peer's staging
+  // region can be described as one [slots * bm, bn] matrix (it always can: slabs are dense).
+  if (fused && (a.mode == CATCOC_MODE_RS || a.mode == CATCOC_MODE_AR) && push_tma_enabled()) {
+    const int pelt = fmt_bytes(a.partial_fmt);
+    const CUtensorMapDataType pdt = a.partial_fmt == CATCOC_FMT_F16    ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
+                                    : a.partial_fmt == CATCOC_FMT_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                    : a.partial_fmt == CATCOC_FMT_F32  ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                                                                       : CU_TENSOR_MAP_DATA_TYPE_INT32;
+    const int64_t slab_rows = 2ll * a.W * p->sched.tiles_per_seg * bm;
+    bool all = true;
+    for (int r = 0; r < a.W && all; ++r) {
+      if (r == a.rank) continue;
+      all = encode_2d(&p->tm_stage[r], a.stage[r], pelt, pdt, slab_rows, bn, bn, 128 / pelt, 32) == CATCOC_OK;
+    }
+    p->stage_tma = all ? 1 : 0;
   }
   p->scale_m = a.scale_m;
   p->scale_n = a.scale_n;

@@ -16,7 +16,7 @@ import sys
 import torch
 
 TRACE_NAMES = ["prod_wait_empty", "prod_issue", "mma_wait_full", "mma_wait_acc", "mma_issue", "epi_wait_full",
-               "epi_work", "epi_wait_peer", "cta_life", "epi_publish", "epi_own", "epi_tmem_ld", "epi_convert", "epi_flush"]
+               "epi_work", "epi_wait_peer", "cta_life", "epi_publish", "epi_own", "epi_tmem_ld", "epi_convert", "epi_flush", "epi_tiles_own", "epi_tiles_pushed"]
 
 
 def main(argv=None) -> int:
