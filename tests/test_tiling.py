@@ -81,12 +81,20 @@ def test_table_roundtrip_best_and_resume(tmp_path):
     assert len(TilingTable.load(tmp_path / "best.csv").rows) == 2
 
 
-def test_heuristic_fills_the_machine_and_is_deterministic():
+def test_heuristic_follows_the_cost_model_and_is_deterministic():
     big = chooser.heuristic("matmul_reduce_scatter", 8192, 8192, 3584, 8, torch.bfloat16)
     assert big.effective_bn == 256 and big.cta_pair == 2
+    # one row of tiles: only narrow tiles give every SM something to do
     small = chooser.heuristic("matmul_allreduce", 128, 8192, 3584, 8, torch.bfloat16)
     assert small.effective_bn == 64 and small.cta_pair == 1
     assert math.ceil(128 / 128) * (8192 // small.effective_bn) >= 128
+    assert chooser.heuristic("matmul", 128, 8192, 1024, 1, torch.bfloat16).effective_bn == 64
+    # from a few hundred rows on the widest tile wins although it leaves SMs idle (measured)
+    for m, n in ((512, 8192), (1024, 4096), (2048, 2048)):
+        mid = chooser.heuristic("matmul", m, n, 4096, 1, torch.bfloat16)
+        assert mid.effective_bn == 256 and mid.cta_pair == 2
+    assert chooser.tile_cost(1024, 1, 4096, 256, 2) < chooser.tile_cost(1024, 1, 4096, 128, 2)
+    assert chooser.tile_cost(128, 1, 8192, 64, 1) < chooser.tile_cost(128, 1, 8192, 256, 1)
     q = chooser.heuristic("quant_matmul_reduce_scatter", 256, 512, 512, 2, torch.int8)
     assert q.effective_bn >= 128
     assert chooser.heuristic("matmul_reduce_scatter", 8192, 8192, 3584, 8, torch.bfloat16) == big
