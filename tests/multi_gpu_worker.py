@@ -48,6 +48,45 @@ def check(name, out, gold, k, dtype, magnitude=None):
     report(name, r.ok and not st, "%s %s" % (r, st))
 
 
+def run_mixed_launches(ctx, W, iters, name):
+    """Many back-to-back launches of mixed ops on one context (epoch parity, stamp and slab reuse):
+    every result is checked, so a launch that raced with its neighbours shows up as a wrong tile."""
+    a, b = matmul_inputs(128 * W, 256, 128, rank, torch.bfloat16, dev, seed=77)
+    gold = ref.matmul_allreduce(a, b, out_dtype=torch.float32)
+    mag = ref.partial_magnitude(a, b)
+    rows = 128
+    ok = True
+    bad = []
+    ag_gold = None
+    for it in range(iters):
+        if it % 3 == 0:
+            o = catcoc.matmul_reduce_scatter(a, b)
+            r = verify(o, gold[rank * rows:(rank + 1) * rows], 128 * W, torch.bfloat16, mag[rank * rows:(rank + 1) * rows])
+            if not r.ok:
+                bad.append("it %d rs rank %d: %s" % (it, rank, r))
+        elif it % 3 == 1:
+            o = catcoc.matmul_allreduce(a, b).clone()
+            r = verify(o, gold, 128 * W, torch.bfloat16, mag)
+            if not r.ok:
+                bad.append("it %d ar rank %d: %s" % (it, rank, r))
+        else:
+            o, gath = catcoc.allgather_matmul(a[:64], b)
+            if ag_gold is None:
+                ag_gold, _ = ref.allgather_matmul(a[:64], b, out_dtype=torch.float32)
+            r = verify(o, ag_gold, 128, torch.bfloat16)
+            if not r.ok:
+                bad.append("it %d ag rank %d: %s" % (it, rank, r))
+    ok = not bad
+    for line in bad[:4]:
+        print(line, flush=True)
+    try:
+        ctx.check("repeat")
+    except RuntimeError as e:
+        ok = False
+        print("rank", rank, e, flush=True)
+    report(name, ok)
+
+
 TILINGS = [None, catcoc.TilingConfig(bn=128, cta_pair=1), catcoc.TilingConfig(bn=256, cta_pair=2, swizzle=4)]
 
 if mode == "ops":
@@ -131,28 +170,7 @@ if mode == "ops":
     o = catcoc.quant_matmul_reduce_scatter(x1, x2, s1, s2, bias, out_dtype=torch.float32)
     exp = ((128.0 + torch.arange(1, 257, device=dev).float()) * W * 1e-4)[None, :].expand(32, 256)
     report("qrs_debug_pattern", bool(torch.allclose(o, exp, rtol=1e-5)))
-    # many back-to-back launches of mixed ops on one context (epoch parity, stamp reuse)
-    a, b = matmul_inputs(128 * W, 256, 128, rank, torch.bfloat16, dev, seed=77)
-    gold = ref.matmul_allreduce(a, b, out_dtype=torch.float32)
-    mag = ref.partial_magnitude(a, b)
-    rows = 128
-    ok = True
-    for it in range(60):
-        if it % 3 == 0:
-            o = catcoc.matmul_reduce_scatter(a, b)
-            ok &= verify(o, gold[rank * rows:(rank + 1) * rows], 128 * W, torch.bfloat16, mag[rank * rows:(rank + 1) * rows]).ok
-        elif it % 3 == 1:
-            o = catcoc.matmul_allreduce(a, b).clone()
-            ok &= verify(o, gold, 128 * W, torch.bfloat16, mag).ok
-        else:
-            o, _ = catcoc.allgather_matmul(a[:64], b[:128] if False else b)
-            ok &= bool(torch.isfinite(o.float()).all())
-    try:
-        ctx.check("repeat")
-    except RuntimeError as e:
-        ok = False
-        print("rank", rank, e, flush=True)
-    report("repeat_60_mixed_launches", ok)
+    run_mixed_launches(ctx, W, 60, "repeat_60_mixed_launches")
     # the flagship block
     from mm_rs_with_catlass_b200.models.tp_mlp import TPMLP, TPMLPConfig
     mlp = TPMLP(TPMLPConfig(hidden=512, ffn=256 * W), ctx, dev)
@@ -160,6 +178,12 @@ if mode == "ops":
     h_ref, _ = ref.allgather_matmul(x, mlp.w_up, out_dtype=torch.bfloat16)
     check("tpmlp", mlp(x), mlp.reference_forward(x).float(), 256 * W, torch.bfloat16,
           ref.partial_magnitude(mlp._act(h_ref), mlp.w_down)[rank * 128:(rank + 1) * 128])
+    ctx.finalize()
+
+elif mode == "repeat":
+    # the mixed-launch loop alone, long: cheap to run when hunting a protocol race
+    ctx = catcoc.init(heap_bytes=1 << 30, multicast=(os.environ.get("CATCOC_TEST_NVLS", "1") == "1"))
+    run_mixed_launches(ctx, world, int(os.environ.get("CATCOC_TEST_REPEATS", "600")), "repeat_mixed_launches")
     ctx.finalize()
 
 elif mode == "withhold":
