@@ -382,6 +382,12 @@ int catcoc_build_params(const CatcocOpArgs* args, FusedParams* p, int* kind_out,
     }
   }
   const int per128 = 128 / rf.elt;
+  // The 3-D maps fetch an M/N-contiguous operand in whole 128-byte column blocks, addressed by
+  // block index: every tile origin must then be a multiple of a block. Tile origins inside a
+  // segment are (multiples of 128 rows / bn columns); segment origins are multiples of seg_len.
+  const bool a_blocks_ok = !(p->sched.W > 1 && seg_dim == SEG_ROWS) || (p->sched.seg_len % per128) == 0;
+  const bool b_blocks_ok = (!(p->sched.W > 1 && seg_dim == SEG_COLS) || (p->sched.seg_len % per128) == 0) &&
+                           ((pair ? bn / 2 : bn) % per128) == 0;
   if (!a.trans_b && (pair ? bn / 2 : bn) < per128) {
     set_error("8-bit operands stored [K, N] need bn >= 128 (one 128-byte run of N per TMA box)");
     return CATCOC_E_UNSUPPORTED;
@@ -417,7 +423,7 @@ int catcoc_build_params(const CatcocOpArgs* args, FusedParams* p, int* kind_out,
   } else if (!a.trans_a) {
     rc = encode_2d(&p->tm_a, a.a, rf.elt, rf.dt, a_rows, a_k, a.lda, rf.bk, kBM);
     if (rc != 0) return rc;
-  } else if (a_rows % per128 == 0) {
+  } else if (a_rows % per128 == 0 && a_blocks_ok) {
     rc = encode_3d_blocks(&p->tm_a, a.a, rf.elt, rf.dt, a_k, a_rows, a.lda, rf.bk, kBM / per128);
     if (rc != 0) return rc;
     p->a_3d = 1;
@@ -427,7 +433,7 @@ int catcoc_build_params(const CatcocOpArgs* args, FusedParams* p, int* kind_out,
   }
   if (a.trans_b) {
     rc = encode_2d(&p->tm_b, a.b, rf.elt, rf.dt, b_n, b_k, a.ldb, rf.bk, pair ? bn / 2 : bn);
-  } else if (b_n % per128 == 0) {
+  } else if (b_n % per128 == 0 && b_blocks_ok) {
     rc = encode_3d_blocks(&p->tm_b, a.b, rf.elt, rf.dt, b_k, b_n, a.ldb, rf.bk, (pair ? bn / 2 : bn) / per128);
     p->b_3d = 1;
   } else {

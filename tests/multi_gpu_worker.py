@@ -123,6 +123,24 @@ if mode == "ops":
             check("ar_seg%d_%s" % (seg, str(dtype)[6:]),
                   catcoc.matmul_allreduce(a, b, tiling=catcoc.TilingConfig(bn=64, seg_dim=seg)), gold, 256 * W, dtype,
                   mag)
+        # column ownership whose segments start inside a 128-byte column block of B (32 and 96
+        # columns per rank): the block-wise 3-D fetch of an N-contiguous B cannot address them
+        for cols, tb in ((32, False), (96, False), (96, True), (40, False)):
+            a, b = matmul_inputs(256, cols * W, 192, rank, dtype, dev, trans_b=tb, seed=cols)
+            gold = ref.matmul_allreduce(a, b, trans_b=tb, out_dtype=torch.float32)
+            mag = ref.partial_magnitude(a, b, trans_b=tb)
+            for bn in (64, 128):
+                check("ar_segcols%d_%d_bn%d_%s" % (cols, tb, bn, str(dtype)[6:]),
+                      catcoc.matmul_allreduce(a, b, trans_b=tb, tiling=catcoc.TilingConfig(bn=bn, seg_dim=1)), gold,
+                      192 * W, dtype, mag)
+        # row ownership with an A stored [K, M] whose segments start inside a 128-byte block of A
+        a, b = matmul_inputs(96 * W, 256, 192, rank, dtype, dev, trans_a=True, seed=5)
+        gold = ref.matmul_allreduce(a, b, trans_a=True, out_dtype=torch.float32)
+        mag = ref.partial_magnitude(a, b, trans_a=True)
+        check("rs_transA_seg96_%s" % str(dtype)[6:], catcoc.matmul_reduce_scatter(a, b, trans_a=True),
+              gold[rank * 96:(rank + 1) * 96], 192 * W, dtype, mag[rank * 96:(rank + 1) * 96])
+        check("ar_transA_seg96_%s" % str(dtype)[6:],
+              catcoc.matmul_allreduce(a, b, trans_a=True, tiling=catcoc.TilingConfig(seg_dim=0)), gold, 192 * W, dtype, mag)
         if ctx.multicast:
             a, b = matmul_inputs(256 * W, 512, 256, rank, dtype, dev, seed=12)
             gold = ref.matmul_allreduce(a, b, out_dtype=torch.float32)

@@ -203,3 +203,38 @@ def test_flagship_block_world1(catcoc, device):
     x = torch.randn(384, 512, device=device).bfloat16()
     assert_close(mlp(x), mlp.reference_forward(x).float(), k=1536)
     _check_status(device, "tpmlp")
+
+
+def test_launch_plans_follow_the_data_not_the_first_call(catcoc, device):
+    """A repeated call reuses its argument block (a launch plan): new contents at the same
+    addresses must give new results, a new output must be written, and operands that need a
+    padded copy are rebuilt on every call."""
+    from mm_rs_with_catlass_b200.ops import gemm as G
+    from mm_rs_with_catlass_b200.utils.verify import assert_close
+    a = torch.randn(256, 192, device=device).bfloat16()
+    b = torch.randn(192, 320, device=device).bfloat16()
+    G._plans.clear()
+    o1 = catcoc.matmul(a, b)
+    n_plans = len(G._plans)
+    assert n_plans == 1
+    a.copy_(torch.randn(256, 192, device=device).bfloat16())
+    o2 = catcoc.matmul(a, b)                       # plan hit, fresh output tensor
+    assert len(G._plans) == n_plans and o2.data_ptr() != o1.data_ptr()
+    _check_status(device, "plan hit")
+    assert_close(o2, a.float() @ b.float(), k=192)
+    out = torch.empty(256, 320, dtype=torch.bfloat16, device=device)
+    assert catcoc.matmul(a, b, out=out) is out     # another key: the output is part of it
+    assert catcoc.matmul(a, b, out=out) is out
+    _check_status(device, "plan hit with out")
+    assert_close(out, a.float() @ b.float(), k=192)
+    # a pitch TMA cannot address goes through the pad kernel: never planned, always current
+    big = torch.randn(256, 200, device=device).bfloat16()
+    av = big[:, 3:195]
+    before = len(G._plans)
+    r1 = catcoc.matmul(av, b)
+    big.mul_(2.0)
+    r2 = catcoc.matmul(av, b)
+    _check_status(device, "padded operand")
+    assert len(G._plans) == before
+    assert_close(r2, av.float() @ b.float(), k=192)
+    assert not torch.equal(r1, r2)
