@@ -18,7 +18,7 @@ import sys
 import torch
 import torch.distributed as dist
 
-HIDDEN, FFN = 8192, 28672
+DEFAULT_HIDDEN, DEFAULT_FFN = 8192, 28672
 LINK_GBS = 770.0          # measured peer copy per direction per GPU on this pool
 
 
@@ -40,7 +40,13 @@ def main(argv=None) -> int:
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--ms", default="128,1024,8192,16384")
     ap.add_argument("--ops", default="ar,ag,rs,q")
+    ap.add_argument("--hidden", type=int, default=DEFAULT_HIDDEN, help="N of the row-parallel ops, K of the all-gather op")
+    ap.add_argument("--ffn", type=int, default=DEFAULT_FFN, help="split over the ranks: K_local = ffn / W")
+    ap.add_argument("--trace", action="store_true",
+                    help="after timing an op, run one more launch with the kernel's cycle counters on and print "
+                         "them per CTA (FusedParams::trace in csrc/include/catcoc/params.h)")
     args = ap.parse_args(argv)
+    HIDDEN, FFN = args.hidden, args.ffn
 
     import mm_rs_with_catlass_b200 as catcoc
     from mm_rs_with_catlass_b200.ops.baseline import Baseline
@@ -67,6 +73,16 @@ def main(argv=None) -> int:
         row = {"op": op, "W": W, "M": M, "fused_us": 1e3 * t_f, "cublas_nccl_us": 1e3 * t_b, "speedup": t_b / t_f,
                "tflops_per_gpu": flops_rank / (t_f * 1e-3) / 1e12, "roofline_us": 1e3 * roof_ms,
                "roofline_frac": roof_ms / t_f, "peak_source": peak_src}
+        if args.trace:
+            from mm_rs_with_catlass_b200.utils.gemm_probe import TRACE_NAMES
+            tr = torch.zeros(16, dtype=torch.int64, device=dev)
+            ctx.trace = tr
+            ctx.plans.clear()          # the counters' address is part of the argument block
+            fused_fn()
+            torch.cuda.synchronize()
+            ctx.trace = None
+            ctx.plans.clear()
+            row["cycles_per_cta"] = {n: round(v / 148) for n, v in zip(TRACE_NAMES, tr.tolist())}
         rows.append(row)
         if rank == 0:
             print(json.dumps(row), flush=True)
