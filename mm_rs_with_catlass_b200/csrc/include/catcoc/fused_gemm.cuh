@@ -40,7 +40,12 @@ constexpr int kABytes = kBM * 128;     // A stage: 128 rows x 128 B (K-major) or
 constexpr int kEpiWarps = 4;
 constexpr int kEpiWinBytes = 32 * 128;             // one staged window: 32 rows x 128 B
 constexpr int kEpiStageBytes = 2 * kEpiWinBytes;   // per epilogue warp: two windows (one may still feed a TMA store)
-constexpr int kThreads = 256;
+constexpr int kThreads = 256;          // warps 0-6 are the GEMM roles, warp 7 a communication warp
+// The plain-epilogue variant (the only one the all-gather runs) fits 204 registers per thread, so
+// it carries two more communication warps: the push of the A shard is latency bound per warp and
+// one warp per SM could not feed the link (measured 173 GB/s per GPU, the GEMM waited on it).
+constexpr int kThreadsPlain = 320;
+CATCOC_HD constexpr int threads_for(int epi) { return epi == EPI_PLAIN ? kThreadsPlain : kThreads; }
 constexpr int kTmemCols = 512;
 constexpr int kMaxStages = 6;
 
@@ -230,7 +235,7 @@ CATCOC_DEVICE TileInfo walk_tile(const FusedParams& p, int t, GroupWalk& w) {
 // The kernel
 // ---------------------------------------------------------------------------------------
 template <int KIND, bool CTA2, int EPI>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(threads_for(EPI), 1)
 fused_gemm_kernel(const __grid_constant__ FusedParams p) {
   // Epilogue variant (see EpiVariant in params.h): stages a launch cannot need are compiled out.
   constexpr bool kReduce = (EPI >= EPI_REDUCE);   // reduce-scatter / all-reduce: peers' partials, pushes, stamps
@@ -1102,8 +1107,8 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
     // Push this rank's A shard into every rank's gathered buffer in units of
     // chunk_rows x 512 B, peer-major: the peer that consumes the shard first is served first.
     if (fused && p.mode == MODE_AG) {
-      const int cw = 0;
-      const int ncw = 1;
+      const int cw = warp - (3 + kEpiWarps);               // this communication warp ...
+      const int ncw = static_cast<int>(blockDim.x >> 5) - (3 + kEpiWarps);   // ... of so many per CTA
       const GatherPlan& gp = p.gp;
       const int units_per_peer = gp.n_chunks * gp.n_slices;
       const int64_t total_units = static_cast<int64_t>(p.W) * units_per_peer;
@@ -1125,7 +1130,8 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
         uint8_t* dstp = p.gathered[peer] + static_cast<int64_t>(parity) * p.gathered_parity_bytes +
                         (static_cast<int64_t>(p.rank) * gp.m + r0) * p.gathered_pitch + cb;
         if (col_ok) {
-          // 16 rows (8 KiB per warp) in flight per round trip: the copy is latency bound
+          // 16 rows (8 KiB per warp) in flight per round trip: the copy is latency bound, which is
+          // why several warps per CTA share it
           for (int r = 0; r < nrows; r += 16) {
             uint4 buf[16];
 #pragma unroll

@@ -32,7 +32,7 @@ cudaError_t launch_one(const FusedParams& p, int grid, cudaStream_t stream) {
   cudaLaunchConfig_t cfg;
   memset(&cfg, 0, sizeof(cfg));
   cfg.gridDim = dim3(grid, 1, 1);
-  cfg.blockDim = dim3(kThreads, 1, 1);
+  cfg.blockDim = dim3(threads_for(EPI), 1, 1);
   cfg.dynamicSmemBytes = Geo<CTA2>::kSmemBytes;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
@@ -50,7 +50,7 @@ int query_clusters() {
   cudaLaunchConfig_t cfg;
   memset(&cfg, 0, sizeof(cfg));
   cfg.gridDim = dim3(2, 1, 1);
-  cfg.blockDim = dim3(kThreads, 1, 1);
+  cfg.blockDim = dim3(threads_for(EPI), 1, 1);
   cfg.dynamicSmemBytes = Geo<true>::kSmemBytes;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeClusterDimension;
