@@ -44,7 +44,7 @@ constexpr int kThreads = 256;          // warps 0-6 are the GEMM roles, warp 7 a
 // The plain-epilogue variant (the only one the all-gather runs) fits 204 registers per thread, so
 // it carries two more communication warps: the push of the A shard is latency bound per warp and
 // one warp per SM could not feed the link (measured 173 GB/s per GPU, the GEMM waited on it).
-constexpr int kThreadsPlain = 320;
+constexpr int kThreadsPlain = 384;
 CATCOC_HD constexpr int threads_for(int epi) { return epi == EPI_PLAIN ? kThreadsPlain : kThreads; }
 constexpr int kTmemCols = 512;
 constexpr int kMaxStages = 6;
