@@ -210,7 +210,7 @@ def main():
         if ours:
             ctx.check("bench e2e")
 
-    # vs_baseline: measured cuBLAS + NCCL rate of the same step on this pool (BASELINE.md)
+    # vs_baseline: measured cuBLAS + NCCL rate of the same step on this pool
     vs = None
     try:
         with open(os.path.join(REPO, "baseline", "measured_baseline.json")) as fh:
