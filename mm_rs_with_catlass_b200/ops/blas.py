@@ -326,9 +326,9 @@ def gemv(a: torch.Tensor, x: torch.Tensor, y: Optional[torch.Tensor] = None, *, 
     when ``trans``. fp16 / bf16 / fp32, fp32 accumulation. The product is HBM-bound (every
     element of A is used once), so it runs on plain SIMT kernels that stream A with 16-byte loads
     rather than on the tensor cores."""
-    dev = cm.require_cuda(a, x, y, out)
     if a.dim() != 2 or x.dim() != 1:
         raise ValueError("gemv takes a matrix and a vector")
+    dev = cm.require_cuda(a, x, y, out)
     if a.dtype not in (torch.float16, torch.bfloat16, torch.float32) or x.dtype != a.dtype:
         raise TypeError("gemv takes fp16 / bf16 / fp32 operands of one dtype")
     if a.stride(-1) != 1:
