@@ -53,6 +53,13 @@ def test_fused_ops_on_plain_peer_stores_without_nvls(gpu_count):
     _run(2, "ops", {"CATCOC_TEST_NVLS": "0"})
 
 
+def test_fused_ops_with_partial_tiles_pushed_by_tma_store(gpu_count):
+    """The opt-in push path: bulk tensor stores into the owners' slabs, stamps one tile late."""
+    if gpu_count < 2:
+        pytest.skip("needs 2 GPUs")
+    _run(2, "ops", {"CATCOC_PUSH_TMA": "1"})
+
+
 def test_withheld_signal_becomes_an_error_status(gpu_count):
     if gpu_count < 2:
         pytest.skip("needs 2 GPUs")
