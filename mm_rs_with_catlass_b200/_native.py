@@ -49,6 +49,7 @@ class OpArgs(C.Structure):
         ("rank", C.c_int), ("W", C.c_int),
         ("partial_fmt", C.c_int),
         ("stage", C.c_void_p * MAX_WORLD),
+        ("stage_parity_bytes", C.c_int64),
         ("arrive", C.c_void_p * MAX_WORLD),
         ("ar_out", C.c_void_p * MAX_WORLD),
         ("ar_out_parity_bytes", C.c_int64),

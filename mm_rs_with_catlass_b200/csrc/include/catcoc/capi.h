@@ -62,6 +62,8 @@ typedef struct CatcocOpArgs {
   int rank, W;
   int partial_fmt;                         /* format of tiles crossing NVLink            */
   void* stage[CATCOC_MAX_WORLD];           /* staging slabs, one base per rank           */
+  int64_t stage_parity_bytes;              /* distance between the two parity halves of a staging region: a
+                                              property of the buffer (>= catcoc_stage_bytes / 2, multiple of 1024) */
   uint32_t* arrive[CATCOC_MAX_WORLD];      /* arrival stamps                             */
   void* ar_out[CATCOC_MAX_WORLD];          /* all-reduce output (parity 0) on every rank */
   int64_t ar_out_parity_bytes;

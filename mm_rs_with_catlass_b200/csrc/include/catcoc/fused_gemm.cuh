@@ -82,6 +82,7 @@ struct SmemTail {
   uint64_t acc_empty[2];
   uint32_t tmem_base;
   uint32_t abort_flag;
+  uint32_t dead;   // the status block already held an error when this CTA started
 };
 
 CATCOC_DEVICE void report_status(const FusedParams& p, uint32_t code, uint32_t what,
@@ -288,6 +289,9 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
       ptx::mbar_init(&tail->acc_empty[b], CTA2 ? 2 * kEpiWarps : kEpiWarps);
     }
     tail->abort_flag = 0;
+    // A fused launch that finds an earlier failure latched in the status block does nothing: the
+    // ranks' epochs no longer agree, so every wait would only run into its time limit again.
+    tail->dead = (p.mode != MODE_LOCAL && p.W > 1 && ptx::ld_relaxed_sys_u32(p.status) != 0u) ? 1u : 0u;
     ptx::mbar_fence_init();
     ptx::prefetch_tmap(&p.tm_a);
     ptx::prefetch_tmap(&p.tm_b);
@@ -307,6 +311,9 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
   if (CTA2) ptx::cluster_sync_all();   // the peer's barriers exist before anyone signals them
   ptx::tcgen05_fence_after();
   const uint32_t tmem_base = tail->tmem_base;
+  // both CTAs of a pair must take the same decision (they meet again at cluster barriers)
+  bool dead = tail->dead != 0u;
+  if (CTA2) dead = dead || ptx::ld_shared_cluster_u32(ptx::map_to_cta(ptx::smem_u32(&tail->dead), static_cast<uint32_t>(sub ^ 1))) != 0u;
   const long long cta_t0 = (p.trace != nullptr) ? ptx::clock_cycles() : 0;
 
   // Epoch of this launch: completed launches + 1. Read before any CTA can finish.
@@ -314,7 +321,9 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
   if (fused) epoch = ptx::ld_relaxed_sys_u32(p.epoch_ptr) + 1;
   const int parity = static_cast<int>(epoch & 1u);
 
-  if (warp == 0) {
+  if (dead) {
+    // nothing to do: fall through to the teardown
+  } else if (warp == 0) {
     // =============================== TMA producer ===============================
     int stage = 0;
     uint32_t phase = 0;
@@ -678,7 +687,7 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
       bool vec_ok = true;
       if (!own) {
         pitch = static_cast<int64_t>(BN) * st_elt;
-        base = p.stage[ti.seg] + stage_slot_offset(sched, st_elt, parity, p.rank, ti.tile_in_seg) +
+        base = p.stage[ti.seg] + stage_slot_offset(sched, st_elt, p.stage_parity_bytes, parity, p.rank, ti.tile_in_seg) +
                static_cast<int64_t>(row_base) * pitch;
       } else if (kReduce && fused && p.mode == MODE_AR) {
         pitch = p.ldc * st_elt;
@@ -712,7 +721,7 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
       // tile's valid extent, so whole windows are pushed and nothing needs clipping.
       const bool tma_push = kReduce && !own && (p.stage_tma != 0);
       const int push_row0 = tma_push
-          ? static_cast<int>(stage_slot_offset(sched, st_elt, parity, p.rank, ti.tile_in_seg) /
+          ? static_cast<int>(stage_slot_offset(sched, st_elt, p.stage_parity_bytes, parity, p.rank, ti.tile_in_seg) /
                              (static_cast<int64_t>(BN) * st_elt)) + row_base
           : 0;
       int groups_sent = 0;
@@ -766,7 +775,7 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
             const uint8_t* sbase = p.stage[p.rank] + (static_cast<int64_t>(row_in_tile) * BN + col0) * pelt;
             const int64_t slot_bytes = stage_tile_bytes(sched, pelt);
             const int64_t src_stride = static_cast<int64_t>(sched.tiles_per_seg) * slot_bytes;
-            const int64_t base_off = (static_cast<int64_t>(parity) * p.W * sched.tiles_per_seg + ti.tile_in_seg) * slot_bytes;
+            const int64_t base_off = static_cast<int64_t>(parity) * p.stage_parity_bytes + ti.tile_in_seg * slot_bytes;
             if (pelt == 2) {
               for (int s0 = 0; s0 < p.W; s0 += 2) {
                 uint4 w[2][4];

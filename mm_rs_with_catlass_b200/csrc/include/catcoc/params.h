@@ -83,6 +83,7 @@ struct alignas(64) FusedParams {
   // partial tiles that cross NVLink
   int partial_fmt;               // ElemFmt of pushed partial tiles
   uint8_t* stage[kMaxWorld];     // per-rank staging base (peer-mapped), see sched.h
+  int64_t stage_parity_bytes;    // distance between the two parity halves of every rank's staging region
   uint32_t* arrive[kMaxWorld];   // per-rank arrival stamps
   // all-reduce broadcast targets
   uint8_t* ar_out[kMaxWorld];    // per-rank parity-0 output base; parity 1 at + ar_out_parity_bytes

@@ -263,17 +263,25 @@ CATCOC_HD int peer_for_push_rs(int rank, int step, int W) { return (rank + step)
 // ---------------------------------------------------------------------------------------
 // Workspace geometry (bytes) for the fused ops; all ranks compute identical numbers.
 // ---------------------------------------------------------------------------------------
-// Staging for pushed partial tiles: [parity 2][source W][tiles_per_seg] slabs of BM x BN elements.
+// Staging for pushed partial tiles: two parity halves, each [source W][tiles_per_seg] slabs of
+// BM x BN elements. The distance between the halves (`parity_bytes`) is a property of the buffer,
+// fixed when it is allocated, NOT of the launch: two launches with different tile geometries then
+// still agree on which bytes belong to which parity, so a rank that runs one launch ahead never
+// writes into the half its peers are still reading.
 CATCOC_HD int64_t stage_tile_bytes(const TileSched& s, int elt_bytes) {
   return static_cast<int64_t>(s.BM) * s.BN * elt_bytes;
 }
-CATCOC_HD int64_t stage_slot_offset(const TileSched& s, int elt_bytes, int parity, int src,
-                                    int tile_in_seg) {
-  return ((static_cast<int64_t>(parity) * s.W + src) * s.tiles_per_seg + tile_in_seg) *
-         stage_tile_bytes(s, elt_bytes);
+CATCOC_HD int64_t stage_half_bytes(const TileSched& s, int elt_bytes) {
+  return static_cast<int64_t>(s.W) * s.tiles_per_seg * stage_tile_bytes(s, elt_bytes);
 }
+CATCOC_HD int64_t stage_slot_offset(const TileSched& s, int elt_bytes, int64_t parity_bytes, int parity,
+                                    int src, int tile_in_seg) {
+  return static_cast<int64_t>(parity) * parity_bytes +
+         (static_cast<int64_t>(src) * s.tiles_per_seg + tile_in_seg) * stage_tile_bytes(s, elt_bytes);
+}
+// Smallest region that holds both halves (the halves are then `stage_half_bytes` apart).
 CATCOC_HD int64_t stage_total_bytes(const TileSched& s, int elt_bytes) {
-  return 2 * static_cast<int64_t>(s.W) * s.tiles_per_seg * stage_tile_bytes(s, elt_bytes);
+  return 2 * stage_half_bytes(s, elt_bytes);
 }
 // Arrival stamps: one 32-bit word per (tile_in_seg, source).
 CATCOC_HD int64_t arrive_flag_index(const TileSched& s, int tile_in_seg, int src) {

@@ -480,6 +480,13 @@ int catcoc_build_params(const CatcocOpArgs* args, FusedParams* p, int* kind_out,
       p->arrive[r] = a.arrive[r];
       if (p->stage[r] == nullptr || p->arrive[r] == nullptr) { set_error("missing staging buffers for rank %d", r); return CATCOC_E_BAD_ARG; }
     }
+    const int64_t half = stage_half_bytes(p->sched, fmt_bytes(a.partial_fmt));
+    if (a.stage_parity_bytes < half || (a.stage_parity_bytes & 1023) != 0) {
+      set_error("stage_parity_bytes (%lld) must be a multiple of 1024 and hold one parity half (%lld bytes)",
+                static_cast<long long>(a.stage_parity_bytes), static_cast<long long>(half));
+      return CATCOC_E_BAD_ARG;
+    }
+    p->stage_parity_bytes = a.stage_parity_bytes;
   }
   // Partial tiles are pushed into the owners' slabs by TMA stores when every peer's staging
   // region can be described as one [slots * bm, bn] matrix (it always can: slabs are dense).
@@ -489,7 +496,9 @@ int catcoc_build_params(const CatcocOpArgs* args, FusedParams* p, int* kind_out,
                                     : a.partial_fmt == CATCOC_FMT_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
                                     : a.partial_fmt == CATCOC_FMT_F32  ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
                                                                        : CU_TENSOR_MAP_DATA_TYPE_INT32;
-    const int64_t slab_rows = 2ll * a.W * p->sched.tiles_per_seg * bm;
+    // both parity halves in one map: the second half starts a whole number of rows further down
+    const int64_t slab_rows = a.stage_parity_bytes / (static_cast<int64_t>(bn) * pelt) +
+                              static_cast<int64_t>(a.W) * p->sched.tiles_per_seg * bm;
     bool all = true;
     for (int r = 0; r < a.W && all; ++r) {
       if (r == a.rank) continue;

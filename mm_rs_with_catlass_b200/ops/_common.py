@@ -153,6 +153,16 @@ def launch(args: N.OpArgs, device: torch.device, timeout_ns: Optional[int] = Non
     code = N.lib().catcoc_fused_launch(C.byref(args), C.c_void_p(stream))
     if code < 0:
         N.check(code)
+    global _launches
+    _launches += 1
+
+
+_launches = 0
+
+
+def launch_count() -> int:
+    """Launches of the library's GEMM kernel queued by this process so far (fused and local)."""
+    return _launches
 
 
 _status_cache = {}
@@ -168,15 +178,26 @@ def local_status(device: torch.device) -> torch.Tensor:
     return st
 
 
+class StatusError(RuntimeError):
+    """A kernel gave up on a wait; ``status`` holds the eight words of its status block
+    (code, rank, what, expected, seen, peer, CTA, reserved)."""
+
+    def __init__(self, message: str, status):
+        super().__init__(message)
+        self.status = list(status)
+
+
 def raise_on_status(status: torch.Tensor, what: str) -> None:
-    """Reads a status block (synchronises) and raises if a kernel reported a failed wait."""
+    """Reads a status block (synchronises) and raises if a kernel reported a failed wait. The
+    block is cleared, so the next launch runs again (a fused launch that finds an error latched
+    returns at once)."""
     vals = status.cpu().tolist()
     if vals[0] != 0:
         status.zero_()
-        raise RuntimeError(
+        raise StatusError(
             "%s failed on rank %d: %s (what=%d expected=%d seen=%d peer=%d cta=%d)"
             % (what, vals[1], N.STATUS_NAMES.get(vals[0], "code %d" % vals[0]), vals[2], vals[3], vals[4], vals[5],
-               vals[6]))
+               vals[6]), vals)
 
 
 def logical_shape(a: torch.Tensor, trans_a: bool, b: torch.Tensor, trans_b: bool) -> Tuple[int, int, int]:

@@ -36,16 +36,32 @@ def _ctx(ctx: Optional[ShmemContext]) -> ShmemContext:
     return ctx if ctx is not None else shmem.default_context()
 
 
-def _grow(ctx: ShmemContext, key: str, nbytes: int) -> SymmBuffer:
-    """Grow-only symmetric region per purpose. Collective by construction: every rank runs the
-    same op sequence with the same shapes, so every rank allocates at the same moments. Fresh
-    regions come zero-filled (stamps start below any epoch)."""
-    buf = ctx.workspaces.get(key)
-    if buf is None or buf.nbytes < nbytes:
-        buf = ctx.malloc(nbytes)
-        ctx.workspaces[key] = buf
+def _data_region(ctx: ShmemContext, purpose: str, half_bytes: int) -> Tuple[SymmBuffer, int]:
+    """The symmetric data region of one purpose (partial-tile slabs, all-reduce output, gathered
+    activation) and the distance between its two parity halves. Collective by construction:
+    every rank runs the same op sequence with the same shapes, so every rank allocates at the
+    same calls.
+
+    The parity stride belongs to the BUFFER (half its size), not to the launch: consecutive
+    launches of different shapes then agree on which bytes are parity 0 and which parity 1, so a
+    rank that is one launch ahead never writes where a peer is still reading, and a result that
+    lives in the heap is not overwritten by the next call of another shape. A shape that needs
+    more than half the region gets a new, larger region; the old one goes back to the heap (the
+    allocator keeps it out of circulation until no rank can still be using it)."""
+    half = (int(half_bytes) + 1023) // 1024 * 1024
+    buf = ctx.workspaces.get(purpose)
+    if buf is None or buf.nbytes < 2 * half:
+        if buf is not None:
+            ctx.free(buf)
+        buf = ctx.malloc(2 * half)
+        ctx.workspaces[purpose] = buf
+        ctx.counters["regions_grown"] = ctx.counters.get("regions_grown", 0) + 1
         _plans_of(ctx).clear()   # plans hold workspace addresses; every rank grows at the same call
-    return buf
+    return buf, (buf.nbytes // 2) // 1024 * 1024
+
+
+def _pair(t: TilingConfig) -> int:
+    return 2 if t.cta_pair == 2 else 1
 
 
 # Launch plans: the argument block of a fused call, keyed by the operands' addresses and layouts
@@ -136,9 +152,13 @@ def _base_args(ctx: ShmemContext, mode: int, a: torch.Tensor, trans_a: bool, b: 
 def _attach_stage(ctx: ShmemContext, args, m: int, n: int, seg_dim: int, t: TilingConfig, partial_fmt: int) -> None:
     lib = N.lib()
     bn = t.effective_bn
-    stage = _grow(ctx, "stage", int(lib.catcoc_stage_bytes(m, n, ctx.world, seg_dim, bn, t.cta_pair, partial_fmt)))
-    arrive = _grow(ctx, "arrive", 4 * int(lib.catcoc_arrive_words(m, n, ctx.world, seg_dim, bn, t.cta_pair)))
+    stage, parity_bytes = _data_region(
+        ctx, "stage", int(lib.catcoc_stage_bytes(m, n, ctx.world, seg_dim, bn, t.cta_pair, partial_fmt)) // 2)
+    # one stamp array per tile geometry: word (tile, source, quarter) is only ever written by `source`
+    arrive = ctx.stamps(("arrive", m, n, ctx.world, seg_dim, bn, _pair(t)),
+                        int(lib.catcoc_arrive_words(m, n, ctx.world, seg_dim, bn, t.cta_pair)))
     args.partial_fmt = partial_fmt
+    args.stage_parity_bytes = parity_bytes
     for p in range(ctx.world):
         args.stage[p] = stage.ptr(p)
         args.arrive[p] = arrive.ptr(p)
@@ -250,9 +270,9 @@ def matmul_allreduce(a: torch.Tensor, b: torch.Tensor, *, trans_a: bool = False,
         args, keep = _base_args(ctx, N.MODE_AR, a, trans_a, b, trans_b, m, n, k, t,
                                 seg_rows=(-(-m // ctx.world)) if seg_dim == _SEG_ROWS else 0)
         args.tiling.seg_dim = seg_dim
-        parity_bytes = (m * n * elt + 255) // 256 * 256
-        obuf = _grow(ctx, "ar_out", 2 * parity_bytes)
-        done = _grow(ctx, "done", 4 * int(lib.catcoc_done_words(m, n, ctx.world, seg_dim, t.effective_bn, t.cta_pair)))
+        obuf, parity_bytes = _data_region(ctx, "ar_out", m * n * elt)
+        done = ctx.stamps(("done", m, n, ctx.world, seg_dim, t.effective_bn, _pair(t)),
+                          int(lib.catcoc_done_words(m, n, ctx.world, seg_dim, t.effective_bn, t.cta_pair)))
         args.out, args.ldc, args.out_fmt = None, n, cm.out_fmt(a.dtype)
         args.ar_out_parity_bytes = parity_bytes
         for p in range(ctx.world):
@@ -342,9 +362,8 @@ def allgather_matmul(a_shard: torch.Tensor, b: torch.Tensor, *, trans_b: bool = 
         args.cta_counter = ctx.launch_state.data_ptr() + 4
         args.status = ctx.status.data_ptr()
         args.ag_m, args.ag_ld = m, ag_ld
-        parity_bytes = (W * m * ag_ld * elt + 255) // 256 * 256
-        gbuf = _grow(ctx, "gathered", 2 * parity_bytes)
-        gfl = _grow(ctx, "gflags", 4 * int(lib.catcoc_gather_flag_words(m, ag_ld, W, elt)))
+        gbuf, parity_bytes = _data_region(ctx, "gathered", W * m * ag_ld * elt)
+        gfl = ctx.stamps(("gflags", m, ag_ld, W, elt, _pair(t)), int(lib.catcoc_gather_flag_words(m, ag_ld, W, elt)))
         args.gathered_parity_bytes = parity_bytes
         for p in range(W):
             args.gathered[p] = gbuf.ptr(p)

@@ -14,6 +14,7 @@ examples/00_matmul_allreduce/matmul_allreduce.cpp:239-300):
 
     ctx = shmem.init(group=None, heap_bytes=2 << 30)
     buf = ctx.malloc(nbytes)              # SymmBuffer: .offset, .tensor(dtype, shape)
+    ctx.free(buf)                         # returns the block (reusable two fused launches later)
     ctx.barrier()                         # device-side barrier_all on the current stream
     ctx.put(peer, dst_buf, src_tensor)    # one-sided copies (non-collective)
     ctx.finalize()
@@ -27,6 +28,7 @@ import ctypes as C
 import os
 import secrets
 import weakref
+from collections import OrderedDict
 from dataclasses import dataclass
 from typing import Dict, List, Optional, Sequence, Tuple
 
@@ -34,9 +36,11 @@ import torch
 import torch.distributed as dist
 
 from .. import _native as N
+from .allocator import HeapExhausted, SymmAllocator
 
 DEFAULT_HEAP_BYTES = 2 << 30
 _ALIGN = 256
+_MAX_STAMP_REGIONS = 64
 
 
 class ShmemError(RuntimeError):
@@ -94,16 +98,20 @@ class ShmemContext:
         self._bases = [int(N.lib().catcoc_heap_base(handle, p) or 0) for p in range(world)]
         self.mc_base = int(N.lib().catcoc_heap_mc_base(handle) or 0) if multicast else 0
         self._local_bytes = torch.as_tensor(_RawCudaMemory(self._bases[rank], heap_bytes, self), device=device)
-        self._cursor = 0
+        # Stamps are compared with launch epochs, so no word of the heap may start out above zero.
+        # init() synchronises and meets the peers after this, before anybody can write here.
+        self._local_bytes.zero_()
+        self._alloc = SymmAllocator(heap_bytes)
+        self.epoch = 0  # host mirror of launch_state[0]: fused launches issued on this context
         self._finalized = False
         self.status = torch.zeros(8, dtype=torch.int32, device=device)
         # launch bookkeeping of the fused kernels: [0] completed launches (epoch), [1] CTA counter
         self.launch_state = torch.zeros(2, dtype=torch.int32, device=device)
         self._barrier_buf = self.malloc(4 * N.MAX_WORLD)
         self._barrier_epoch = 0
-        self.workspaces: Dict[str, object] = {}
+        self.workspaces: Dict[object, object] = {}   # data regions of the fused ops, by purpose
+        self.stamp_regions: "OrderedDict[object, SymmBuffer]" = OrderedDict()   # stamp arrays, by geometry
         self.plans: Dict[object, object] = {}   # launch plans of the fused ops (ops/fused.py)
-        self.epoch = 0  # host mirror of launch_state[0]: fused launches completed on this context
         self.counters: Dict[str, int] = {"launches": 0, "bytes_pushed": 0, "pad_copies": 0}
 
     # ---- addresses -------------------------------------------------------------------
@@ -122,20 +130,50 @@ class ShmemContext:
         return c
 
     # ---- allocator (collective: every rank must make the same sequence of calls) ------
-    def malloc(self, nbytes: int, align: int = _ALIGN) -> SymmBuffer:
+    def malloc(self, nbytes: int) -> SymmBuffer:
+        """A block of the heap at the same offset on every rank (256-byte aligned). The contents
+        are whatever the block last held; stamp arrays are zeroed by their owner (``stamps``)."""
         if nbytes <= 0:
             raise ShmemError("malloc of %d bytes" % nbytes)
-        start = (self._cursor + align - 1) // align * align
-        if start + nbytes > self.heap_bytes:
-            raise ShmemError(
-                "symmetric heap exhausted: need %d bytes at offset %d, heap is %d bytes per rank "
-                "(raise heap_bytes in shmem.init or CATCOC_HEAP_BYTES)" % (nbytes, start, self.heap_bytes))
-        self._cursor = start + nbytes
+        try:
+            start = self._alloc.malloc(nbytes, tick=self.epoch)
+        except HeapExhausted as e:
+            raise ShmemError("%s; the heap has %d bytes per rank (raise heap_bytes in shmem.init or "
+                             "CATCOC_HEAP_BYTES)" % (e, self.heap_bytes)) from None
         return SymmBuffer(self, start, nbytes)
 
-    def free_all_after(self, buf: SymmBuffer) -> None:
-        """Stack-style release: everything allocated after ``buf`` (and ``buf`` itself)."""
-        self._cursor = min(self._cursor, buf.offset)
+    def free(self, buf: SymmBuffer) -> None:
+        """Returns a block to the heap (the reference's shmem_free,
+        examples/00_matmul_allreduce/matmul_allreduce.cpp:290). Collective like ``malloc``. The
+        block is handed out again only after two more fused launches were issued on this
+        context: peers run at most one launch apart, so by then none of them can still touch it.
+        A caller that moves data with ``put`` / ``get`` outside the fused ops must make sure with a
+        ``barrier()`` that no peer still uses the block."""
+        try:
+            self._alloc.free(buf.offset, tick=self.epoch)
+        except ValueError as e:
+            raise ShmemError(str(e)) from None
+
+    def stamps(self, key, words: int) -> SymmBuffer:
+        """The stamp array of one (purpose, geometry) ``key``, created on first use. Collective:
+        every rank reaches the first use of a key at the same call. A new array is zeroed and the
+        ranks meet at a device barrier before anybody stamps it. Arrays are kept per geometry so
+        that every word has one writer and one meaning for as long as it lives; the least recently
+        used ones are released when more than ``_MAX_STAMP_REGIONS`` exist."""
+        buf = self.stamp_regions.get(key)
+        if buf is not None:
+            self.stamp_regions.move_to_end(key)
+            return buf
+        while len(self.stamp_regions) >= _MAX_STAMP_REGIONS:
+            _, old = self.stamp_regions.popitem(last=False)
+            self.free(old)
+            self.plans.clear()   # plans may hold the released addresses
+        buf = self.malloc(4 * max(1, int(words)))
+        buf.tensor(torch.int32).zero_()
+        if self.world > 1:
+            self.barrier()
+        self.stamp_regions[key] = buf
+        return buf
 
     def empty(self, shape: Sequence[int], dtype: torch.dtype) -> Tuple[torch.Tensor, SymmBuffer]:
         n = 1
@@ -146,7 +184,12 @@ class ShmemContext:
 
     @property
     def bytes_in_use(self) -> int:
-        return self._cursor
+        return self._alloc.bytes_in_use
+
+    @property
+    def high_water(self) -> int:
+        """Largest offset the allocator has handed out so far."""
+        return self._alloc.high_water
 
     # ---- synchronisation ---------------------------------------------------------------
     def _stream(self) -> C.c_void_p:
@@ -248,6 +291,7 @@ class ShmemContext:
         except Exception:
             pass
         self.workspaces.clear()
+        self.stamp_regions.clear()
         self.plans.clear()
         self._local_bytes = None
         N.lib().catcoc_heap_destroy(self._h)
@@ -375,6 +419,9 @@ def init(group=None, heap_bytes: Optional[int] = None, device: Optional[torch.de
                 use_mc = _setup_multicast(handle, rank, world, uid, group, bootstrap_timeout_ms)
             dist.barrier(group=group)
         ctx = ShmemContext(group, rank, world, device, handle, int(lib.catcoc_heap_bytes(handle)), use_mc)
+        torch.cuda.synchronize(device)   # the heap is zeroed ...
+        if world > 1:
+            dist.barrier(group=group)    # ... on every rank before any peer may write into it
     except Exception:
         lib.catcoc_heap_destroy(handle)
         raise

@@ -87,6 +87,96 @@ def run_mixed_launches(ctx, W, iters, name):
     report(name, ok)
 
 
+class _DeviceCheck:
+    """Acceptance rule of ``verify`` evaluated on the device and accumulated without a host
+    synchronisation, so that the launches under test stay back to back."""
+
+    def __init__(self, gold, k, dtype, magnitude=None):
+        from mm_rs_with_catlass_b200.utils.verify import get_rtol
+        g = gold.float()
+        scale = g.abs() if magnitude is None else torch.maximum(g.abs(), magnitude.float())
+        self.gold = g
+        self.tol = get_rtol(dtype, k) * torch.clamp(scale, min=1.0)
+        self.bad = torch.zeros((), dtype=torch.int64, device=gold.device)
+        self.calls = 0
+
+    def add(self, out):
+        o = out.float()
+        self.bad += ((o - self.gold).abs() > self.tol).sum() + (~torch.isfinite(o)).sum()
+        self.calls += 1
+
+
+def run_mixed_geometries(ctx, W, iters, name):
+    """Back-to-back launches that alternate DIFFERENT tile geometries and ops on one context,
+    several tiles per segment, rank-dependent data, no host synchronisation between calls and
+    rank-dependent stalls in between (so ranks really run a launch apart). Every result of every
+    iteration is checked on the device. This is the case in which stamp words or slab bytes
+    shared between geometries would be overwritten by a rank that runs ahead or lags behind."""
+    T = catcoc.TilingConfig
+    bf = torch.bfloat16
+    cases = []
+    # reduce-scatter on 256-row pair tiles, 4 x 2 tiles per segment
+    a, b = matmul_inputs(1024 * W, 512, 256, rank, bf, dev, seed=201)
+    gold = ref.matmul_allreduce(a, b, out_dtype=torch.float32)
+    mag = ref.partial_magnitude(a, b)
+    sl = slice(rank * 1024, (rank + 1) * 1024)
+    t_rs_pair = T(bn=256, cta_pair=2, swizzle=2)
+    cases.append(("rs_pair", lambda a=a, b=b: catcoc.matmul_reduce_scatter(a, b, tiling=t_rs_pair),
+                  _DeviceCheck(gold[sl], 256 * W, bf, mag[sl])))
+    # all-reduce with column ownership on 128-row tiles (2 x 2 tiles per segment)
+    a2, b2 = matmul_inputs(256, 256 * W, 192, rank, bf, dev, seed=202)
+    gold2 = ref.matmul_allreduce(a2, b2, out_dtype=torch.float32)
+    t_ar_cols = T(bn=128, seg_dim=1, use_multicast=bool(ctx.multicast))
+    cases.append(("ar_cols", lambda: catcoc.matmul_allreduce(a2, b2, tiling=t_ar_cols).clone(),
+                  _DeviceCheck(gold2, 192 * W, bf, ref.partial_magnitude(a2, b2))))
+    # all-gather with another K
+    a3, b3 = matmul_inputs(192, 384, 320, rank, bf, dev, seed=203)
+    gold3, _ = ref.allgather_matmul(a3, b3, out_dtype=torch.float32)
+    cases.append(("ag", lambda: catcoc.allgather_matmul(a3, b3)[0], _DeviceCheck(gold3, 320, bf)))
+    # quantised reduce-scatter on pair tiles with four lagged rounds
+    x1, x2, s1, s2, bias = quant_inputs(1024 * W, 256, 256, rank, dev, seed=204)
+    gold4 = ref.quant_matmul_reduce_scatter(x1, x2, s1, s2, bias, out_dtype=torch.float32)
+    t_q = T(bn=256, cta_pair=2, rounds=4)
+    cases.append(("qrs_rounds4", lambda: catcoc.quant_matmul_reduce_scatter(x1, x2, s1, s2, bias, tiling=t_q),
+                  _DeviceCheck(gold4, 512, bf)))
+    # reduce-scatter of another shape on single 128-column tiles, and an all-reduce by rows
+    a5, b5 = matmul_inputs(256 * W, 384, 128, rank, bf, dev, seed=205)
+    gold5 = ref.matmul_allreduce(a5, b5, out_dtype=torch.float32)
+    mag5 = ref.partial_magnitude(a5, b5)
+    sl5 = slice(rank * 256, (rank + 1) * 256)
+    t_single = T(bn=128, cta_pair=1)
+    cases.append(("rs_single", lambda: catcoc.matmul_reduce_scatter(a5, b5, tiling=t_single),
+                  _DeviceCheck(gold5[sl5], 128 * W, bf, mag5[sl5])))
+    t_ar_rows = T(bn=128, seg_dim=0)
+    cases.append(("ar_rows", lambda: catcoc.matmul_allreduce(a5, b5, tiling=t_ar_rows).clone(),
+                  _DeviceCheck(gold5, 128 * W, bf, mag5)))
+    # the all-reduce result lives in the heap: the next call of another shape must not touch it
+    keep = catcoc.matmul_allreduce(a2, b2, tiling=t_ar_cols)
+    catcoc.matmul_allreduce(a5, b5, tiling=t_ar_rows)
+    cases[1][2].add(keep)
+    g = torch.Generator()
+    g.manual_seed(4242)
+    order = torch.randint(0, len(cases), (iters,), generator=g).tolist()
+    stalls = torch.randint(0, W * 4, (iters,), generator=g).tolist()
+    for it in range(iters):
+        if stalls[it] == rank:
+            torch.cuda._sleep(400000)   # about 0.2 ms: lets the other ranks run ahead
+        _, fn, chk = cases[order[it]]
+        chk.add(fn())
+    ok = True
+    try:
+        ctx.check(name)
+    except RuntimeError as e:
+        ok = False
+        print("rank", rank, e, flush=True)
+    for cname, _, chk in cases:
+        nbad = int(chk.bad.item())
+        if nbad:
+            ok = False
+            print("rank %d: %s: %d elements out of tolerance over %d calls" % (rank, cname, nbad, chk.calls), flush=True)
+    report(name, ok)
+
+
 TILINGS = [None, catcoc.TilingConfig(bn=128, cta_pair=1), catcoc.TilingConfig(bn=256, cta_pair=2, swizzle=4)]
 
 if mode == "ops":
@@ -189,6 +279,7 @@ if mode == "ops":
     exp = ((128.0 + torch.arange(1, 257, device=dev).float()) * W * 1e-4)[None, :].expand(32, 256)
     report("qrs_debug_pattern", bool(torch.allclose(o, exp, rtol=1e-5)))
     run_mixed_launches(ctx, W, 60, "repeat_60_mixed_launches")
+    run_mixed_geometries(ctx, W, 120, "mixed_geometries_120")
     # the flagship block
     from mm_rs_with_catlass_b200.models.tp_mlp import TPMLP, TPMLPConfig
     mlp = TPMLP(TPMLPConfig(hidden=512, ffn=256 * W), ctx, dev)
@@ -202,6 +293,12 @@ elif mode == "repeat":
     # the mixed-launch loop alone, long: cheap to run when hunting a protocol race
     ctx = catcoc.init(heap_bytes=1 << 30, multicast=(os.environ.get("CATCOC_TEST_NVLS", "1") == "1"))
     run_mixed_launches(ctx, world, int(os.environ.get("CATCOC_TEST_REPEATS", "600")), "repeat_mixed_launches")
+    ctx.finalize()
+
+elif mode == "mixed":
+    # different geometries back to back, no synchronisation between the calls
+    ctx = catcoc.init(heap_bytes=2 << 30, multicast=(os.environ.get("CATCOC_TEST_NVLS", "1") == "1"))
+    run_mixed_geometries(ctx, world, int(os.environ.get("CATCOC_TEST_REPEATS", "400")), "mixed_geometries")
     ctx.finalize()
 
 elif mode == "withhold":

@@ -47,6 +47,16 @@ def test_fused_ops_match_goldens(world, gpu_count):
     assert len(cases) > 100
 
 
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_mixed_geometries_back_to_back(world, gpu_count):
+    """Different tile geometries and ops alternate on one context with no synchronisation in
+    between; every result is checked. On three or more GPUs this is the sequence in which stamp
+    words shared between geometries used to be overwritten by a lagging rank."""
+    if gpu_count < world:
+        pytest.skip("needs %d GPUs" % world)
+    _run(world, "mixed", {"CATCOC_TIMEOUT_MS": "2000"}, timeout=600)
+
+
 def test_fused_ops_on_plain_peer_stores_without_nvls(gpu_count):
     if gpu_count < 2:
         pytest.skip("needs 2 GPUs")
