@@ -22,10 +22,14 @@ def _run(world, mode, extra_env=None, timeout=900):
     env = dict(os.environ)
     env.setdefault("CATCOC_TIMEOUT_MS", "5000")
     env.update(extra_env or {})
-    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", str(world),
-           "--master-addr", "127.0.0.1", "--master-port", str(_free_port()), os.path.join(HERE, "multi_gpu_worker.py"),
-           mode]
-    proc = subprocess.run(cmd, capture_output=True, text=True, timeout=timeout, env=env)
+    for attempt in range(3):
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", str(world),
+               "--master-addr", "127.0.0.1", "--master-port", str(_free_port()),
+               os.path.join(HERE, "multi_gpu_worker.py"), mode]
+        proc = subprocess.run(cmd, capture_output=True, text=True, timeout=timeout, env=env)
+        # the port found free a moment ago can be taken by the time the rendezvous binds it
+        if proc.returncode == 0 or "EADDRINUSE" not in proc.stderr:
+            break
     cases = []
     for line in proc.stdout.splitlines():
         if line.startswith("{"):
