@@ -34,7 +34,8 @@ STATUS_NAMES = {
 
 class Tiling(C.Structure):
     _fields_ = [("bn", C.c_int), ("swizzle", C.c_int), ("num_ctas", C.c_int), ("seg_dim", C.c_int),
-                ("use_multicast", C.c_int), ("rounds", C.c_int), ("cta_pair", C.c_int)]
+                ("use_multicast", C.c_int), ("rounds", C.c_int), ("cta_pair", C.c_int), ("pull", C.c_int),
+                ("comm_warps", C.c_int)]
 
 
 class OpArgs(C.Structure):
@@ -56,6 +57,8 @@ class OpArgs(C.Structure):
         ("ar_out_mc", C.c_void_p),
         ("done", C.c_void_p * MAX_WORLD),
         ("done_mc", C.c_void_p),
+        ("part", C.c_void_p), ("part_mc", C.c_void_p), ("part_parity_bytes", C.c_int64),
+        ("gathered_mc", C.c_void_p), ("gflags_mc", C.c_void_p),
         ("gathered", C.c_void_p * MAX_WORLD),
         ("gathered_parity_bytes", C.c_int64),
         ("gflags", C.c_void_p * MAX_WORLD),
@@ -109,6 +112,7 @@ def _declare(lib) -> None:
         "catcoc_sched_total_tiles": (i32, [i32] * 6),
         "catcoc_sched_get_tile": (i32, [i32] * 9 + [P(Tile)]),
         "catcoc_sched_get_tile_rounds": (i32, [i32] * 10 + [P(Tile)]),
+        "catcoc_sched_get_tile_order": (i32, [i32] * 10 + [P(Tile)]),
         "catcoc_group_walk_replay": (i32, [i32, i32, i32, i32, i32, vp, i32, i32, P(Tile)]),
         "catcoc_oracle_matmul_f32": (i32, [vp, vp, vp, i32, i32, i32, i32, i32]),
         "catcoc_oracle_quant_matmul": (i32, [vp, vp, vp, vp, i32, i32, i32, i32, i32]),

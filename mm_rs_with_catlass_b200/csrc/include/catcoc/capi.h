@@ -46,6 +46,9 @@ typedef struct CatcocTiling {
   int use_multicast; /* all-reduce broadcast through the NVLS multicast alias if mapped  */
   int rounds;      /* owner work is spread over this many rounds (0 = default); reduce-scatter / all-reduce */
   int cta_pair;    /* 2: 256-row tiles on 2-CTA clusters (tcgen05 cta_group::2); else 1 CTA */
+  int pull;        /* reduce-scatter / all-reduce: 1 = partial tiles stay in the local heap and the owner
+                      sums them through the switch (multimem.ld_reduce); needs the multicast alias   */
+  int comm_warps;  /* communication / reducer warps per CTA, 1..5 (0 = 5); all-gather and pull flavours */
 } CatcocTiling;
 
 typedef struct CatcocOpArgs {
@@ -70,6 +73,11 @@ typedef struct CatcocOpArgs {
   void* ar_out_mc;                         /* multicast alias or NULL                    */
   uint32_t* done[CATCOC_MAX_WORLD];
   uint32_t* done_mc;
+  void* part;                              /* pull flavour: this rank's partial buffer (parity 0) ... */
+  void* part_mc;                           /* ... and its multicast alias                */
+  int64_t part_parity_bytes;
+  void* gathered_mc;                       /* all-gather with use_multicast: aliases of gathered / gflags */
+  uint32_t* gflags_mc;
   void* gathered[CATCOC_MAX_WORLD];        /* all-gather: gathered A (parity 0)          */
   int64_t gathered_parity_bytes;
   uint32_t* gflags[CATCOC_MAX_WORLD];
@@ -128,6 +136,10 @@ int catcoc_sched_get_tile(int M, int N, int bm, int bn, int W, int seg_dim, int 
                           int swizzle, int t, CatcocTile* out);
 int catcoc_sched_get_tile_rounds(int M, int N, int bm, int bn, int W, int seg_dim, int first_seg,
                                  int swizzle, int rounds, int t, CatcocTile* out);
+/* order: 0 rotated (segment after segment from first_seg), 1 interleaved (tile i of every segment, then
+ * tile i + 1: pull flavours), 2 local first (segment first_seg, then the others interleaved: multicast all-gather) */
+int catcoc_sched_get_tile_order(int M, int N, int bm, int bn, int W, int seg_dim, int first_seg,
+                                int swizzle, int order, int t, CatcocTile* out);
 /* Host replay of the group walk of a grouped / batched / split-K launch: writes up to max_tiles
  * tiles in launch order (seg = group) and returns the walk's tile count. `ends` is host memory
  * here (cumulative rows per group) or NULL for uniform groups of group_rows rows. */

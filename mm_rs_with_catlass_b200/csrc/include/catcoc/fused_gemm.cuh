@@ -45,7 +45,7 @@ constexpr int kThreads = 256;          // warps 0-6 are the GEMM roles, warp 7 a
 // it carries two more communication warps: the push of the A shard is latency bound per warp and
 // one warp per SM could not feed the link (measured 173 GB/s per GPU, the GEMM waited on it).
 constexpr int kThreadsPlain = 384;
-CATCOC_HD constexpr int threads_for(int epi) { return epi == EPI_PLAIN ? kThreadsPlain : kThreads; }
+CATCOC_HD constexpr int threads_for(int epi) { return (epi == EPI_PLAIN || epi == EPI_PULL) ? kThreadsPlain : kThreads; }
 constexpr int kTmemCols = 512;
 constexpr int kMaxStages = 6;
 
@@ -110,13 +110,16 @@ struct Tick {
 };
 
 // Polls a stamp until it reaches `epoch` (wrap-safe), the time budget ends or the CTA aborts.
+// `pace_ns` > 0 sleeps that long between polls (for waits that are expected to be long and must
+// not load the memory system meanwhile).
 CATCOC_DEVICE bool wait_stamp(const uint32_t* flag, uint32_t epoch, uint64_t timeout_ns,
-                              volatile uint32_t* abort_flag, uint32_t* seen) {
+                              volatile uint32_t* abort_flag, uint32_t* seen, uint32_t pace_ns = 0) {
   uint32_t v = ptx::ld_acquire_sys_u32(flag);
   if (static_cast<int32_t>(v - epoch) >= 0) return true;
   const uint64_t t0 = ptx::globaltimer_ns();
   uint32_t spins = 0;
   while (true) {
+    if (pace_ns) __nanosleep(pace_ns);
     v = ptx::ld_acquire_sys_u32(flag);
     if (static_cast<int32_t>(v - epoch) >= 0) return true;
     if ((++spins & 0xf) == 0) {
@@ -239,8 +242,9 @@ template <int KIND, bool CTA2, int EPI>
 __global__ void __launch_bounds__(threads_for(EPI), 1)
 fused_gemm_kernel(const __grid_constant__ FusedParams p) {
   // Epilogue variant (see EpiVariant in params.h): stages a launch cannot need are compiled out.
-  constexpr bool kReduce = (EPI >= EPI_REDUCE);   // reduce-scatter / all-reduce: peers' partials, pushes, stamps
+  constexpr bool kReduce = (EPI == EPI_REDUCE || EPI == EPI_FULL);   // push flavour of RS / AR: peers' partials, pushes, stamps
   constexpr bool kScale = (EPI == EPI_FULL);      // int32 bias, dequantisation, alpha / beta / C / fp32 bias
+  constexpr bool kPull = (EPI == EPI_PULL);       // pull flavour of RS / AR: local partials, stamps, reducer warps
   using G = Geo<CTA2>;
   constexpr int kStages = G::kStages;
   constexpr int kStageBytes = G::kStageBytes;
@@ -263,6 +267,7 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
   const int sub_bytes = (kps != kKPS) ? (kABytes + BN * 128) : kSubBytes;
   const int num_kb = ceil_div(p.K, p.bk * kps);   // pipeline stages per tile
   const bool fused = (p.mode != MODE_LOCAL) && (p.W > 1);
+  const bool pull = kPull && fused && (p.pull != 0) && (p.mode == MODE_RS || p.mode == MODE_AR);
   // Pair flavour: `sub` is this CTA's half of the 256-row tile, work is dealt out per pair.
   const int sub = CTA2 ? static_cast<int>(ptx::cluster_ctarank()) : 0;
   const bool leader = (sub == 0);
@@ -295,7 +300,7 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
     ptx::mbar_fence_init();
     ptx::prefetch_tmap(&p.tm_a);
     ptx::prefetch_tmap(&p.tm_b);
-    if (p.out_tma) ptx::prefetch_tmap(&p.tm_out);
+    if (p.out_tma) ptx::prefetch_tmap(kPull && p.pull ? &p.tm_part[0] : &p.tm_out);
   }
   if (warp == 1) {
     if (CTA2) {
@@ -623,6 +628,7 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
     // stall the warp for a link round trip. `pending_stamp` is the stamp still owed (lane 0).
     const bool any_tma = (p.out_tma != 0) || (kReduce && p.stage_tma != 0);
     uint32_t* pending_stamp = nullptr;
+    bool prev_win_tma = false;   // the most recent window of this warp left by a TMA store
     auto settle_pending = [&]() {
       // every bulk store of this warp is complete; its stamp can go out
       if (lane == 0 && pending_stamp != nullptr) {
@@ -638,7 +644,7 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
       const TileInfo ti = walk_tile(p, t, walk);
       const bool own = !kReduce || !fused || (p.mode == MODE_AG) || (ti.seg == p.rank);
       const bool reduce_here = kReduce && fused && own && (p.mode == MODE_RS || p.mode == MODE_AR);
-      const int st_fmt = own ? p.out_fmt : pfmt;   // format of what this tile's epilogue stores
+      const int st_fmt = (own && !pull) ? p.out_fmt : pfmt;   // format of what this tile's epilogue stores
       const int st_elt = fmt_bytes(st_fmt);
       const int rows_valid = max(0, min(32, ti.rows - row_base));
       const int nvec_off = grouped ? ti.seg * p.g_nvec : 0;   // this group's per-column vectors
@@ -685,7 +691,14 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
       uint8_t* const* peer_bases = nullptr;  // broadcast by per-peer stores
       int64_t off = 0;
       bool vec_ok = true;
-      if (!own) {
+      const int64_t row_shift = pull ? 0 : p.out_row_shift;
+      if (kPull && pull) {
+        // the partial tile goes to its true (m, n) position of this rank's own partial buffer
+        pitch = p.ldp * st_elt;
+        base = p.part_local + static_cast<int64_t>(parity) * p.part_parity_bytes +
+               (static_cast<int64_t>(ti.m0 + row_base) * p.ldp + ti.n0) * st_elt;
+        vec_ok = (p.out_vec_ok != 0) && ((ti.n0 * st_elt) % 16 == 0);
+      } else if (!own) {
         pitch = static_cast<int64_t>(BN) * st_elt;
         base = p.stage[ti.seg] + stage_slot_offset(sched, st_elt, p.stage_parity_bytes, parity, p.rank, ti.tile_in_seg) +
                static_cast<int64_t>(row_base) * pitch;
@@ -702,7 +715,7 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
       } else {
         pitch = p.ldc * st_elt;
         base = static_cast<uint8_t*>(p.out) +
-               (static_cast<int64_t>(ti.m0 + row_base - p.out_row_shift) * p.ldc + ti.n0) * st_elt;
+               (static_cast<int64_t>(ti.m0 + row_base - row_shift) * p.ldc + ti.n0) * st_elt;
         vec_ok = (p.out_vec_ok != 0) && ((ti.n0 * st_elt) % 16 == 0);
       }
 
@@ -720,26 +733,36 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
       // A partial tile goes to its owner's slab the same way. Slabs are BM x BN whatever the
       // tile's valid extent, so whole windows are pushed and nothing needs clipping.
       const bool tma_push = kReduce && !own && (p.stage_tma != 0);
+      // pull flavour: the stamp of a tile stored by TMA follows the completion of its bulk stores
+      const bool stamp_late = tma_push || (kPull && pull && tma_out && rows_valid > 0);
+      const CUtensorMap* tm_o = (kPull && pull) ? &p.tm_part[parity] : &p.tm_out;
       const int push_row0 = tma_push
           ? static_cast<int>(stage_slot_offset(sched, st_elt, p.stage_parity_bytes, parity, p.rank, ti.tile_in_seg) /
                              (static_cast<int64_t>(BN) * st_elt)) + row_base
           : 0;
       int groups_sent = 0;
+      // A tile that ends at a segment boundary inside the matrix (column-split ownership) must not
+      // store past its last column: TMA clips at the tensor's edge only, so such a window (its
+      // unused half holds stale staging bytes) leaves by plain, clipped stores.
+      const bool cols_by_tensor_edge = (ti.n0 + ti.cols >= sched.N);
 
       for (int win = 0; win < nwin; ++win) {
         if (win * groups_per_win * 32 >= ti.cols) break;
+        const bool win_full = cols_by_tensor_edge || ((win + 1) * groups_per_win * 32 <= ti.cols);
+        const bool win_tma_out = tma_out && win_full;
         // the store that read this staging buffer two windows ago must be done with it
         const uint32_t stg = stg_base + (win_count & 1u) * kEpiWinBytes;
         ++win_count;
         if (any_tma) {
           if (lane == 0) {
-            // a window sent by TMA leaves one younger store in flight; a window sent by plain
-            // stores adds no group, so everything older has to be drained
-            if (tma_out || tma_push) ptx::bulk_wait_group_read<1>();
+            // if the previous window left by TMA its store may still be reading the OTHER buffer;
+            // a window sent by plain stores adds no group, so everything older has to be drained
+            if (prev_win_tma) ptx::bulk_wait_group_read<1>();
             else ptx::bulk_wait_group_read<0>();
           }
           __syncwarp();
         }
+        prev_win_tma = tma_push || (win_tma_out && rows_valid > 0);
         for (int h = 0; h < groups_per_win; ++h) {
           const int g = win * groups_per_win + h;
           const int col0 = g * 32;
@@ -940,13 +963,13 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
               ptx::bulk_commit_group();
             }
             ++groups_sent;
-          } else if (tma_out) {
+          } else if (win_tma_out) {
             if (rows_valid > 0) {
               ptx::fence_proxy_async_smem();   // the staged bytes become visible to the TMA unit
               __syncwarp();
               if (lane == 0) {
-                ptx::tma_store_2d(&p.tm_out, stg, ti.n0 + win * per_win,
-                                  static_cast<int>(ti.m0 + row_base - p.out_row_shift));
+                ptx::tma_store_2d(tm_o, stg, ti.n0 + win * per_win,
+                                  static_cast<int>(ti.m0 + row_base - row_shift));
                 ptx::bulk_commit_group();
               }
             }
@@ -971,7 +994,22 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
       }
 
       // ---- publish this warp's quarter of the tile ----
-      if (kReduce && fused && (p.mode == MODE_RS || p.mode == MODE_AR) && (!own || p.mode == MODE_AR)) {
+      if (kPull && pull) {
+        // Tell the tile's owner that this rank's partial rows are in place. Plain stores are ordered
+        // before the release by the warp barrier; TMA stores must have completed first. They go to
+        // local memory, so the wait is short, and the accumulator was handed back before it: unlike
+        // a push over the link this costs less than announcing the tile one tile late would (with a
+        // deep K the next tile ends tens of microseconds later, and the owner would sit idle).
+        __syncwarp();
+        if (lane == 0 && !p.withhold_signals) {
+          if (stamp_late) {
+            ptx::bulk_wait_group_all();
+            ptx::fence_proxy_async();
+          }
+          ptx::st_release_sys_u32(p.arrive[ti.seg] + arrive_flag_index(sched, ti.tile_in_seg, p.rank) * qpt + qid,
+                                  epoch);
+        }
+      } else if (kReduce && fused && (p.mode == MODE_RS || p.mode == MODE_AR) && (!own || p.mode == MODE_AR)) {
         // Data stores of all 32 lanes happen-before lane 0's release through the warp barrier;
         // the release is cumulative, so one system-scope release by one lane publishes them all.
         __syncwarp();
@@ -1019,7 +1057,7 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
 
     // every TMA store of this warp has to be performed before the kernel ends, and the last
     // pushed tile is still unannounced
-    if (kReduce) settle_pending();
+    if (kReduce || kPull) settle_pending();
     if (any_tma && lane == 0) ptx::bulk_wait_group_all();
     __syncwarp();
     tick.lap(c_work);
@@ -1031,7 +1069,7 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
     }
 
     // all-reduce tail: this rank's output is complete only when every owner's tiles landed
-    if (kReduce && fused && p.mode == MODE_AR && ok && !*abort_flag) {
+    if ((kReduce || kPull) && fused && p.mode == MODE_AR && ok && !*abort_flag) {
       const int et = (warp - 2) * 32 + lane;
       const int nstamps = sched.total_tiles * qpt;
       for (int j = blockIdx.x + et * gridDim.x; j < nstamps; j += gridDim.x * kEpiWarps * 32) {
@@ -1112,15 +1150,19 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
       }
     }
   } else {
-    // ======================= communication warp (all-gather) =======================
-    // Push this rank's A shard into every rank's gathered buffer in units of
-    // chunk_rows x 512 B, peer-major: the peer that consumes the shard first is served first.
+    // ======================= communication warps =======================
+    const int cw = warp - (3 + kEpiWarps);               // this communication warp ...
+    const int ncw = static_cast<int>(blockDim.x >> 5) - (3 + kEpiWarps);   // ... of so many per CTA
     if (fused && p.mode == MODE_AG) {
-      const int cw = warp - (3 + kEpiWarps);               // this communication warp ...
-      const int ncw = static_cast<int>(blockDim.x >> 5) - (3 + kEpiWarps);   // ... of so many per CTA
+      // All-gather: send this rank's A shard into every rank's gathered buffer in units of
+      // chunk_rows x 512 B. With the multicast alias one multimem.st per 16 bytes reaches every
+      // rank (the shard leaves this GPU once), chunk-major: the consumers visit the chunks of all
+      // peers side by side. Without it the units go to one peer after the other, the peer that
+      // consumes the shard first is served first.
       const GatherPlan& gp = p.gp;
+      const bool mcast = (p.gathered_mc != nullptr) && (p.gflags_mc != nullptr);
       const int units_per_peer = gp.n_chunks * gp.n_slices;
-      const int64_t total_units = static_cast<int64_t>(p.W) * units_per_peer;
+      const int64_t total_units = mcast ? units_per_peer : static_cast<int64_t>(p.W) * units_per_peer;
       const int slice_bytes = gp.slice_cols * p.elt_bytes_a;   // <= 512
       const int64_t row_bytes = static_cast<int64_t>(gp.K) * p.elt_bytes_a;
       for (int64_t u = static_cast<int64_t>(blockIdx.x) * ncw + cw; u < total_units;
@@ -1136,7 +1178,8 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
         const int64_t cb = static_cast<int64_t>(slice) * slice_bytes + lane * 16;
         const bool col_ok = (lane * 16 < slice_bytes) && (cb + 16 <= row_bytes);
         const uint8_t* src = p.a_local + static_cast<int64_t>(r0) * p.a_local_pitch + cb;
-        uint8_t* dstp = p.gathered[peer] + static_cast<int64_t>(parity) * p.gathered_parity_bytes +
+        uint8_t* dstp = (mcast ? p.gathered_mc : p.gathered[peer]) +
+                        static_cast<int64_t>(parity) * p.gathered_parity_bytes +
                         (static_cast<int64_t>(p.rank) * gp.m + r0) * p.gathered_pitch + cb;
         if (col_ok) {
           // 16 rows (8 KiB per warp) in flight per round trip: the copy is latency bound, which is
@@ -1147,17 +1190,99 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
             for (int i = 0; i < 16; ++i)
               if (r + i < nrows)
                 buf[i] = ptx::ld_global_nc_v4(src + static_cast<int64_t>(r + i) * p.a_local_pitch);
+            if (mcast) {
 #pragma unroll
-            for (int i = 0; i < 16; ++i)
-              if (r + i < nrows)
-                ptx::st_global_v4(dstp + static_cast<int64_t>(r + i) * p.gathered_pitch, buf[i]);
+              for (int i = 0; i < 16; ++i)
+                if (r + i < nrows)
+                  ptx::multimem_st_v4(dstp + static_cast<int64_t>(r + i) * p.gathered_pitch, buf[i]);
+            } else {
+#pragma unroll
+              for (int i = 0; i < 16; ++i)
+                if (r + i < nrows)
+                  ptx::st_global_v4(dstp + static_cast<int64_t>(r + i) * p.gathered_pitch, buf[i]);
+            }
           }
         }
         // all lanes' stores happen-before lane 0's release through the warp barrier (cumulative)
         __syncwarp();
-        if (lane == 0 && !p.withhold_signals)
-          ptx::st_release_sys_u32(p.gflags[peer] + gather_flag_index(gp, p.rank, chunk, slice),
-                                  epoch);
+        if (lane == 0 && !p.withhold_signals) {
+          const int64_t fi = gather_flag_index(gp, p.rank, chunk, slice);
+          if (mcast) ptx::multimem_st_release_u32(p.gflags_mc + fi, epoch);
+          else ptx::st_release_sys_u32(p.gflags[peer] + fi, epoch);
+        }
+      }
+    } else if (kPull && pull) {
+      // Reducer warps of the pull flavour. Task j = (i-th tile of MY segment in visiting order, a
+      // 32-row quarter of it), dealt out round-robin over all reducer warps of the grid so that
+      // the tiles that finish first are reduced first. A task waits until every rank's stamp for
+      // that quarter is in, reads the sum of the W partial copies through the switch
+      // (multimem.ld_reduce, fp32 accumulation) and stores it: into `out` (reduce-scatter) or, with
+      // one multimem.st per 16 bytes, into every rank's output followed by a `done` stamp
+      // (all-reduce). Nothing in the GEMM pipeline ever waits for these warps.
+      const int gw = static_cast<int>(blockIdx.x) * ncw + cw;
+      const int total_gw = static_cast<int>(gridDim.x) * ncw;
+      const int tasks = sched.tiles_per_seg * qpt;
+      const bool bf = (p.partial_fmt == FMT_BF16);
+      const uint8_t* src_base = p.part_mc + static_cast<int64_t>(parity) * p.part_parity_bytes;
+      const bool ar = (p.mode == MODE_AR);
+      uint8_t* dst_base = ar ? p.ar_out_mc + static_cast<int64_t>(parity) * p.ar_out_parity_bytes
+                             : static_cast<uint8_t*>(p.out);
+      bool ok = true;
+      for (int j = gw; ok && j < tasks; j += total_gw) {
+        if (*abort_flag) break;
+        const int i = j / qpt, qd = j - i * qpt;
+        const TileInfo ti = seg_tile(sched, p.rank, i);
+        const int row0 = qd * 32;
+        const int rows_valid = max(0, min(32, ti.rows - row0));
+        if (rows_valid > 0 && ti.cols > 0) {
+          for (int src = lane; src < p.W; src += 32) {
+            uint32_t seen = 0;
+            const int64_t idx = arrive_flag_index(sched, ti.tile_in_seg, src) * qpt + qd;
+            if (!wait_stamp(p.arrive[p.rank] + idx, epoch, p.timeout_ns, abort_flag, &seen, 200)) {
+              report_status(p, STATUS_TIMEOUT_ARRIVE, static_cast<uint32_t>(ti.tile_in_seg), epoch, seen,
+                            static_cast<uint32_t>(src));
+              *abort_flag = 1;
+              ok = false;
+            }
+          }
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+          ptx::fence_acq_rel_sys();   // the other lanes' acquires order this lane's loads too
+          const int upr = (ti.cols * 2 + 15) >> 4;          // 16-byte units per row
+          const int total_units = rows_valid * upr;
+          const int64_t src_row0 = (static_cast<int64_t>(ti.m0 + row0) * p.ldp + ti.n0) * 2;
+          const int64_t dst_row0 = (static_cast<int64_t>(ti.m0 + row0 - (ar ? 0 : p.out_row_shift)) * p.ldc + ti.n0) * 2;
+          for (int u0 = 0; u0 < total_units; u0 += 32 * 8) {
+            uint4 v[8];
+            int64_t doff[8];
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+              const int u = u0 + k * 32 + lane;
+              if (u < total_units) {
+                const int r = u / upr, c = u - r * upr;
+                const uint8_t* sp = src_base + src_row0 + static_cast<int64_t>(r) * p.ldp * 2 + c * 16;
+                doff[k] = dst_row0 + static_cast<int64_t>(r) * p.ldc * 2 + c * 16;
+                v[k] = bf ? ptx::multimem_ld_reduce_add_bf16x2_v4(sp) : ptx::multimem_ld_reduce_add_f16x2_v4(sp);
+              }
+            }
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+              const int u = u0 + k * 32 + lane;
+              if (u < total_units) {
+                if (ar) ptx::multimem_st_v4(dst_base + doff[k], v[k]);
+                else ptx::st_global_v4(dst_base + doff[k], v[k]);
+              }
+            }
+          }
+        }
+        if (ar) {
+          // the reduced rows are in every rank's output: stamp them everywhere
+          __syncwarp();
+          if (lane == 0 && !p.withhold_signals) {
+            const int gid = (p.rank * sched.tiles_per_seg + ti.tile_in_seg) * qpt + qd;
+            ptx::multimem_st_release_u32(p.done_mc + gid, epoch);
+          }
+        }
       }
     }
   }

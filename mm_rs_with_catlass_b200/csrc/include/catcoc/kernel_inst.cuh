@@ -4,6 +4,7 @@
 //   EPI_PLAIN   convert and store only (local GEMM, all-gather GEMM)
 //   EPI_REDUCE  + the owner-side fold of the peers' partial tiles (reduce-scatter, all-reduce)
 //   EPI_FULL    + int32 bias, per-row / per-column scales, alpha / beta / C / fp32 bias
+//   EPI_PULL    16-bit kinds only: partial tiles stay local, reducer warps sum them through the switch
 // The variants exist because the optional stages, although skipped at run time, slow the plain
 // path down measurably (code size and register pressure in the epilogue warps).
 #pragma once
@@ -17,7 +18,7 @@ namespace inst {
 // What a translation unit exports for its (kind, flavour).
 struct Unit {
   cudaError_t (*prepare)();                                                        // smem attributes
-  cudaError_t (*launch)(int epi, const FusedParams& p, int grid, cudaStream_t s);   // epi: EPI_*
+  cudaError_t (*launch)(int epi, const FusedParams& p, int grid, int threads, cudaStream_t s);   // epi: EPI_*
   int (*max_clusters)();                                                           // pair flavour: resident 2-CTA clusters
 };
 
@@ -28,11 +29,13 @@ cudaError_t set_smem_attr() {
 }
 
 template <int KIND, bool CTA2, int EPI>
-cudaError_t launch_one(const FusedParams& p, int grid, cudaStream_t stream) {
+cudaError_t launch_one(const FusedParams& p, int grid, int threads, cudaStream_t stream) {
   cudaLaunchConfig_t cfg;
   memset(&cfg, 0, sizeof(cfg));
   cfg.gridDim = dim3(grid, 1, 1);
-  cfg.blockDim = dim3(threads_for(EPI), 1, 1);
+  // the variants with communication warps may be launched with fewer of them (threads = 0: all)
+  const int max_threads = threads_for(EPI);
+  cfg.blockDim = dim3((threads >= kThreads && threads <= max_threads && threads % 32 == 0) ? threads : max_threads, 1, 1);
   cfg.dynamicSmemBytes = Geo<CTA2>::kSmemBytes;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
@@ -86,10 +89,33 @@ const Unit& unit_mx_single();
     if (e == cudaSuccess) e = set_smem_attr<KIND, CTA2, EPI_FULL>();                                  \
     return e;                                                                                         \
   }                                                                                                   \
-  static cudaError_t NAME##_launch(int epi, const FusedParams& p, int grid, cudaStream_t s) {         \
-    if (epi == EPI_PLAIN) return launch_one<KIND, CTA2, EPI_PLAIN>(p, grid, s);                       \
-    if (epi == EPI_REDUCE) return launch_one<KIND, CTA2, EPI_REDUCE>(p, grid, s);                     \
-    return launch_one<KIND, CTA2, EPI_FULL>(p, grid, s);                                              \
+  static cudaError_t NAME##_launch(int epi, const FusedParams& p, int grid, int threads, cudaStream_t s) {         \
+    if (epi == EPI_PLAIN) return launch_one<KIND, CTA2, EPI_PLAIN>(p, grid, threads, s);                       \
+    if (epi == EPI_REDUCE) return launch_one<KIND, CTA2, EPI_REDUCE>(p, grid, threads, s);                     \
+    return launch_one<KIND, CTA2, EPI_FULL>(p, grid, threads, s);                                              \
+  }                                                                                                   \
+  static int NAME##_clusters() { return CTA2 ? query_clusters<KIND, EPI_FULL>() : 0; }                \
+  const Unit& unit_##NAME() {                                                                         \
+    static const Unit u = {NAME##_prepare, NAME##_launch, NAME##_clusters};                           \
+    return u;                                                                                         \
+  }                                                                                                   \
+  } }
+
+// Four variants: the three above and the pull flavour of reduce-scatter / all-reduce.
+#define CATCOC_DEFINE_UNIT_4(NAME, KIND, CTA2)                                                        \
+  namespace catcoc { namespace inst {                                                                 \
+  static cudaError_t NAME##_prepare() {                                                               \
+    cudaError_t e = set_smem_attr<KIND, CTA2, EPI_PLAIN>();                                           \
+    if (e == cudaSuccess) e = set_smem_attr<KIND, CTA2, EPI_REDUCE>();                                \
+    if (e == cudaSuccess) e = set_smem_attr<KIND, CTA2, EPI_FULL>();                                  \
+    if (e == cudaSuccess) e = set_smem_attr<KIND, CTA2, EPI_PULL>();                                  \
+    return e;                                                                                         \
+  }                                                                                                   \
+  static cudaError_t NAME##_launch(int epi, const FusedParams& p, int grid, int threads, cudaStream_t s) { \
+    if (epi == EPI_PLAIN) return launch_one<KIND, CTA2, EPI_PLAIN>(p, grid, threads, s);              \
+    if (epi == EPI_REDUCE) return launch_one<KIND, CTA2, EPI_REDUCE>(p, grid, threads, s);            \
+    if (epi == EPI_PULL) return launch_one<KIND, CTA2, EPI_PULL>(p, grid, threads, s);                \
+    return launch_one<KIND, CTA2, EPI_FULL>(p, grid, threads, s);                                     \
   }                                                                                                   \
   static int NAME##_clusters() { return CTA2 ? query_clusters<KIND, EPI_FULL>() : 0; }                \
   const Unit& unit_##NAME() {                                                                         \
@@ -106,9 +132,9 @@ const Unit& unit_mx_single();
     if (e == cudaSuccess) e = set_smem_attr<KIND, CTA2, EPI_FULL>();                                  \
     return e;                                                                                         \
   }                                                                                                   \
-  static cudaError_t NAME##_launch(int epi, const FusedParams& p, int grid, cudaStream_t s) {         \
-    if (epi == EPI_PLAIN) return launch_one<KIND, CTA2, EPI_PLAIN>(p, grid, s);                       \
-    return launch_one<KIND, CTA2, EPI_FULL>(p, grid, s);                                              \
+  static cudaError_t NAME##_launch(int epi, const FusedParams& p, int grid, int threads, cudaStream_t s) {         \
+    if (epi == EPI_PLAIN) return launch_one<KIND, CTA2, EPI_PLAIN>(p, grid, threads, s);                       \
+    return launch_one<KIND, CTA2, EPI_FULL>(p, grid, threads, s);                                              \
   }                                                                                                   \
   static int NAME##_clusters() { return CTA2 ? query_clusters<KIND, EPI_FULL>() : 0; }                \
   const Unit& unit_##NAME() {                                                                         \
@@ -121,8 +147,8 @@ const Unit& unit_mx_single();
 #define CATCOC_DEFINE_UNIT_1(NAME, KIND, CTA2)                                                        \
   namespace catcoc { namespace inst {                                                                 \
   static cudaError_t NAME##_prepare() { return set_smem_attr<KIND, CTA2, EPI_FULL>(); }               \
-  static cudaError_t NAME##_launch(int, const FusedParams& p, int grid, cudaStream_t s) {             \
-    return launch_one<KIND, CTA2, EPI_FULL>(p, grid, s);                                              \
+  static cudaError_t NAME##_launch(int, const FusedParams& p, int grid, int threads, cudaStream_t s) {             \
+    return launch_one<KIND, CTA2, EPI_FULL>(p, grid, threads, s);                                              \
   }                                                                                                   \
   static int NAME##_clusters() { return 0; }                                                          \
   const Unit& unit_##NAME() {                                                                         \

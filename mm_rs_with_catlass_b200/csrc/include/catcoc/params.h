@@ -12,6 +12,7 @@ constexpr int kMaxWorld = 8;
 enum FusedMode : int {
   MODE_LOCAL = 0,  // plain GEMM: tile -> out
   MODE_RS = 1,     // matmul + reduce-scatter: push partial tile to its owner, owner sums
+                   //   (pull flavour: partial tile stays local, the owner sums through the switch)
   MODE_AR = 2,     // matmul + all-reduce: as RS, then the owner broadcasts the reduced tile
   MODE_AG = 3,     // all-gather + matmul: comm warps push the A shard, producer waits per chunk
 };
@@ -34,6 +35,8 @@ enum EpiVariant {
   EPI_PLAIN = 0,    // convert and store (local GEMM, all-gather GEMM)
   EPI_REDUCE = 1,   // + owner-side fold of the peers' partial tiles, pushes and stamps (RS / AR)
   EPI_FULL = 2,     // + int32 bias, per-row / per-column scales, alpha / beta / C / fp32 bias
+  EPI_PULL = 3,     // plain stores of partial tiles into the local heap + stamps; extra warps reduce the
+                    // owned tiles through the switch (multimem.ld_reduce) and store / broadcast them
 };
 
 // Error codes written to status[0] by a kernel that gave up on a wait.
@@ -85,6 +88,15 @@ struct alignas(64) FusedParams {
   uint8_t* stage[kMaxWorld];     // per-rank staging base (peer-mapped), see sched.h
   int64_t stage_parity_bytes;    // distance between the two parity halves of every rank's staging region
   uint32_t* arrive[kMaxWorld];   // per-rank arrival stamps
+  // Pull flavour of RS / AR (pull != 0, needs the multicast alias): every rank stores its partial
+  // [M, N] into its own heap at the same symmetric offset; the owner of a tile reads the sum of all
+  // ranks' copies with multimem.ld_reduce (fp32 accumulation in the switch).
+  int pull;
+  CUtensorMap tm_part[2];        // this rank's partial buffer as [M, ldp] per parity, 32-row x 128-byte box
+  uint8_t* part_local;           // this rank's partial buffer, parity 0
+  const uint8_t* part_mc;        // multicast alias of the same buffer
+  int64_t part_parity_bytes;
+  int64_t ldp;                   // elements per row of the partial buffer
   // all-reduce broadcast targets
   uint8_t* ar_out[kMaxWorld];    // per-rank parity-0 output base; parity 1 at + ar_out_parity_bytes
   int64_t ar_out_parity_bytes;
@@ -99,6 +111,8 @@ struct alignas(64) FusedParams {
   int64_t gathered_parity_bytes;
   int64_t gathered_pitch;        // bytes per row of the gathered buffer
   uint32_t* gflags[kMaxWorld];   // per-rank chunk stamps
+  uint8_t* gathered_mc;          // multicast aliases: one multimem.st lands a piece of the shard (and its
+  uint32_t* gflags_mc;           //   stamp) on every rank; null => one store per peer
   GatherPlan gp;
   int elt_bytes_a;
 

@@ -31,6 +31,18 @@ CATCOC_HD int imin(int a, int b) { return a < b ? a : b; }
 
 enum SegDim : int { SEG_ROWS = 0, SEG_COLS = 1 };
 
+// Order in which a rank visits the segments' tiles.
+//   ORDER_ROTATED      segment after segment, starting at `first_seg` (push flavours: every rank
+//                      starts on another peer; own segment last for RS / AR, first for AG)
+//   ORDER_INTERLEAVED  tile i of segment 0, of segment 1, ..., of segment W-1, then tile i+1: all
+//                      ranks compute the same tile at about the same time and the tiles in flight
+//                      belong to all owners alike. For the pull flavours, where an owner reduces
+//                      a tile through the switch as soon as every rank has stored its partial.
+//   ORDER_LOCAL_FIRST  all tiles of segment `first_seg` (the local shard), then tile i of every
+//                      other segment, tile i+1, ...: for the all-gather whose shards travel by
+//                      multicast, where chunk i of every peer arrives at about the same time.
+enum TileOrder : int { ORDER_ROTATED = 0, ORDER_INTERLEAVED = 1, ORDER_LOCAL_FIRST = 2 };
+
 struct TileSched {
   int M, N;          // extent of the grid being tiled (output rows / cols)
   int BM, BN;        // tile shape
@@ -50,6 +62,7 @@ struct TileSched {
   // Rounds apply to schedules whose own segment comes last (first_seg = rank + 1).
   int rounds;
   int round_len;         // tiles along the cut dimension per round (last round may be shorter)
+  int order;             // TileOrder (rounds apply to ORDER_ROTATED only)
 };
 
 struct TileInfo {
@@ -61,8 +74,10 @@ struct TileInfo {
 };
 
 CATCOC_HD TileSched make_sched(int M, int N, int BM, int BN, int W, int seg_dim, int first_seg,
-                               int swizzle, int rounds = 1) {
+                               int swizzle, int rounds = 1, int order = ORDER_ROTATED) {
   TileSched s;
+  s.order = (order == ORDER_INTERLEAVED || order == ORDER_LOCAL_FIRST) ? order : ORDER_ROTATED;
+  if (s.order != ORDER_ROTATED) rounds = 1;
   s.M = M; s.N = N; s.BM = BM; s.BN = BN; s.W = W < 1 ? 1 : W;
   s.seg_dim = seg_dim;
   s.swizzle = swizzle < 1 ? 1 : swizzle;
@@ -106,11 +121,48 @@ CATCOC_HD void seg_tile_coord(const TileSched& s, int i, int* mi, int* ni) {
 // swizzles still agree on which slot a tile lives in.
 CATCOC_HD int seg_tile_id(const TileSched& s, int mi, int ni) { return mi * s.seg_nt + ni; }
 
+// Fills id, origin and clipped extent of a tile from (seg, mi, ni).
+CATCOC_HD void fill_tile_extent(const TileSched& s, TileInfo* t) {
+  TileInfo& ti = *t;
+  ti.tile_in_seg = seg_tile_id(s, ti.mi, ti.ni);
+  if (s.seg_dim == SEG_ROWS) {
+    const int seg_begin = ti.seg * s.seg_len;
+    const int seg_end = imin(seg_begin + s.seg_len, s.M);
+    ti.m0 = seg_begin + ti.mi * s.BM;
+    ti.n0 = ti.ni * s.BN;
+    ti.rows = imin(s.BM, seg_end - ti.m0);
+    ti.cols = imin(s.BN, s.N - ti.n0);
+  } else {
+    const int seg_begin = ti.seg * s.seg_len;
+    const int seg_end = imin(seg_begin + s.seg_len, s.N);
+    ti.m0 = ti.mi * s.BM;
+    ti.n0 = seg_begin + ti.ni * s.BN;
+    ti.rows = imin(s.BM, s.M - ti.m0);
+    ti.cols = imin(s.BN, seg_end - ti.n0);
+  }
+  if (ti.rows < 0) ti.rows = 0;
+  if (ti.cols < 0) ti.cols = 0;
+}
+
 CATCOC_HD TileInfo get_tile(const TileSched& s, int t) {
   TileInfo ti;
   // t -> (round, phase, index inside the round's slice of the segment)
   int round = 0, phase, i;
-  if (s.rounds <= 1) {
+  if (s.order == ORDER_INTERLEAVED) {
+    i = t / s.W;
+    ti.seg = t - i * s.W;
+    seg_tile_coord(s, i, &ti.mi, &ti.ni);
+  } else if (s.order == ORDER_LOCAL_FIRST) {
+    if (t < s.tiles_per_seg || s.W == 1) {
+      i = t;
+      ti.seg = s.first_seg;
+    } else {
+      const int r = t - s.tiles_per_seg;
+      i = r / (s.W - 1);
+      ti.seg = (s.first_seg + 1 + (r - i * (s.W - 1))) % s.W;
+    }
+    seg_tile_coord(s, i, &ti.mi, &ti.ni);
+  } else if (s.rounds <= 1) {
     phase = t / s.tiles_per_seg;
     i = t - phase * s.tiles_per_seg;
     ti.seg = (s.first_seg + phase) % s.W;
@@ -162,24 +214,16 @@ CATCOC_HD TileInfo get_tile(const TileSched& s, int t) {
       ti.ni += round * s.round_len;
     }
   }
-  ti.tile_in_seg = seg_tile_id(s, ti.mi, ti.ni);
-  if (s.seg_dim == SEG_ROWS) {
-    const int seg_begin = ti.seg * s.seg_len;
-    const int seg_end = imin(seg_begin + s.seg_len, s.M);
-    ti.m0 = seg_begin + ti.mi * s.BM;
-    ti.n0 = ti.ni * s.BN;
-    ti.rows = imin(s.BM, seg_end - ti.m0);
-    ti.cols = imin(s.BN, s.N - ti.n0);
-  } else {
-    const int seg_begin = ti.seg * s.seg_len;
-    const int seg_end = imin(seg_begin + s.seg_len, s.N);
-    ti.m0 = ti.mi * s.BM;
-    ti.n0 = seg_begin + ti.ni * s.BN;
-    ti.rows = imin(s.BM, s.M - ti.m0);
-    ti.cols = imin(s.BN, seg_end - ti.n0);
-  }
-  if (ti.rows < 0) ti.rows = 0;
-  if (ti.cols < 0) ti.cols = 0;
+  fill_tile_extent(s, &ti);
+  return ti;
+}
+
+// The i-th tile (in the segment's swizzled order) of segment `seg`, whoever visits it when.
+CATCOC_HD TileInfo seg_tile(const TileSched& s, int seg, int i) {
+  TileInfo ti;
+  ti.seg = seg;
+  seg_tile_coord(s, i, &ti.mi, &ti.ni);
+  fill_tile_extent(s, &ti);
   return ti;
 }
 

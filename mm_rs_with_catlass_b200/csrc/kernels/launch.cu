@@ -182,6 +182,17 @@ static int pick_seg_dim(const CatcocOpArgs& a) {
   return (a.M >= a.W * kBM) ? SEG_ROWS : SEG_COLS;
 }
 
+// Pull flavour of reduce-scatter / all-reduce: asked for by the tiling and possible for this call?
+static bool wants_pull(const CatcocOpArgs& a) {
+  return a.mode != CATCOC_MODE_LOCAL && a.W > 1 && (a.mode == CATCOC_MODE_RS || a.mode == CATCOC_MODE_AR) &&
+         a.tiling.pull == 1;
+}
+// All-gather whose shard travels by multicast stores?
+static bool wants_ag_multicast(const CatcocOpArgs& a) {
+  return a.mode == CATCOC_MODE_AG && a.W > 1 && a.tiling.use_multicast && a.gathered_mc != nullptr &&
+         a.gflags_mc != nullptr;
+}
+
 static TileSched build_sched(const CatcocOpArgs& a, int bm, int bn, int seg_dim) {
   const bool fused = a.mode != CATCOC_MODE_LOCAL && a.W > 1;
   const int W = fused ? a.W : 1;
@@ -190,7 +201,10 @@ static TileSched build_sched(const CatcocOpArgs& a, int bm, int bn, int seg_dim)
   const int swz = a.tiling.swizzle > 0 ? a.tiling.swizzle : 8;
   int rounds = 1;
   if (fused && (a.mode == CATCOC_MODE_RS || a.mode == CATCOC_MODE_AR)) rounds = a.tiling.rounds > 0 ? a.tiling.rounds : 1;
-  return make_sched(a.M, a.N, bm, bn, W, seg_dim, first, swz, rounds);
+  int order = ORDER_ROTATED;
+  if (wants_pull(a)) order = ORDER_INTERLEAVED;
+  else if (wants_ag_multicast(a)) order = ORDER_LOCAL_FIRST;
+  return make_sched(a.M, a.N, bm, bn, W, seg_dim, first, swz, rounds, order);
 }
 
 }  // namespace host
@@ -230,6 +244,16 @@ extern "C" int catcoc_sched_total_tiles(int M, int N, int bm, int bn, int W, int
 extern "C" int catcoc_sched_get_tile_rounds(int M, int N, int bm, int bn, int W, int seg_dim, int first_seg,
                                             int swizzle, int rounds, int t, CatcocTile* out) {
   TileSched s = make_sched(M, N, bm, bn, W, seg_dim, first_seg, swizzle, rounds);
+  if (t < 0 || t >= s.total_tiles || out == nullptr) return CATCOC_E_BAD_ARG;
+  TileInfo ti = get_tile(s, t);
+  out->seg = ti.seg; out->tile_in_seg = ti.tile_in_seg; out->mi = ti.mi; out->ni = ti.ni;
+  out->m0 = ti.m0; out->n0 = ti.n0; out->rows = ti.rows; out->cols = ti.cols;
+  return CATCOC_OK;
+}
+// Replay with a visiting order (catcoc::TileOrder: 0 rotated, 1 interleaved, 2 local first).
+extern "C" int catcoc_sched_get_tile_order(int M, int N, int bm, int bn, int W, int seg_dim, int first_seg,
+                                           int swizzle, int order, int t, CatcocTile* out) {
+  TileSched s = make_sched(M, N, bm, bn, W, seg_dim, first_seg, swizzle, 1, order);
   if (t < 0 || t >= s.total_tiles || out == nullptr) return CATCOC_E_BAD_ARG;
   TileInfo ti = get_tile(s, t);
   out->seg = ti.seg; out->tile_in_seg = ti.tile_in_seg; out->mi = ti.mi; out->ni = ti.ni;
@@ -414,6 +438,10 @@ int catcoc_build_params(const CatcocOpArgs* args, FusedParams* p, int* kind_out,
     if ((p->a_local_pitch & 15) != 0) { set_error("allgather: A pitch must be a multiple of 16 bytes"); return CATCOC_E_ALIGNMENT; }
     p->gathered_parity_bytes = a.gathered_parity_bytes;
     p->gathered_pitch = gpitch;
+    if (wants_ag_multicast(a)) {
+      p->gathered_mc = static_cast<uint8_t*>(a.gathered_mc);
+      p->gflags_mc = a.gflags_mc;
+    }
     p->gp = make_gather_plan(a.ag_m, ag_ld, bm, 512 / rf.elt);
     for (int r = 0; r < a.W; ++r) {
       p->gathered[r] = static_cast<uint8_t*>(a.gathered[r]);
@@ -474,7 +502,62 @@ int catcoc_build_params(const CatcocOpArgs* args, FusedParams* p, int* kind_out,
                                                                    : CU_TENSOR_MAP_DATA_TYPE_INT32;
     if (encode_2d(&p->tm_out, a.out, oelt, odt, rows_out, a.N, a.ldc, 128 / oelt, 32) == CATCOC_OK) p->out_tma = 1;
   }
-  if (fused && (a.mode == CATCOC_MODE_RS || a.mode == CATCOC_MODE_AR)) {
+  const bool pull = wants_pull(a);
+  if (pull) {
+    // Partial tiles stay in this rank's heap; the owner sums all ranks' copies through the switch.
+    const int pelt = fmt_bytes(a.partial_fmt);
+    if (rf.kind != KIND_F16 || pelt != 2 || a.out_fmt != a.partial_fmt) {
+      set_error("the pull flavour takes fp16 / bf16 operands with partial tiles and output of the same type");
+      return CATCOC_E_UNSUPPORTED;
+    }
+    if (a.scale_m != nullptr || a.scale_n != nullptr || a.bias != nullptr || a.affine) {
+      set_error("the pull flavour has no scaled / affine epilogue");
+      return CATCOC_E_UNSUPPORTED;
+    }
+    if (a.part == nullptr || a.part_mc == nullptr || (a.part_parity_bytes & 1023) != 0 ||
+        a.part_parity_bytes < static_cast<int64_t>(a.M) * a.N * pelt) {
+      set_error("the pull flavour needs the partial buffer, its multicast alias and a parity stride that holds [M, N]");
+      return CATCOC_E_BAD_ARG;
+    }
+    // every 16-byte unit a reducer reads must lie inside one tile row: N and the column segment
+    // origins are multiples of 8 elements
+    if ((a.N % 8) != 0 || (seg_dim == SEG_COLS && (p->sched.seg_len % 8) != 0) ||
+        (reinterpret_cast<uintptr_t>(a.part) & 15) != 0 || (reinterpret_cast<uintptr_t>(a.part_mc) & 15) != 0) {
+      set_error("the pull flavour needs N (and the columns per rank of a column split) to be multiples of 8");
+      return CATCOC_E_ALIGNMENT;
+    }
+    if (a.mode == CATCOC_MODE_AR && (a.ar_out_mc == nullptr || a.done_mc == nullptr)) {
+      set_error("the pull flavour of the all-reduce broadcasts through the multicast alias of the output");
+      return CATCOC_E_BAD_ARG;
+    }
+    if (a.mode == CATCOC_MODE_RS && !p->out_vec_ok) {
+      set_error("the pull flavour of the reduce-scatter needs a 16-byte aligned output base and pitch");
+      return CATCOC_E_ALIGNMENT;
+    }
+    p->pull = 1;
+    p->part_local = static_cast<uint8_t*>(a.part);
+    p->part_mc = static_cast<const uint8_t*>(a.part_mc);
+    p->part_parity_bytes = a.part_parity_bytes;
+    p->ldp = a.N;
+    const CUtensorMapDataType pdt = a.partial_fmt == CATCOC_FMT_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
+                                                                     : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+    for (int par = 0; par < 2; ++par) {
+      rc = encode_2d(&p->tm_part[par], p->part_local + par * a.part_parity_bytes, pelt, pdt, a.M, a.N, a.N, 128 / pelt, 32);
+      if (rc != 0) return rc;
+    }
+    // in the epilogue "out" now means the partial buffer: vector / TMA stores are always possible
+    p->out_vec_ok = 1;
+    p->out_tma = out_tma_enabled() ? 1 : 0;
+    for (int r = 0; r < a.W; ++r) {
+      p->arrive[r] = a.arrive[r];
+      if (p->arrive[r] == nullptr) { set_error("missing stamp arrays for rank %d", r); return CATCOC_E_BAD_ARG; }
+    }
+    if (a.mode == CATCOC_MODE_AR) {
+      p->ar_out_mc = static_cast<uint8_t*>(a.ar_out_mc);
+      p->done_mc = a.done_mc;
+    }
+  }
+  if (!pull && fused && (a.mode == CATCOC_MODE_RS || a.mode == CATCOC_MODE_AR)) {
     for (int r = 0; r < a.W; ++r) {
       p->stage[r] = static_cast<uint8_t*>(a.stage[r]);
       p->arrive[r] = a.arrive[r];
@@ -490,7 +573,7 @@ int catcoc_build_params(const CatcocOpArgs* args, FusedParams* p, int* kind_out,
   }
   // Partial tiles are pushed into the owners' slabs by TMA stores when every peer's staging
   // region can be described as one [slots * bm, bn] matrix (it always can: slabs are dense).
-  if (fused && (a.mode == CATCOC_MODE_RS || a.mode == CATCOC_MODE_AR) && push_tma_enabled()) {
+  if (!pull && fused && (a.mode == CATCOC_MODE_RS || a.mode == CATCOC_MODE_AR) && push_tma_enabled()) {
     const int pelt = fmt_bytes(a.partial_fmt);
     const CUtensorMapDataType pdt = a.partial_fmt == CATCOC_FMT_F16    ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
                                     : a.partial_fmt == CATCOC_FMT_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
@@ -600,12 +683,13 @@ int max_active_pairs(int kind) {
 
 // The leanest epilogue variant that covers this launch.
 static int pick_epi(const FusedParams& p) {
+  if (p.pull) return EPI_PULL;
   if (p.scale_m != nullptr || p.scale_n != nullptr || p.bias != nullptr || p.affine != 0) return EPI_FULL;
   if (p.W > 1 && (p.mode == MODE_RS || p.mode == MODE_AR)) return EPI_REDUCE;
   return EPI_PLAIN;
 }
 
-int catcoc_launch_params(const FusedParams& p, int kind, int grid, int pair, cudaStream_t stream) {
+int catcoc_launch_params(const FusedParams& p, int kind, int grid, int pair, int threads, cudaStream_t stream) {
   cudaError_t e = prepare_kernels();
   if (e != cudaSuccess) {
     set_error("cudaFuncSetAttribute failed: %s", cudaGetErrorString(e));
@@ -613,7 +697,7 @@ int catcoc_launch_params(const FusedParams& p, int kind, int grid, int pair, cud
   }
   const inst::Unit* u = unit_for(kind, pair != 0);
   if (u == nullptr) { set_error("no kernel for kind %d with cta_pair=%d", kind, pair ? 2 : 1); return CATCOC_E_UNSUPPORTED; }
-  e = u->launch(pick_epi(p), p, grid, stream);
+  e = u->launch(pick_epi(p), p, grid, threads, stream);
   if (e != cudaSuccess) {
     set_error("kernel launch failed: %s", cudaGetErrorString(e));
     return -1000 - static_cast<int>(e);
@@ -676,5 +760,8 @@ extern "C" int catcoc_fused_launch(const CatcocOpArgs* args, void* stream) {
     memcpy(&slot.key, args, sizeof(CatcocOpArgs));
     slot.params = p; slot.kind = kind; slot.grid = grid; slot.pair = pair;
   }
-  return catcoc_launch_params(p, kind, grid, pair, static_cast<cudaStream_t>(stream));
+  // communication / reducer warps per CTA (variants that have them): 7 GEMM warps + 1..5
+  const int cw = args->tiling.comm_warps;
+  const int threads = (cw >= 1 && cw <= 5) ? (7 + cw) * 32 : 0;
+  return catcoc_launch_params(p, kind, grid, pair, threads, static_cast<cudaStream_t>(stream));
 }

@@ -11,7 +11,7 @@ using namespace catcoc::host;
 
 // Implemented in launch.cu / shmem_prims.cu.
 int catcoc_build_params(const CatcocOpArgs* args, FusedParams* p, int* kind_out, int* grid_out, int* pair_out);
-int catcoc_launch_params(const FusedParams& p, int kind, int grid, int pair, cudaStream_t stream);
+int catcoc_launch_params(const FusedParams& p, int kind, int grid, int pair, int threads, cudaStream_t stream);
 
 // The scratch area. In host code this name is only a stand-in for the symbol: it is NOT a
 // device address and must never be handed to a kernel or a copy. Host code uses the address
@@ -127,7 +127,7 @@ extern "C" int catcoc_matmul_noalloc(const void* a, int64_t lda, const void* b, 
   int kind = 0, grid = 0, pair = 0;
   rc = catcoc_build_params(&args, &p, &kind, &grid, &pair);
   if (rc != 0) return rc;
-  return catcoc_launch_params(p, kind, grid, pair, stream);
+  return catcoc_launch_params(p, kind, grid, pair, 0, stream);
 }
 
 extern "C" int catcoc_matmul_noalloc_status(uint32_t* host_words) {

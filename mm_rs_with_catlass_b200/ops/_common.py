@@ -131,6 +131,8 @@ def fill_tiling(args: N.OpArgs, tiling: Optional[TilingConfig]) -> None:
     args.tiling.use_multicast = 1 if t.use_multicast else 0
     args.tiling.cta_pair = t.cta_pair
     args.tiling.rounds = t.rounds
+    args.tiling.pull = 0              # the fused ops switch it on once the buffers it needs are attached
+    args.tiling.comm_warps = t.comm_warps
 
 
 def default_timeout_ns() -> int:

@@ -18,6 +18,7 @@ the same kernel.
 """
 from __future__ import annotations
 
+import os
 from typing import Optional, Tuple
 
 import torch
@@ -164,6 +165,41 @@ def _attach_stage(ctx: ShmemContext, args, m: int, n: int, seg_dim: int, t: Tili
         args.arrive[p] = arrive.ptr(p)
 
 
+def _pull_possible(ctx: ShmemContext, t: TilingConfig, n: int, seg_dim: int, out: Optional[torch.Tensor]) -> bool:
+    """Whether this reduce-scatter / all-reduce call takes the pull flavour: the tiling asks for it
+    (or leaves the choice open), the heap has a multicast alias, and every 16-byte unit a reducer
+    reads lies inside one tile row. ``CATCOC_PULL=0`` switches the automatic choice off."""
+    if t.pull == 0 or t.fp32_partials or not ctx.mc_base:
+        why = None if t.pull != 1 else ("fp32 partials" if t.fp32_partials else "no multicast alias")
+    elif t.pull == -1 and os.environ.get("CATCOC_PULL", "1") == "0":
+        why = None
+    elif n % 8 or (seg_dim == _SEG_COLS and (-(-n // ctx.world)) % 8):
+        why = "N or the columns per rank are not multiples of 8"
+    elif out is not None and (out.data_ptr() % 16 or (out.stride(0) * out.element_size()) % 16):
+        why = "the output is not 16-byte aligned"
+    else:
+        return True
+    if why is not None:
+        ctx.note_fallback("pull -> push: " + why)
+    return False
+
+
+def _attach_pull(ctx: ShmemContext, args, m: int, n: int, seg_dim: int, t: TilingConfig, fmt: int) -> None:
+    """Buffers of the pull flavour: this rank's partial [M, N] (two parity halves) with its
+    multicast alias, and the per-geometry stamp array in which every rank tells a tile's owner
+    that its partial rows are in place."""
+    lib = N.lib()
+    part, parity_bytes = _data_region(ctx, "part", m * n * 2)
+    ready = ctx.stamps(("ready", m, n, ctx.world, seg_dim, t.effective_bn, _pair(t)),
+                       int(lib.catcoc_arrive_words(m, n, ctx.world, seg_dim, t.effective_bn, t.cta_pair)))
+    args.partial_fmt = fmt
+    args.part, args.part_mc, args.part_parity_bytes = part.ptr(), part.mc_ptr(), parity_bytes
+    for p in range(ctx.world):
+        args.arrive[p] = ready.ptr(p)
+    args.tiling.pull = 1
+    ctx.counters["pull_launch_plans"] = ctx.counters.get("pull_launch_plans", 0) + 1
+
+
 def _launched(ctx: ShmemContext, args) -> int:
     """Launch and advance the host mirror of the epoch; returns the epoch of this launch."""
     trace = getattr(ctx, "trace", None)
@@ -221,7 +257,10 @@ def matmul_reduce_scatter(a: torch.Tensor, b: torch.Tensor, *, trans_a: bool = F
     with torch.cuda.device(dev):
         args, keep = _base_args(ctx, N.MODE_RS, a, trans_a, b, trans_b, m, n, k, t, seg_rows=rows)
         args.out, args.ldc, args.out_fmt = out.data_ptr(), out.stride(0), cm.out_fmt(out.dtype)
-        _attach_stage(ctx, args, m, n, _SEG_ROWS, t, N.FMT_F32 if t.fp32_partials else cm.out_fmt(a.dtype))
+        if _pull_possible(ctx, t, n, _SEG_ROWS, out):
+            _attach_pull(ctx, args, m, n, _SEG_ROWS, t, cm.out_fmt(a.dtype))
+        else:
+            _attach_stage(ctx, args, m, n, _SEG_ROWS, t, N.FMT_F32 if t.fp32_partials else cm.out_fmt(a.dtype))
         _launched(ctx, args)
         if not (keep[0].copied or keep[1].copied):
             _plan_put(ctx, key, (args, tuple(out.shape), out.dtype))
@@ -280,7 +319,11 @@ def matmul_allreduce(a: torch.Tensor, b: torch.Tensor, *, trans_a: bool = False,
             args.done[p] = done.ptr(p)
         args.ar_out_mc = obuf.mc_ptr() or None
         args.done_mc = done.mc_ptr() or None
-        _attach_stage(ctx, args, m, n, seg_dim, t, N.FMT_F32 if t.fp32_partials else cm.out_fmt(a.dtype))
+        if _pull_possible(ctx, t, n, seg_dim, None):
+            _attach_pull(ctx, args, m, n, seg_dim, t, cm.out_fmt(a.dtype))
+            args.tiling.use_multicast = 1     # the reducers broadcast through the alias
+        else:
+            _attach_stage(ctx, args, m, n, seg_dim, t, N.FMT_F32 if t.fp32_partials else cm.out_fmt(a.dtype))
         epoch = _launched(ctx, args)
         views = [obuf.tensor(a.dtype, (m, n), byte_offset=par * parity_bytes) for par in (0, 1)]
         view = views[epoch & 1]
@@ -368,6 +411,15 @@ def allgather_matmul(a_shard: torch.Tensor, b: torch.Tensor, *, trans_b: bool = 
         for p in range(W):
             args.gathered[p] = gbuf.ptr(p)
             args.gflags[p] = gfl.ptr(p)
+        # shard broadcast by multicast stores (one multimem.st reaches every rank) when the heap has
+        # the alias and the tiling or CATCOC_AG_MULTICAST asks for it
+        want_mc = t.use_multicast if os.environ.get("CATCOC_AG_MULTICAST") is None \
+            else os.environ["CATCOC_AG_MULTICAST"] == "1"
+        if want_mc and ctx.mc_base:
+            args.gathered_mc, args.gflags_mc = gbuf.mc_ptr(), gfl.mc_ptr()
+            args.tiling.use_multicast = 1
+        else:
+            args.tiling.use_multicast = 0
         args.out, args.ldc, args.out_fmt = out.data_ptr(), out.stride(0), cm.out_fmt(out.dtype)
         args.partial_fmt = args.out_fmt
         epoch = _launched(ctx, args)

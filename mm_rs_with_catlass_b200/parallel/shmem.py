@@ -112,7 +112,12 @@ class ShmemContext:
         self.workspaces: Dict[object, object] = {}   # data regions of the fused ops, by purpose
         self.stamp_regions: "OrderedDict[object, SymmBuffer]" = OrderedDict()   # stamp arrays, by geometry
         self.plans: Dict[object, object] = {}   # launch plans of the fused ops (ops/fused.py)
-        self.counters: Dict[str, int] = {"launches": 0, "bytes_pushed": 0, "pad_copies": 0}
+        self.counters: Dict[str, int] = {"launches": 0, "pad_copies": 0}
+        self.fallbacks: Dict[str, int] = {}
+
+    def note_fallback(self, reason: str) -> None:
+        """Records that a call could not take the path its tiling asked for (counted per reason)."""
+        self.fallbacks[reason] = self.fallbacks.get(reason, 0) + 1
 
     # ---- addresses -------------------------------------------------------------------
     def base(self, peer: int) -> int:

@@ -83,7 +83,9 @@ def heuristic(op: str, m: int, n: int, k: int, world: int, dtype: torch.dtype) -
     rounds = 4 if (op == "quant_matmul_reduce_scatter" and world > 1 and rows >= 2048) else 0
     if allreduce:
         return TilingConfig(bn=bn, swizzle=swizzle, cta_pair=1, use_multicast=True, seg_dim=1 if ar_cols else -1)
-    return TilingConfig(bn=bn, swizzle=swizzle, cta_pair=pair, rounds=rounds)
+    # the all-gather broadcasts its shard by multicast stores when the heap has the alias
+    return TilingConfig(bn=bn, swizzle=swizzle, cta_pair=pair, rounds=rounds,
+                        use_multicast=(op == "allgather_matmul" and world > 1))
 
 
 def choose(op: str, m: int, n: int, k: int, world: int, dtype: torch.dtype,

@@ -12,9 +12,9 @@ reference field    meaning there                           here
 m0 / n0 / k0       GEMM block tile (fixed 128x256x256)     tile is 128 x ``bn`` (64/128/256), K stage
                                                            64 (16-bit) or 128 (8-bit) elements
 commInterval       GEMM blocks per core per comm round     no rounds: every tile is published as it
-                                                           retires; kept for table compatibility
-commNpuSplit x     vector cores doing communication and    ``num_ctas`` persistent CTAs; the epilogue
-commDataSplit      peers addressed concurrently            warps of every CTA communicate
+                                                           retires; ``rounds`` lags the owner's work
+commNpuSplit x     vector cores doing communication and    ``num_ctas`` persistent CTAs x ``comm_warps``
+commDataSplit      peers addressed concurrently            communication / reducer warps per CTA
 commBlockM /       rows per comm task / per DMA            fixed 32-row quarters x 128-byte windows
 commTileM
 swizzle <7,1>      L2-friendly block order                 ``swizzle`` tiles per column group
@@ -37,6 +37,10 @@ class TilingConfig:
     rounds: int = 0        # reduce-scatter / all-reduce: owner tiles are spread over this many lagged rounds (0 = 1)
     fp32_partials: bool = False  # partial tiles cross NVLink in fp32 instead of the operand dtype (2x bytes, no rounding)
     cta_pair: int = 0      # 2: 256-row tiles on 2-CTA clusters (tcgen05 cta_group::2); 1: single CTA; 0 = 1
+    pull: int = -1         # reduce-scatter / all-reduce data path: 1 = partial tiles stay in the local heap and the
+                           # owner sums them through NVSwitch (multimem.ld_reduce); 0 = partial tiles are pushed
+                           # to the owner, who sums them in rank order (deterministic); -1 = pull when possible
+    comm_warps: int = 0    # communication / reducer warps per CTA, 1..5 (0 = 5): all-gather and pull flavours
     # --- reference-compatible fields (carried, reported, not steering the kernel) ---
     m0: int = 128
     n0: int = 256
@@ -62,6 +66,10 @@ class TilingConfig:
             raise ValueError("rounds must be in [0, 64]")
         if self.seg_dim not in (-1, 0, 1):
             raise ValueError("seg_dim must be -1, 0 or 1")
+        if self.pull not in (-1, 0, 1):
+            raise ValueError("pull must be -1, 0 or 1")
+        if self.comm_warps < 0 or self.comm_warps > 5:
+            raise ValueError("comm_warps must be in [0, 5]")
         return self
 
     def to_dict(self) -> Dict[str, object]:

@@ -71,7 +71,7 @@ def test_fused_ops_with_partial_tiles_pushed_by_tma_store(gpu_count):
     """The opt-in push path: bulk tensor stores into the owners' slabs, stamps one tile late."""
     if gpu_count < 2:
         pytest.skip("needs 2 GPUs")
-    _run(2, "ops", {"CATCOC_PUSH_TMA": "1"})
+    _run(2, "ops", {"CATCOC_PUSH_TMA": "1", "CATCOC_PULL": "0"})
 
 
 def test_withheld_signal_becomes_an_error_status(gpu_count):
@@ -79,3 +79,12 @@ def test_withheld_signal_becomes_an_error_status(gpu_count):
         pytest.skip("needs 2 GPUs")
     cases = _run(2, "withhold", {"NCCL_NVLS_ENABLE": "0"}, timeout=300)
     assert {c["case"] for c in cases} >= {"withheld_signal_detected", "recovers_after_reset"}
+
+
+def test_shmem_primitives_and_switch_sum_numerics(gpu_count):
+    """put / get / signal / wait_until over peer memory, multicast broadcast, and how far the
+    in-switch bf16 sum (multimem.ld_reduce) is from the exact sum of its terms."""
+    if gpu_count < 2:
+        pytest.skip("needs 2 GPUs")
+    cases = _run(2, "prims", timeout=300)
+    assert {c["case"] for c in cases} >= {"shmem_get_reads_the_peer", "shmem_put_signal_wait"}

@@ -138,3 +138,49 @@ def test_owner_tiles_lag_one_round_behind_the_remote_tiles():
     # within a round the remote segments still rotate starting at rank + 1
     first_round = [t.seg for t in ts[:pos[("remote", 0)][1] + 1]]
     assert list(dict.fromkeys(first_round)) == [(rank + 1 + p) % W for p in range(W - 1)]
+
+
+def tiles_order(M, Nn, bm, bn, W, seg_dim, first, swz, order):
+    lib = N.lib()
+    total = lib.catcoc_sched_total_tiles(M, Nn, bm, bn, W, seg_dim)
+    out = []
+    for t in range(total):
+        ti = N.Tile()
+        assert lib.catcoc_sched_get_tile_order(M, Nn, bm, bn, W, seg_dim, first, swz, order, t, C.byref(ti)) == 0
+        out.append(ti)
+    return out
+
+
+@pytest.mark.parametrize("M,Nn", [(1024, 1024), (200, 328), (1030, 260), (23, 45)])
+@pytest.mark.parametrize("W", [1, 2, 3, 4, 8])
+@pytest.mark.parametrize("seg_dim", [0, 1])
+@pytest.mark.parametrize("order", [1, 2])
+def test_other_visiting_orders_cover_the_same_tiles(M, Nn, W, seg_dim, order):
+    """Interleaved (pull flavours) and local-first (multicast all-gather) orders visit exactly the
+    tiles of the rotated order, with the same ids and extents."""
+    key = lambda t: (t.seg, t.tile_in_seg, t.mi, t.ni, t.m0, t.n0, t.rows, t.cols)
+    base = sorted(key(t) for t in tiles(M, Nn, 128, 128, W, seg_dim, 1 % W, 4))
+    got = sorted(key(t) for t in tiles_order(M, Nn, 128, 128, W, seg_dim, 1 % W, 4, order))
+    assert got == base
+
+
+@pytest.mark.parametrize("W", [2, 4, 8])
+def test_interleaved_order_cycles_through_the_owners(W):
+    ts = tiles_order(2048 * W, 1024, 128, 256, W, 0, 3 % W, 8, 1)
+    for t0 in range(0, len(ts), W):
+        grp = ts[t0:t0 + W]
+        assert [t.seg for t in grp] == list(range(W))            # every owner once, the same on all ranks
+        assert len({(t.mi, t.ni) for t in grp}) == 1             # the same tile position in every segment
+
+
+@pytest.mark.parametrize("W", [2, 4, 8])
+def test_local_first_order_finishes_the_own_shard_then_interleaves_the_peers(W):
+    rank = W - 1
+    ts = tiles_order(512 * W, 1024, 128, 256, W, 0, rank, 8, 2)
+    per_seg = len(ts) // W
+    assert all(t.seg == rank for t in ts[:per_seg])
+    rest = ts[per_seg:]
+    for t0 in range(0, len(rest), W - 1):
+        grp = rest[t0:t0 + W - 1]
+        assert [t.seg for t in grp] == [(rank + 1 + s) % W for s in range(W - 1)]
+        assert len({(t.mi, t.ni) for t in grp}) == 1
