@@ -118,6 +118,14 @@ def _declare(lib) -> None:
         "catcoc_oracle_quant_matmul": (i32, [vp, vp, vp, vp, i32, i32, i32, i32, i32]),
         "catcoc_oracle_dequant": (i32, [vp, vp, vp, vp, i32, i32]),
         "catcoc_oracle_compare": (i64, [vp, vp, i64, C.c_float, P(C.c_double)]),
+        "catcoc_oracle_gemm": (i32, [vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, C.c_float, C.c_float]),
+        "catcoc_oracle_gemv": (i32, [vp, vp, vp, vp, i32, i32, i32, C.c_float, C.c_float]),
+        "catcoc_oracle_batched_matmul": (i32, [vp, vp, vp, i32, i32, i32, i32, i32, i32]),
+        "catcoc_oracle_grouped_matmul": (i32, [vp, vp, vp, i32, vp, i32, i32, i32, i32]),
+        "catcoc_oracle_grouped_matmul_slice_k": (i32, [vp, vp, vp, i32, vp, i32, i32, i32]),
+        "catcoc_oracle_grouped_quant_matmul": (i32, [vp, vp, vp, i32, vp, vp, vp, i32, i32, i32, i32]),
+        "catcoc_oracle_grouped_quant_matmul_slice_k": (i32, [vp, vp, vp, i32, vp, vp, vp, i32, i32, i32]),
+        "catcoc_oracle_group_gemm": (i32, [i32, vp, vp, vp, vp, vp, vp, vp]),
         "catcoc_heap_create": (i32, [i32, i32, i32, i64, P(vp)]),
         "catcoc_heap_bytes": (i64, [vp]),
         "catcoc_heap_export_fd": (i32, [vp]),

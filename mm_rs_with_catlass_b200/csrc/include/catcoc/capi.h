@@ -155,6 +155,31 @@ int catcoc_oracle_dequant(const int32_t* acc, const float* scale_m, const float*
                           float* out, int M, int N);
 int64_t catcoc_oracle_compare(const float* out, const float* golden, int64_t n, float rtol,
                               double* mean_rel_bias);
+/* the rest of the catalogue: out = alpha op(A) op(B) + beta C + bias[col] (C, bias may be NULL) */
+int catcoc_oracle_gemm(const float* a, const float* b, const float* c, const float* bias, float* out, int M, int N,
+                       int K, int trans_a, int trans_b, float alpha, float beta);
+/* y = alpha op(A) x + beta y_in, A row-major [rows, cols] */
+int catcoc_oracle_gemv(const float* a, const float* x, const float* y_in, float* y, int rows, int cols, int trans,
+                       float alpha, float beta);
+int catcoc_oracle_batched_matmul(const float* a, const float* b, float* out, int batch, int M, int N, int K,
+                                 int trans_a, int trans_b);
+/* grouped along M: rows [ends[g-1], ends[g]) of A [M_total, K] times B[g] ([K, N] or, trans_b, [N, K]) */
+int catcoc_oracle_grouped_matmul(const float* a, const float* b, const int32_t* ends, int groups, float* out,
+                                 int M_total, int N, int K, int trans_b);
+/* grouped along K: out[g] = A[:, ks of g] B[ks of g, :], A stored [K_total, M], B stored [K_total, N] */
+int catcoc_oracle_grouped_matmul_slice_k(const float* a, const float* b, const int32_t* ends, int groups, float* out,
+                                         int M, int N, int K_total);
+/* int8 grouped products with dequantisation (scale_n [groups, N]; scale_m [M_total] resp. [groups, M]);
+ * CATCOC_E_TOO_LARGE when an exact sum does not fit the device's int32 accumulator */
+int catcoc_oracle_grouped_quant_matmul(const int8_t* a, const int8_t* b, const int32_t* ends, int groups,
+                                       const float* scale_m, const float* scale_n, float* out, int M_total, int N,
+                                       int K, int trans_b);
+int catcoc_oracle_grouped_quant_matmul_slice_k(const int8_t* a, const int8_t* b, const int32_t* ends, int groups,
+                                               const float* scale_m, const float* scale_n, float* out, int M, int N,
+                                               int K_total);
+/* independent problems packed back to back, mnk = 3 ints per problem */
+int catcoc_oracle_group_gemm(int count, const int32_t* mnk, const float* alphas, const float* betas, const float* a,
+                             const float* b, const float* c, float* out);
 
 /* ---- symmetric heap (csrc/shmem/host.cu) ---- */
 typedef struct CatcocHeap CatcocHeap;

@@ -27,10 +27,12 @@ from .. import _native as N
 from ..parallel import shmem
 from ..parallel.shmem import ShmemContext, SymmBuffer
 from ..tiling.config import TilingConfig
+from ..utils.log import get_logger
 from . import _common as cm
 from .gemm import matmul as _local_matmul
 
 _SEG_ROWS, _SEG_COLS = 0, 1
+_NVTX = os.environ.get("CATCOC_NVTX", "0") == "1"   # NVTX range around every fused launch
 
 
 def _ctx(ctx: Optional[ShmemContext]) -> ShmemContext:
@@ -181,6 +183,7 @@ def _pull_possible(ctx: ShmemContext, t: TilingConfig, n: int, seg_dim: int, out
         return True
     if why is not None:
         ctx.note_fallback("pull -> push: " + why)
+        _log.info("pull flavour not possible (%s): partial tiles are pushed to their owners", why)
     return False
 
 
@@ -200,14 +203,59 @@ def _attach_pull(ctx: ShmemContext, args, m: int, n: int, seg_dim: int, t: Tilin
     ctx.counters["pull_launch_plans"] = ctx.counters.get("pull_launch_plans", 0) + 1
 
 
-def _launched(ctx: ShmemContext, args) -> int:
+_FMT_BYTES = {N.FMT_F16: 2, N.FMT_BF16: 2, N.FMT_F32: 4, N.FMT_S32: 4}
+_MODE_NAMES = {N.MODE_RS: "matmul_reduce_scatter", N.MODE_AR: "matmul_allreduce", N.MODE_AG: "allgather_matmul"}
+_log = get_logger("catcoc.ops")
+
+
+def link_bytes_out(args) -> int:
+    """Bytes one launch sends over this GPU's NVLink port (what the kernel's data path moves, from
+    the argument block): partial tiles to their owners or to the switch, reduced tiles to every
+    rank, the A shard to the peers."""
+    W = args.W
+    if W <= 1:
+        return 0
+    if args.mode == N.MODE_AG:
+        shard = (args.M // W) * args.K * (1 if args.in_fmt >= N.IN_S8 else 2)
+        return shard if (args.gathered_mc and args.tiling.use_multicast) else (W - 1) * shard
+    S = args.M * args.N * _FMT_BYTES.get(args.partial_fmt, 2)
+    out = S if args.tiling.pull else (W - 1) * S // W          # pull: the switch reads this rank's whole partial
+    if args.mode == N.MODE_AR:
+        o = args.M * args.N * _FMT_BYTES.get(args.out_fmt, 2) // W
+        out += o if (args.tiling.use_multicast and args.ar_out_mc) else (W - 1) * o
+    return out
+
+
+def _describe(ctx: ShmemContext, args, t: TilingConfig) -> None:
+    """Record of what a fused call was resolved to: kept on the context (``last_call``) and logged
+    at DEBUG level (``CATCOC_LOG=DEBUG``). Runs when a launch plan is built, not on plan hits."""
+    path = "local"
+    if args.W > 1:
+        if args.mode == N.MODE_AG:
+            path = "multicast" if (args.gathered_mc and args.tiling.use_multicast) else "peer stores"
+        else:
+            path = "pull (in-switch sum)" if args.tiling.pull else "push (owner-side sum)"
+    ctx.last_call = {"op": _MODE_NAMES.get(args.mode, "matmul"), "M": args.M, "N": args.N, "K": args.K,
+                     "world": args.W, "path": path, "tiling": t, "link_bytes_out": link_bytes_out(args)}
+    if _log.isEnabledFor(10):
+        _log.debug("%(op)s M=%(M)d N=%(N)d K=%(K)d W=%(world)d -> %(path)s, %(link_bytes_out)d B out, %(tiling)s",
+                   ctx.last_call)
+
+
+def _launched(ctx: ShmemContext, args, nvtx: Optional[str] = None) -> int:
     """Launch and advance the host mirror of the epoch; returns the epoch of this launch."""
     trace = getattr(ctx, "trace", None)
     if trace is not None:   # int64[16] device tensor of per-role cycle counters (params.h)
         args.trace = trace.data_ptr()
-    cm.launch(args, ctx.device)
+    if _NVTX:
+        torch.cuda.nvtx.range_push(_MODE_NAMES.get(args.mode, "matmul"))
+        cm.launch(args, ctx.device)
+        torch.cuda.nvtx.range_pop()
+    else:
+        cm.launch(args, ctx.device)
     ctx.epoch += 1
     ctx.counters["launches"] += 1
+    ctx.counters["bytes_out"] += link_bytes_out(args)
     return ctx.epoch
 
 
@@ -261,6 +309,7 @@ def matmul_reduce_scatter(a: torch.Tensor, b: torch.Tensor, *, trans_a: bool = F
             _attach_pull(ctx, args, m, n, _SEG_ROWS, t, cm.out_fmt(a.dtype))
         else:
             _attach_stage(ctx, args, m, n, _SEG_ROWS, t, N.FMT_F32 if t.fp32_partials else cm.out_fmt(a.dtype))
+        _describe(ctx, args, t)
         _launched(ctx, args)
         if not (keep[0].copied or keep[1].copied):
             _plan_put(ctx, key, (args, tuple(out.shape), out.dtype))
@@ -324,6 +373,7 @@ def matmul_allreduce(a: torch.Tensor, b: torch.Tensor, *, trans_a: bool = False,
             args.tiling.use_multicast = 1     # the reducers broadcast through the alias
         else:
             _attach_stage(ctx, args, m, n, seg_dim, t, N.FMT_F32 if t.fp32_partials else cm.out_fmt(a.dtype))
+        _describe(ctx, args, t)
         epoch = _launched(ctx, args)
         views = [obuf.tensor(a.dtype, (m, n), byte_offset=par * parity_bytes) for par in (0, 1)]
         view = views[epoch & 1]
@@ -422,6 +472,7 @@ def allgather_matmul(a_shard: torch.Tensor, b: torch.Tensor, *, trans_b: bool = 
             args.tiling.use_multicast = 0
         args.out, args.ldc, args.out_fmt = out.data_ptr(), out.stride(0), cm.out_fmt(out.dtype)
         args.partial_fmt = args.out_fmt
+        _describe(ctx, args, t)
         epoch = _launched(ctx, args)
         gviews = [gbuf.tensor(a_shard.dtype, (W * m, ag_ld), byte_offset=par * parity_bytes) for par in (0, 1)]
         if ag_ld != k:
@@ -489,6 +540,7 @@ def quant_matmul_reduce_scatter(x1: torch.Tensor, x2: torch.Tensor, scale_x1: to
         args.scale_n = scale_x2.data_ptr()
         args.bias = bias.data_ptr() if bias is not None else None
         _attach_stage(ctx, args, m, n, _SEG_ROWS, t, N.FMT_S32)
+        _describe(ctx, args, t)
         _launched(ctx, args)
         if not (keep[0].copied or keep[1].copied):
             _plan_put(ctx, key, (args, tuple(out.shape), out.dtype))

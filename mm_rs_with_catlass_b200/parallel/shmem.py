@@ -112,7 +112,9 @@ class ShmemContext:
         self.workspaces: Dict[object, object] = {}   # data regions of the fused ops, by purpose
         self.stamp_regions: "OrderedDict[object, SymmBuffer]" = OrderedDict()   # stamp arrays, by geometry
         self.plans: Dict[object, object] = {}   # launch plans of the fused ops (ops/fused.py)
-        self.counters: Dict[str, int] = {"launches": 0, "pad_copies": 0}
+        # launches of fused kernels, bytes they sent over this GPU's NVLink port, padded operand copies
+        self.counters: Dict[str, int] = {"launches": 0, "bytes_out": 0, "pad_copies": 0}
+        self.last_call: Optional[dict] = None   # what the most recent new launch plan was resolved to
         self.fallbacks: Dict[str, int] = {}
 
     def note_fallback(self, reason: str) -> None:
