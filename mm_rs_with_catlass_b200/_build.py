@@ -19,6 +19,14 @@ CSRC = PKG_DIR / "csrc"
 LIB_DIR = PKG_DIR / "_lib"
 LIB_PATH = LIB_DIR / "libcatcoc_b200.so"
 STAMP_PATH = LIB_DIR / "build.stamp"
+# the same sources with -DCATCOC_CHECKED: every workspace / peer / output / TMEM offset of the kernels is
+# compared with the extent of its buffer, a violation is recorded in the status block and the access skipped
+CHECKED_LIB_PATH = LIB_DIR / "libcatcoc_b200_checked.so"
+CHECKED_STAMP_PATH = LIB_DIR / "build_checked.stamp"
+
+
+def lib_path(checked: bool = False) -> Path:
+    return CHECKED_LIB_PATH if checked else LIB_PATH
 
 SOURCES = [
     "kernels/launch.cu",
@@ -71,12 +79,14 @@ def source_digest() -> str:
     return h.hexdigest()
 
 
-def is_current() -> bool:
-    return LIB_PATH.exists() and STAMP_PATH.exists() and STAMP_PATH.read_text().strip() == source_digest()
+def is_current(checked: bool = False) -> bool:
+    lib, stamp = (CHECKED_LIB_PATH, CHECKED_STAMP_PATH) if checked else (LIB_PATH, STAMP_PATH)
+    return lib.exists() and stamp.exists() and stamp.read_text().strip() == source_digest()
 
 
-def _compile_one(src: Path, obj: Path, verbose: bool) -> str:
-    cmd = [_nvcc(), *NVCC_FLAGS, *_extra_flags(), "-I", str(CSRC / "include"), "-c", str(src), "-o", str(obj)]
+def _compile_one(src: Path, obj: Path, verbose: bool, checked: bool = False) -> str:
+    cmd = [_nvcc(), *NVCC_FLAGS, *_extra_flags(), *(["-DCATCOC_CHECKED=1"] if checked else []),
+           "-I", str(CSRC / "include"), "-c", str(src), "-o", str(obj)]
     if verbose:
         cmd += ["-Xptxas", "-v"]
     proc = subprocess.run(cmd, capture_output=True, text=True)
@@ -85,13 +95,15 @@ def _compile_one(src: Path, obj: Path, verbose: bool) -> str:
     return proc.stderr
 
 
-def build(force: bool = False, verbose: bool = False) -> Path:
+def build(force: bool = False, verbose: bool = False, checked: bool = False) -> Path:
     """Compile every CUDA source of the package for sm_100a and link one shared library. The
-    translation units (one per kernel flavour) compile in parallel."""
-    if not force and is_current():
+    translation units (one per kernel flavour) compile in parallel. ``checked`` builds the
+    bounds-checked variant next to the normal one."""
+    LIB_PATH, STAMP_PATH = (CHECKED_LIB_PATH, CHECKED_STAMP_PATH) if checked else (globals()["LIB_PATH"], globals()["STAMP_PATH"])
+    if not force and is_current(checked):
         return LIB_PATH
     LIB_DIR.mkdir(exist_ok=True)
-    obj_dir = LIB_DIR / ("obj%d" % os.getpid())
+    obj_dir = LIB_DIR / ("obj%d%s" % (os.getpid(), "c" if checked else ""))
     obj_dir.mkdir(exist_ok=True)
     sources = _existing_sources()
     objs = [obj_dir / (s.relative_to(CSRC).as_posix().replace("/", "_") + ".o") for s in sources]
@@ -99,7 +111,7 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     try:
         workers = max(1, min(len(sources), os.cpu_count() or 1, int(os.environ.get("CATCOC_BUILD_JOBS", "8"))))
         with ThreadPoolExecutor(max_workers=workers) as pool:
-            logs = list(pool.map(lambda so: _compile_one(so[0], so[1], verbose), zip(sources, objs)))
+            logs = list(pool.map(lambda so: _compile_one(so[0], so[1], verbose, checked), zip(sources, objs)))
         if verbose:
             sys.stderr.write("".join(logs))
         link = [_nvcc(), "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-Xcompiler", "-fPIC",
@@ -116,4 +128,4 @@ def build(force: bool = False, verbose: bool = False) -> Path:
 
 
 if __name__ == "__main__":
-    print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))
+    print(build(force="--force" in sys.argv, verbose="-v" in sys.argv, checked="--checked" in sys.argv))

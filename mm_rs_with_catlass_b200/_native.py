@@ -29,13 +29,15 @@ STATUS_NAMES = {
     4: "a peer's A chunk never arrived",
     5: "barrier / wait_until timed out",
     6: "bad argument",
+    7: "an offset left its buffer (bounds-checked build: what = site, expected = limit, seen = offset)",
 }
+LIM_STAGE, LIM_ARRIVE, LIM_DONE, LIM_AR_OUT, LIM_GATHERED, LIM_GFLAGS, LIM_PART, LIM_OUT = range(8)
 
 
 class Tiling(C.Structure):
     _fields_ = [("bn", C.c_int), ("swizzle", C.c_int), ("num_ctas", C.c_int), ("seg_dim", C.c_int),
                 ("use_multicast", C.c_int), ("rounds", C.c_int), ("cta_pair", C.c_int), ("pull", C.c_int),
-                ("comm_warps", C.c_int)]
+                ("comm_warps", C.c_int), ("push_tma", C.c_int)]
 
 
 class OpArgs(C.Structure):
@@ -71,6 +73,7 @@ class OpArgs(C.Structure):
         ("a_rows_total", C.c_int), ("a_k_total", C.c_int), ("b_n_total", C.c_int), ("b_k_total", C.c_int),
         ("g_a_row_back", C.c_int), ("g_a_k", C.c_int), ("g_b_row", C.c_int), ("g_b_k", C.c_int),
         ("g_nvec", C.c_int),
+        ("limit", C.c_int64 * 8),
         ("epoch_ptr", C.c_void_p), ("cta_counter", C.c_void_p), ("status", C.c_void_p),
         ("timeout_ns", C.c_uint64),
         ("withhold_signals", C.c_int),
@@ -103,6 +106,7 @@ def _declare(lib) -> None:
     sigs = {
         "catcoc_last_error": (C.c_char_p, []),
         "catcoc_version": (i32, []),
+        "catcoc_is_checked_build": (i32, []),
         "catcoc_num_sms": (i32, [i32]),
         "catcoc_fused_launch": (i32, [P(OpArgs), vp]),
         "catcoc_stage_bytes": (i64, [i32, i32, i32, i32, i32, i32, i32]),
@@ -167,10 +171,13 @@ def lib():
     if _lib is None:
         with _lock:
             if _lib is None:
-                if os.environ.get("CATCOC_NO_BUILD") and _build.LIB_PATH.exists():
-                    path = _build.LIB_PATH
+                # CATCOC_CHECKED=1 loads the build whose kernels bounds-check every workspace offset
+                checked = os.environ.get("CATCOC_CHECKED", "0") == "1"
+                target = _build.lib_path(checked)
+                if os.environ.get("CATCOC_NO_BUILD") and target.exists():
+                    path = target
                 else:
-                    path = _build.build()
+                    path = _build.build(checked=checked)
                 loaded = C.CDLL(str(path), mode=C.RTLD_GLOBAL)
                 _declare(loaded)
                 _lib = loaded

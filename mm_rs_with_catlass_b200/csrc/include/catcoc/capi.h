@@ -49,6 +49,8 @@ typedef struct CatcocTiling {
   int pull;        /* reduce-scatter / all-reduce: 1 = partial tiles stay in the local heap and the owner
                       sums them through the switch (multimem.ld_reduce); needs the multicast alias   */
   int comm_warps;  /* communication / reducer warps per CTA, 1..5 (0 = 5); all-gather and pull flavours */
+  int push_tma;    /* push flavour: 1 = partial tiles go to their owners' slabs by TMA stores (stamps one tile
+                      late), 0 = by 16-byte stores, -1 = CATCOC_PUSH_TMA decides (default off)            */
 } CatcocTiling;
 
 typedef struct CatcocOpArgs {
@@ -108,6 +110,11 @@ typedef struct CatcocOpArgs {
   int a_rows_total, a_k_total, b_n_total, b_k_total;
   int g_a_row_back, g_a_k, g_b_row, g_b_k, g_nvec;
 
+  /* Extents of the buffers handed in above, for the bounds-checked build of the library (0 = unknown):
+   * [0] stage bytes, [1] arrive words, [2] done words, [3] ar_out bytes, [4] gathered bytes,
+   * [5] gflags words, [6] partial buffer bytes, [7] out bytes. The launcher also checks the tensor maps
+   * it builds over these buffers against them in every build. */
+  int64_t limit[8];
   uint32_t* epoch_ptr; uint32_t* cta_counter; uint32_t* status;
   uint64_t timeout_ns;
   int withhold_signals;
@@ -116,6 +123,7 @@ typedef struct CatcocOpArgs {
 
 const char* catcoc_last_error(void);
 int catcoc_version(void);
+int catcoc_is_checked_build(void);   /* 1: device-side bounds checks compiled in (see FusedParams::limit) */
 
 /* Launches the fused kernel on `stream` (a cudaStream_t). */
 int catcoc_fused_launch(const CatcocOpArgs* args, void* stream);

@@ -47,6 +47,7 @@ constexpr int kThreads = 256;          // warps 0-6 are the GEMM roles, warp 7 a
 constexpr int kThreadsPlain = 384;
 CATCOC_HD constexpr int threads_for(int epi) { return (epi == EPI_PLAIN || epi == EPI_PULL) ? kThreadsPlain : kThreads; }
 constexpr int kTmemCols = 512;
+constexpr int kPullStrips = 4;   // pull flavour: a 32-row quarter is reduced in this many strips (one reducer task each)
 constexpr int kMaxStages = 6;
 
 // Two flavours of the same kernel:
@@ -98,6 +99,26 @@ CATCOC_DEVICE void report_status(const FusedParams& p, uint32_t code, uint32_t w
     __threadfence_system();
   }
 }
+
+// Bounds-checked build (-DCATCOC_CHECKED): every offset into a workspace, a peer's memory, the
+// output or the accumulator goes through CATCOC_BOUND(p, site, end, limit_id): `end` is one past
+// the last byte (word, column) the access touches. An offset outside its buffer is recorded once
+// in the status block (site, limit, offset) and the access is SKIPPED, so a wrong index shows up
+// as an error with a location instead of as a fault or as wrong numbers somewhere else. In the
+// normal build the macro is the constant `true` and costs nothing.
+#if defined(CATCOC_CHECKED)
+CATCOC_DEVICE bool bound_ok(const FusedParams& p, uint32_t site, int64_t end, int64_t limit) {
+  if (limit <= 0 || (end >= 0 && end <= limit)) return true;   // 0: the caller did not tell the extent
+  report_status(p, STATUS_OUT_OF_RANGE, site, static_cast<uint32_t>(limit), static_cast<uint32_t>(end),
+                static_cast<uint32_t>(static_cast<uint64_t>(end) >> 32));
+  return false;
+}
+#define CATCOC_BOUND(p, site, end, id) ::catcoc::bound_ok((p), (site), static_cast<int64_t>(end), (p).limit[(id)])
+#define CATCOC_BOUND_ABS(p, site, end, lim) ::catcoc::bound_ok((p), (site), static_cast<int64_t>(end), static_cast<int64_t>(lim))
+#else
+#define CATCOC_BOUND(p, site, end, id) (true)
+#define CATCOC_BOUND_ABS(p, site, end, lim) (true)
+#endif
 
 // Cycle accounting for the optional trace counters.
 struct Tick {
@@ -362,6 +383,7 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
             for (int s = lane; ok && s < p.gp.n_slices; s += 32) {
               uint32_t seen = 0;
               const int64_t idx = gather_flag_index(p.gp, ti.seg, ti.mi, s);
+              if (!CATCOC_BOUND(p, SITE_GFLAG_POLL, idx + 1, LIM_GFLAGS)) continue;
               if (!wait_stamp(fl + idx, epoch, p.timeout_ns, abort_flag, &seen)) {
                 report_status(p, STATUS_TIMEOUT_GATHER, static_cast<uint32_t>(idx), epoch, seen,
                               static_cast<uint32_t>(ti.seg));
@@ -387,7 +409,9 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
             const uint32_t* fl = p.gflags[p.rank];
             bool okl = true;
             for (int s = lane; s < p.gp.n_slices; s += 32) {
-              const uint32_t v = ptx::ld_relaxed_sys_u32(fl + gather_flag_index(p.gp, tin.seg, tin.mi, s));
+              const int64_t fi = gather_flag_index(p.gp, tin.seg, tin.mi, s);
+              if (!CATCOC_BOUND(p, SITE_GFLAG_POLL, fi + 1, LIM_GFLAGS)) { okl = false; continue; }
+              const uint32_t v = ptx::ld_relaxed_sys_u32(fl + fi);
               okl = okl && (static_cast<int32_t>(v - epoch) >= 0);
             }
             pre_ok = okl;
@@ -658,7 +682,9 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
         if (lane < p.W && lane != p.rank) {
           uint32_t seen = 0;
           const int64_t idx = arrive_flag_index(sched, ti.tile_in_seg, lane) * qpt + qid;
-          if (!wait_stamp(p.arrive[p.rank] + idx, epoch, p.timeout_ns, abort_flag, &seen)) {
+          if (!CATCOC_BOUND(p, SITE_ARRIVE_POLL, idx + 1, LIM_ARRIVE)) {
+            ok = false;
+          } else if (!wait_stamp(p.arrive[p.rank] + idx, epoch, p.timeout_ns, abort_flag, &seen)) {
             report_status(p, STATUS_TIMEOUT_ARRIVE, static_cast<uint32_t>(ti.tile_in_seg), epoch,
                           seen, static_cast<uint32_t>(lane));
             *abort_flag = 1;
@@ -719,6 +745,24 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
         vec_ok = (p.out_vec_ok != 0) && ((ti.n0 * st_elt) % 16 == 0);
       }
 
+      // checked build: the last byte this warp stores for this tile must lie inside its buffer
+      bool dst_ok = true;
+#if defined(CATCOC_CHECKED)
+      if (rows_valid > 0 && ti.cols > 0) {
+        const int64_t span = static_cast<int64_t>(rows_valid - 1) * pitch + static_cast<int64_t>(ti.cols) * st_elt;
+        if (kPull && pull) {
+          dst_ok = CATCOC_BOUND(p, SITE_PART_STORE, (base - p.part_local) + span, LIM_PART);
+        } else if (!own) {   // slabs are stored whole
+          dst_ok = CATCOC_BOUND(p, SITE_PUSH_SLAB, (base - p.stage[ti.seg]) + 31 * pitch + static_cast<int64_t>(BN) * st_elt,
+                                LIM_STAGE);
+        } else if (kReduce && fused && p.mode == MODE_AR) {
+          dst_ok = CATCOC_BOUND(p, SITE_AR_OUT, off + span, LIM_AR_OUT);
+        } else {
+          dst_ok = CATCOC_BOUND(p, SITE_OUT_STORE, (base - static_cast<uint8_t*>(p.out)) + span, LIM_OUT);
+        }
+      }
+#endif
+
       const int groups = BN / 32;                        // 32-column groups in the accumulator
       const int groups_per_win = (st_elt == 2) ? 2 : 1;  // groups per 128 B window of output
       const int nwin = groups / groups_per_win;
@@ -769,8 +813,13 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
           if (col0 >= ti.cols) break;
           uint32_t v[32];
           tick.lap(c_pub);
-          ptx::tmem_ld_32x32b_x32(taddr + static_cast<uint32_t>(col0), v);
-          ptx::tcgen05_wait_ld();
+          if (CATCOC_BOUND_ABS(p, SITE_TMEM, acc * acc_stride + col0 + 32, KIND == KIND_MX ? 256 : kTmemCols)) {
+            ptx::tmem_ld_32x32b_x32(taddr + static_cast<uint32_t>(col0), v);
+            ptx::tcgen05_wait_ld();
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = 0u;
+          }
           tick.lap(c_tld);
           if (g == last_group) {
             // every TMEM read of this tile is done: hand the accumulator back to the MMA warp
@@ -792,7 +841,12 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
             }
           }
 
-          if (kReduce && reduce_here && row_in_tile < ti.rows) {
+          if (kReduce && reduce_here && row_in_tile < ti.rows &&
+              CATCOC_BOUND(p, SITE_FOLD_SLAB,
+                           static_cast<int64_t>(parity) * p.stage_parity_bytes +
+                               (static_cast<int64_t>(p.W - 1) * sched.tiles_per_seg + ti.tile_in_seg) * stage_tile_bytes(sched, pelt) +
+                               (static_cast<int64_t>(row_in_tile) * BN + col0 + 32) * pelt,
+                           LIM_STAGE)) {
             // fold the peers' partials in a fixed source order => deterministic sum. The loads of
             // two sources are issued back to back before their adds to keep more bytes in flight.
             const uint8_t* sbase = p.stage[p.rank] + (static_cast<int64_t>(row_in_tile) * BN + col0) * pelt;
@@ -955,7 +1009,9 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
           const int per_win = 128 / st_elt;
           const int cols_valid = min(per_win, ti.cols - win * per_win);
           const int64_t wb = static_cast<int64_t>(win) * 128;
-          if (tma_push) {
+          if (!dst_ok) {
+            // checked build: the destination lies outside its buffer; reported, nothing is stored
+          } else if (tma_push) {
             ptx::fence_proxy_async_smem();
             __syncwarp();
             if (lane == 0) {
@@ -1006,8 +1062,8 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
             ptx::bulk_wait_group_all();
             ptx::fence_proxy_async();
           }
-          ptx::st_release_sys_u32(p.arrive[ti.seg] + arrive_flag_index(sched, ti.tile_in_seg, p.rank) * qpt + qid,
-                                  epoch);
+          const int64_t si = arrive_flag_index(sched, ti.tile_in_seg, p.rank) * qpt + qid;
+          if (CATCOC_BOUND(p, SITE_ARRIVE_POST, si + 1, LIM_ARRIVE)) ptx::st_release_sys_u32(p.arrive[ti.seg] + si, epoch);
         }
       } else if (kReduce && fused && (p.mode == MODE_RS || p.mode == MODE_AR) && (!own || p.mode == MODE_AR)) {
         // Data stores of all 32 lanes happen-before lane 0's release through the warp barrier;
@@ -1016,8 +1072,11 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
         tick.lap(c_work);
         if (!p.withhold_signals) {
           if (!own) {
-            uint32_t* stamp = p.arrive[ti.seg] + arrive_flag_index(sched, ti.tile_in_seg, p.rank) * qpt + qid;
-            if (tma_push) {
+            const int64_t si = arrive_flag_index(sched, ti.tile_in_seg, p.rank) * qpt + qid;
+            uint32_t* stamp = p.arrive[ti.seg] + si;
+            if (!CATCOC_BOUND(p, SITE_ARRIVE_POST, si + 1, LIM_ARRIVE)) {
+              // checked build: reported, no stamp
+            } else if (tma_push) {
               // the stores of the tile before this one are complete once at most this tile's
               // groups are in flight: announce that tile now, this one a tile later
               if (lane == 0 && pending_stamp != nullptr) {
@@ -1037,7 +1096,9 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
           } else {
             // the reduced rows are in every rank's output: stamp them everywhere
             const int gid = (ti.seg * sched.tiles_per_seg + ti.tile_in_seg) * qpt + qid;
-            if (p.done_mc != nullptr && mc != nullptr) {
+            if (!CATCOC_BOUND(p, SITE_DONE_POST, gid + 1, LIM_DONE)) {
+              // checked build: reported, no stamp
+            } else if (p.done_mc != nullptr && mc != nullptr) {
               if (lane == 0) ptx::multimem_st_release_u32(p.done_mc + gid, epoch);
             } else if (lane < p.W) {
               ptx::st_release_sys_u32(p.done[lane] + gid, epoch);
@@ -1071,9 +1132,10 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
     // all-reduce tail: this rank's output is complete only when every owner's tiles landed
     if ((kReduce || kPull) && fused && p.mode == MODE_AR && ok && !*abort_flag) {
       const int et = (warp - 2) * 32 + lane;
-      const int nstamps = sched.total_tiles * qpt;
+      const int nstamps = sched.total_tiles * qpt * ((kPull && pull) ? kPullStrips : 1);
       for (int j = blockIdx.x + et * gridDim.x; j < nstamps; j += gridDim.x * kEpiWarps * 32) {
         uint32_t seen = 0;
+        if (!CATCOC_BOUND(p, SITE_DONE_POLL, j + 1, LIM_DONE)) break;
         if (!wait_stamp(p.done[p.rank] + j, epoch, p.timeout_ns, abort_flag, &seen)) {
           report_status(p, STATUS_TIMEOUT_DONE, static_cast<uint32_t>(j), epoch, seen,
                         static_cast<uint32_t>((j / qpt) / sched.tiles_per_seg));
@@ -1181,7 +1243,9 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
         uint8_t* dstp = (mcast ? p.gathered_mc : p.gathered[peer]) +
                         static_cast<int64_t>(parity) * p.gathered_parity_bytes +
                         (static_cast<int64_t>(p.rank) * gp.m + r0) * p.gathered_pitch + cb;
-        if (col_ok) {
+        const int64_t dst_end = static_cast<int64_t>(parity) * p.gathered_parity_bytes +
+                                (static_cast<int64_t>(p.rank) * gp.m + r0 + nrows - 1) * p.gathered_pitch + cb + 16;
+        if (col_ok && nrows > 0 && CATCOC_BOUND(p, SITE_GATHER_PUSH, dst_end, LIM_GATHERED)) {
           // 16 rows (8 KiB per warp) in flight per round trip: the copy is latency bound, which is
           // why several warps per CTA share it
           for (int r = 0; r < nrows; r += 16) {
@@ -1207,21 +1271,25 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
         __syncwarp();
         if (lane == 0 && !p.withhold_signals) {
           const int64_t fi = gather_flag_index(gp, p.rank, chunk, slice);
-          if (mcast) ptx::multimem_st_release_u32(p.gflags_mc + fi, epoch);
+          if (!CATCOC_BOUND(p, SITE_GFLAG_POST, fi + 1, LIM_GFLAGS)) {
+            // checked build: reported, no stamp
+          } else if (mcast) ptx::multimem_st_release_u32(p.gflags_mc + fi, epoch);
           else ptx::st_release_sys_u32(p.gflags[peer] + fi, epoch);
         }
       }
     } else if (kPull && pull) {
       // Reducer warps of the pull flavour. Task j = (i-th tile of MY segment in visiting order, a
-      // 32-row quarter of it), dealt out round-robin over all reducer warps of the grid so that
-      // the tiles that finish first are reduced first. A task waits until every rank's stamp for
+      // 32-row quarter of it, an 8-row strip of the quarter), dealt out round-robin over all reducer
+      // warps of the grid so that the tiles that finish first are reduced first. A strip is one
+      // batch of loads per lane: after the last tile of the launch the whole grid's reducer warps
+      // share what is left, each with a single round trip through the switch. A task waits until every rank's stamp for
       // that quarter is in, reads the sum of the W partial copies through the switch
       // (multimem.ld_reduce, fp32 accumulation) and stores it: into `out` (reduce-scatter) or, with
       // one multimem.st per 16 bytes, into every rank's output followed by a `done` stamp
       // (all-reduce). Nothing in the GEMM pipeline ever waits for these warps.
       const int gw = static_cast<int>(blockIdx.x) * ncw + cw;
       const int total_gw = static_cast<int>(gridDim.x) * ncw;
-      const int tasks = sched.tiles_per_seg * qpt;
+      const int tasks = sched.tiles_per_seg * qpt * kPullStrips;
       const bool bf = (p.partial_fmt == FMT_BF16);
       const uint8_t* src_base = p.part_mc + static_cast<int64_t>(parity) * p.part_parity_bytes;
       const bool ar = (p.mode == MODE_AR);
@@ -1230,15 +1298,19 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
       bool ok = true;
       for (int j = gw; ok && j < tasks; j += total_gw) {
         if (*abort_flag) break;
-        const int i = j / qpt, qd = j - i * qpt;
+        const int strip = j % kPullStrips;
+        const int jq = j / kPullStrips;
+        const int i = jq / qpt, qd = jq - i * qpt;
         const TileInfo ti = seg_tile(sched, p.rank, i);
-        const int row0 = qd * 32;
-        const int rows_valid = max(0, min(32, ti.rows - row0));
+        const int row0 = qd * 32 + strip * (32 / kPullStrips);
+        const int rows_valid = max(0, min(32 / kPullStrips, ti.rows - row0));
         if (rows_valid > 0 && ti.cols > 0) {
           for (int src = lane; src < p.W; src += 32) {
             uint32_t seen = 0;
             const int64_t idx = arrive_flag_index(sched, ti.tile_in_seg, src) * qpt + qd;
-            if (!wait_stamp(p.arrive[p.rank] + idx, epoch, p.timeout_ns, abort_flag, &seen, 200)) {
+            if (!CATCOC_BOUND(p, SITE_ARRIVE_POLL, idx + 1, LIM_ARRIVE)) {
+              ok = false;
+            } else if (!wait_stamp(p.arrive[p.rank] + idx, epoch, p.timeout_ns, abort_flag, &seen, 200)) {
               report_status(p, STATUS_TIMEOUT_ARRIVE, static_cast<uint32_t>(ti.tile_in_seg), epoch, seen,
                             static_cast<uint32_t>(src));
               *abort_flag = 1;
@@ -1252,7 +1324,15 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
           const int total_units = rows_valid * upr;
           const int64_t src_row0 = (static_cast<int64_t>(ti.m0 + row0) * p.ldp + ti.n0) * 2;
           const int64_t dst_row0 = (static_cast<int64_t>(ti.m0 + row0 - (ar ? 0 : p.out_row_shift)) * p.ldc + ti.n0) * 2;
-          for (int u0 = 0; u0 < total_units; u0 += 32 * 8) {
+          const int64_t row_span = static_cast<int64_t>(upr) * 16;
+          const bool io_ok =
+              CATCOC_BOUND(p, SITE_PART_REDUCE, static_cast<int64_t>(parity) * p.part_parity_bytes + src_row0 +
+                                                    static_cast<int64_t>(rows_valid - 1) * p.ldp * 2 + row_span, LIM_PART) &&
+              (ar ? CATCOC_BOUND(p, SITE_AR_OUT, static_cast<int64_t>(parity) * p.ar_out_parity_bytes + dst_row0 +
+                                                     static_cast<int64_t>(rows_valid - 1) * p.ldc * 2 + row_span, LIM_AR_OUT)
+                  : CATCOC_BOUND(p, SITE_OUT_STORE, dst_row0 + static_cast<int64_t>(rows_valid - 1) * p.ldc * 2 + row_span,
+                                 LIM_OUT));
+          for (int u0 = 0; io_ok && u0 < total_units; u0 += 32 * 8) {
             uint4 v[8];
             int64_t doff[8];
 #pragma unroll
@@ -1279,8 +1359,8 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
           // the reduced rows are in every rank's output: stamp them everywhere
           __syncwarp();
           if (lane == 0 && !p.withhold_signals) {
-            const int gid = (p.rank * sched.tiles_per_seg + ti.tile_in_seg) * qpt + qd;
-            ptx::multimem_st_release_u32(p.done_mc + gid, epoch);
+            const int gid = ((p.rank * sched.tiles_per_seg + ti.tile_in_seg) * qpt + qd) * kPullStrips + strip;
+            if (CATCOC_BOUND(p, SITE_DONE_POST, gid + 1, LIM_DONE)) ptx::multimem_st_release_u32(p.done_mc + gid, epoch);
           }
         }
       }

@@ -48,6 +48,31 @@ enum StatusCode : uint32_t {
   STATUS_TIMEOUT_GATHER = 4,    // a peer's A chunk never arrived (AG producer)
   STATUS_TIMEOUT_BARRIER = 5,   // barrier_all / wait_until ran out of time
   STATUS_BAD_ARGUMENT = 6,
+  STATUS_OUT_OF_RANGE = 7,      // checked build: an offset left its buffer (what = site, expected = limit, seen = offset)
+};
+
+// Buffers whose extents the checked build (-DCATCOC_CHECKED) knows; index into FusedParams::limit.
+// Byte counts for data, word counts for stamp arrays, 0 = unknown (not checked).
+enum LimitId : int {
+  LIM_STAGE = 0, LIM_ARRIVE = 1, LIM_DONE = 2, LIM_AR_OUT = 3, LIM_GATHERED = 4, LIM_GFLAGS = 5, LIM_PART = 6,
+  LIM_OUT = 7, LIM_COUNT = 8,
+};
+// Where a checked access sits (status word `what` of STATUS_OUT_OF_RANGE).
+enum CheckSite : uint32_t {
+  SITE_PUSH_SLAB = 1,      // partial tile -> owner's staging slab
+  SITE_FOLD_SLAB = 2,      // owner reads the peers' slabs
+  SITE_ARRIVE_POST = 3,    // arrival stamp written
+  SITE_ARRIVE_POLL = 4,    // arrival stamp polled
+  SITE_DONE_POST = 5,
+  SITE_DONE_POLL = 6,
+  SITE_AR_OUT = 7,         // reduced tile -> every rank's output
+  SITE_GATHER_PUSH = 8,    // A shard -> gathered buffer
+  SITE_GFLAG_POST = 9,
+  SITE_GFLAG_POLL = 10,
+  SITE_PART_STORE = 11,    // pull flavour: partial tile -> local partial buffer
+  SITE_PART_REDUCE = 12,   // pull flavour: in-switch sum of the partial copies
+  SITE_OUT_STORE = 13,     // final rows -> out
+  SITE_TMEM = 14,          // accumulator columns
 };
 
 // Layout of the status block (uint32 words): [0] code, [1] rank, [2] what (tile / chunk id),
@@ -152,6 +177,7 @@ struct alignas(64) FusedParams {
   uint32_t* epoch_ptr;       // completed launches on this workspace (local memory)
   uint32_t* cta_counter;     // CTAs finished in this launch (local memory)
   uint32_t* status;          // kStatusWords words, host-visible
+  int64_t limit[LIM_COUNT];  // extents of the buffers above for the checked build (see LimitId)
   uint64_t timeout_ns;
   int withhold_signals;      // test hook: this rank posts no arrival / done / chunk stamps
   // Optional per-launch cycle counters (summed over CTAs), null = off:

@@ -214,7 +214,15 @@ using namespace catcoc;
 using namespace catcoc::host;
 
 extern "C" const char* catcoc_last_error(void) { return last_error(); }
-extern "C" int catcoc_version(void) { return 100; }
+extern "C" int catcoc_version(void) { return 110; }
+// 1 when this library was built with the device-side bounds checks (-DCATCOC_CHECKED)
+extern "C" int catcoc_is_checked_build(void) {
+#if defined(CATCOC_CHECKED)
+  return 1;
+#else
+  return 0;
+#endif
+}
 extern "C" int catcoc_num_sms(int device) { return sm_count(device); }
 
 static int norm_bn(int bn) { return (bn == 64 || bn == 128 || bn == 256) ? bn : 256; }
@@ -573,7 +581,8 @@ int catcoc_build_params(const CatcocOpArgs* args, FusedParams* p, int* kind_out,
   }
   // Partial tiles are pushed into the owners' slabs by TMA stores when every peer's staging
   // region can be described as one [slots * bm, bn] matrix (it always can: slabs are dense).
-  if (!pull && fused && (a.mode == CATCOC_MODE_RS || a.mode == CATCOC_MODE_AR) && push_tma_enabled()) {
+  if (!pull && fused && (a.mode == CATCOC_MODE_RS || a.mode == CATCOC_MODE_AR) &&
+      (a.tiling.push_tma == 1 || (a.tiling.push_tma < 0 && push_tma_enabled()))) {
     const int pelt = fmt_bytes(a.partial_fmt);
     const CUtensorMapDataType pdt = a.partial_fmt == CATCOC_FMT_F16    ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
                                     : a.partial_fmt == CATCOC_FMT_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
@@ -604,6 +613,27 @@ int catcoc_build_params(const CatcocOpArgs* args, FusedParams* p, int* kind_out,
     p->bias_f = a.bias_f;
   }
 
+  // Extents of the caller's buffers: checked on the device in the bounds-checked build, and here, in
+  // every build, against what the tensor maps built above may write.
+  for (int i = 0; i < LIM_COUNT; ++i) p->limit[i] = a.limit[i] > 0 ? a.limit[i] : 0;
+  if (p->pull && p->limit[LIM_PART] > 0 &&
+      p->limit[LIM_PART] < a.part_parity_bytes + static_cast<int64_t>(a.M) * a.N * fmt_bytes(a.partial_fmt)) {
+    set_error("the partial buffer (%lld bytes) cannot hold two parity halves of [M, N]", static_cast<long long>(p->limit[LIM_PART]));
+    return CATCOC_E_BAD_ARG;
+  }
+  if (p->stage_tma && p->limit[LIM_STAGE] > 0 &&
+      p->limit[LIM_STAGE] < a.stage_parity_bytes + stage_half_bytes(p->sched, fmt_bytes(a.partial_fmt))) {
+    set_error("the staging region (%lld bytes) cannot hold two parity halves of slabs", static_cast<long long>(p->limit[LIM_STAGE]));
+    return CATCOC_E_BAD_ARG;
+  }
+  if (p->out_tma && !p->pull && p->limit[LIM_OUT] > 0) {
+    const int64_t rows_out = (fused && a.mode == CATCOC_MODE_RS) ? p->sched.seg_len : a.M;
+    if (p->limit[LIM_OUT] < ((rows_out - 1) * a.ldc + a.N) * fmt_bytes(a.out_fmt)) {
+      set_error("the output buffer (%lld bytes) is smaller than [%lld, %d] with pitch %lld",
+                static_cast<long long>(p->limit[LIM_OUT]), static_cast<long long>(rows_out), a.N, static_cast<long long>(a.ldc));
+      return CATCOC_E_BAD_ARG;
+    }
+  }
   p->epoch_ptr = a.epoch_ptr;
   p->cta_counter = a.cta_counter;
   p->status = a.status;

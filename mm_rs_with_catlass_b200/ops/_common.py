@@ -133,6 +133,7 @@ def fill_tiling(args: N.OpArgs, tiling: Optional[TilingConfig]) -> None:
     args.tiling.rounds = t.rounds
     args.tiling.pull = 0              # the fused ops switch it on once the buffers it needs are attached
     args.tiling.comm_warps = t.comm_warps
+    args.tiling.push_tma = t.push_tma
 
 
 def default_timeout_ns() -> int:

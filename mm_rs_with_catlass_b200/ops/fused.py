@@ -32,6 +32,10 @@ from . import _common as cm
 from .gemm import matmul as _local_matmul
 
 _SEG_ROWS, _SEG_COLS = 0, 1
+# Smallest world size at which a tiling that leaves the choice open (pull = -1) takes the pull flavour.
+# Measured at M = 8192 (K = 28672 / W): on 2 and 4 GPUs pushing the partial tiles is 5-7 % faster (the
+# pushes hide behind a long K loop and the owner's last tiles need no further round trip).
+_PULL_MIN_WORLD = 8
 _NVTX = os.environ.get("CATCOC_NVTX", "0") == "1"   # NVTX range around every fused launch
 
 
@@ -61,6 +65,11 @@ def _data_region(ctx: ShmemContext, purpose: str, half_bytes: int) -> Tuple[Symm
         ctx.counters["regions_grown"] = ctx.counters.get("regions_grown", 0) + 1
         _plans_of(ctx).clear()   # plans hold workspace addresses; every rank grows at the same call
     return buf, (buf.nbytes // 2) // 1024 * 1024
+
+
+def _span_bytes(t: torch.Tensor) -> int:
+    """Bytes from a 2-D row-major tensor's first element to one past its last."""
+    return ((t.shape[0] - 1) * t.stride(0) + t.shape[1]) * t.element_size() if t.numel() else 0
 
 
 def _pair(t: TilingConfig) -> int:
@@ -162,6 +171,7 @@ def _attach_stage(ctx: ShmemContext, args, m: int, n: int, seg_dim: int, t: Tili
                         int(lib.catcoc_arrive_words(m, n, ctx.world, seg_dim, bn, t.cta_pair)))
     args.partial_fmt = partial_fmt
     args.stage_parity_bytes = parity_bytes
+    args.limit[N.LIM_STAGE], args.limit[N.LIM_ARRIVE] = stage.nbytes, arrive.nbytes // 4
     for p in range(ctx.world):
         args.stage[p] = stage.ptr(p)
         args.arrive[p] = arrive.ptr(p)
@@ -173,7 +183,7 @@ def _pull_possible(ctx: ShmemContext, t: TilingConfig, n: int, seg_dim: int, out
     reads lies inside one tile row. ``CATCOC_PULL=0`` switches the automatic choice off."""
     if t.pull == 0 or t.fp32_partials or not ctx.mc_base:
         why = None if t.pull != 1 else ("fp32 partials" if t.fp32_partials else "no multicast alias")
-    elif t.pull == -1 and os.environ.get("CATCOC_PULL", "1") == "0":
+    elif t.pull == -1 and os.environ.get("CATCOC_PULL", "1" if ctx.world >= _PULL_MIN_WORLD else "0") == "0":
         why = None
     elif n % 8 or (seg_dim == _SEG_COLS and (-(-n // ctx.world)) % 8):
         why = "N or the columns per rank are not multiples of 8"
@@ -197,6 +207,7 @@ def _attach_pull(ctx: ShmemContext, args, m: int, n: int, seg_dim: int, t: Tilin
                        int(lib.catcoc_arrive_words(m, n, ctx.world, seg_dim, t.effective_bn, t.cta_pair)))
     args.partial_fmt = fmt
     args.part, args.part_mc, args.part_parity_bytes = part.ptr(), part.mc_ptr(), parity_bytes
+    args.limit[N.LIM_PART], args.limit[N.LIM_ARRIVE] = part.nbytes, ready.nbytes // 4
     for p in range(ctx.world):
         args.arrive[p] = ready.ptr(p)
     args.tiling.pull = 1
@@ -305,6 +316,7 @@ def matmul_reduce_scatter(a: torch.Tensor, b: torch.Tensor, *, trans_a: bool = F
     with torch.cuda.device(dev):
         args, keep = _base_args(ctx, N.MODE_RS, a, trans_a, b, trans_b, m, n, k, t, seg_rows=rows)
         args.out, args.ldc, args.out_fmt = out.data_ptr(), out.stride(0), cm.out_fmt(out.dtype)
+        args.limit[N.LIM_OUT] = _span_bytes(out)
         if _pull_possible(ctx, t, n, _SEG_ROWS, out):
             _attach_pull(ctx, args, m, n, _SEG_ROWS, t, cm.out_fmt(a.dtype))
         else:
@@ -359,8 +371,9 @@ def matmul_allreduce(a: torch.Tensor, b: torch.Tensor, *, trans_a: bool = False,
                                 seg_rows=(-(-m // ctx.world)) if seg_dim == _SEG_ROWS else 0)
         args.tiling.seg_dim = seg_dim
         obuf, parity_bytes = _data_region(ctx, "ar_out", m * n * elt)
+        # one word per 32-row quarter of a tile; the pull flavour stamps each of the quarter's 4 strips
         done = ctx.stamps(("done", m, n, ctx.world, seg_dim, t.effective_bn, _pair(t)),
-                          int(lib.catcoc_done_words(m, n, ctx.world, seg_dim, t.effective_bn, t.cta_pair)))
+                          4 * int(lib.catcoc_done_words(m, n, ctx.world, seg_dim, t.effective_bn, t.cta_pair)))
         args.out, args.ldc, args.out_fmt = None, n, cm.out_fmt(a.dtype)
         args.ar_out_parity_bytes = parity_bytes
         for p in range(ctx.world):
@@ -368,6 +381,7 @@ def matmul_allreduce(a: torch.Tensor, b: torch.Tensor, *, trans_a: bool = False,
             args.done[p] = done.ptr(p)
         args.ar_out_mc = obuf.mc_ptr() or None
         args.done_mc = done.mc_ptr() or None
+        args.limit[N.LIM_AR_OUT], args.limit[N.LIM_DONE] = obuf.nbytes, done.nbytes // 4
         if _pull_possible(ctx, t, n, seg_dim, None):
             _attach_pull(ctx, args, m, n, seg_dim, t, cm.out_fmt(a.dtype))
             args.tiling.use_multicast = 1     # the reducers broadcast through the alias
@@ -461,6 +475,8 @@ def allgather_matmul(a_shard: torch.Tensor, b: torch.Tensor, *, trans_b: bool = 
         for p in range(W):
             args.gathered[p] = gbuf.ptr(p)
             args.gflags[p] = gfl.ptr(p)
+        args.limit[N.LIM_GATHERED], args.limit[N.LIM_GFLAGS] = gbuf.nbytes, gfl.nbytes // 4
+        args.limit[N.LIM_OUT] = _span_bytes(out)
         # shard broadcast by multicast stores (one multimem.st reaches every rank) when the heap has
         # the alias and the tiling or CATCOC_AG_MULTICAST asks for it
         want_mc = t.use_multicast if os.environ.get("CATCOC_AG_MULTICAST") is None \
@@ -536,6 +552,7 @@ def quant_matmul_reduce_scatter(x1: torch.Tensor, x2: torch.Tensor, scale_x1: to
     with torch.cuda.device(dev):
         args, keep = _base_args(ctx, N.MODE_RS, x1, trans_a, x2, trans_b, m, n, k, t, seg_rows=rows)
         args.out, args.ldc, args.out_fmt = out.data_ptr(), out.stride(0), cm.out_fmt(out_dtype)
+        args.limit[N.LIM_OUT] = _span_bytes(out)
         args.scale_m = scale_x1.data_ptr()
         args.scale_n = scale_x2.data_ptr()
         args.bias = bias.data_ptr() if bias is not None else None

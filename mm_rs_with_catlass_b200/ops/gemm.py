@@ -110,6 +110,7 @@ def matmul(a: torch.Tensor, b: torch.Tensor, *, trans_a: bool = False, trans_b: 
         args.a, args.lda = oa.ptr, oa.ld
         args.b, args.ldb = ob.ptr, ob.ld
         args.out, args.ldc, args.out_fmt = out.data_ptr(), out.stride(0), cm.out_fmt(out_dtype)
+        args.limit[N.LIM_OUT] = ((out.shape[0] - 1) * out.stride(0) + out.shape[1]) * out.element_size()
         args.partial_fmt = args.out_fmt
         cm.fill_tiling(args, tiling)
         args.rank, args.W = 0, 1

@@ -41,6 +41,8 @@ class TilingConfig:
                            # owner sums them through NVSwitch (multimem.ld_reduce); 0 = partial tiles are pushed
                            # to the owner, who sums them in rank order (deterministic); -1 = pull when possible
     comm_warps: int = 0    # communication / reducer warps per CTA, 1..5 (0 = 5): all-gather and pull flavours
+    push_tma: int = -1     # push flavour: partial tiles travel by TMA stores (1) or 16-byte stores (0); -1: the
+                           # CATCOC_PUSH_TMA environment variable decides (default: 16-byte stores)
     # --- reference-compatible fields (carried, reported, not steering the kernel) ---
     m0: int = 128
     n0: int = 256
@@ -68,6 +70,8 @@ class TilingConfig:
             raise ValueError("seg_dim must be -1, 0 or 1")
         if self.pull not in (-1, 0, 1):
             raise ValueError("pull must be -1, 0 or 1")
+        if self.push_tma not in (-1, 0, 1):
+            raise ValueError("push_tma must be -1, 0 or 1")
         if self.comm_warps < 0 or self.comm_warps > 5:
             raise ValueError("comm_warps must be in [0, 5]")
         return self

@@ -23,7 +23,7 @@ from .config import TilingConfig
 COLUMNS = ["Op", "M", "K", "N", "Transpose A", "Transpose B", "commInterval", "commTileM", "commBlockM",
            "commNpuSplit", "commDataSplit", "Time(us)",
            "dtype", "world", "bn", "swizzle", "num_ctas", "seg_dim", "use_multicast", "cta_pair", "fp32_partials", "rounds", "baseline_us",
-           "pull", "comm_warps"]
+           "pull", "comm_warps", "push_tma"]
 
 _DTYPE_NAMES = {torch.float16: "fp16", torch.bfloat16: "bf16", torch.int8: "int8"}
 DEFAULT_TABLE_PATH = Path(__file__).resolve().parent / "best_tilings.csv"
@@ -56,7 +56,7 @@ class Row:
                 t.comm_block_m, t.comm_npu_split, t.comm_data_split,
                 "" if math.isnan(self.time_us) else "%.3f" % self.time_us,
                 self.dtype, self.world, t.bn, t.swizzle, t.num_ctas, t.seg_dim, int(t.use_multicast), t.cta_pair, int(t.fp32_partials), t.rounds,
-                "" if math.isnan(self.baseline_us) else "%.3f" % self.baseline_us, t.pull, t.comm_warps]
+                "" if math.isnan(self.baseline_us) else "%.3f" % self.baseline_us, t.pull, t.comm_warps, t.push_tma]
 
     @staticmethod
     def from_csv(r: Dict[str, str]) -> "Row":
@@ -66,6 +66,7 @@ class Row:
                          seg_dim=int(r.get("seg_dim") or -1), use_multicast=bool(int(r.get("use_multicast") or 0)), cta_pair=int(r.get("cta_pair") or 0), fp32_partials=bool(int(r.get("fp32_partials") or 0)), rounds=int(r.get("rounds") or 0),
                          pull=int(r.get("pull") if r.get("pull") not in (None, "") else -1),
                          comm_warps=int(r.get("comm_warps") or 0),
+                         push_tma=int(r.get("push_tma") if r.get("push_tma") not in (None, "") else -1),
                          comm_interval=int(r.get("commInterval") or 1), comm_tile_m=int(r.get("commTileM") or 32),
                          comm_block_m=int(r.get("commBlockM") or 32), comm_npu_split=int(r.get("commNpuSplit") or 1),
                          comm_data_split=int(r.get("commDataSplit") or 4))

@@ -12,7 +12,7 @@ All times are CUDA-event times, max over ranks, 10 warm-up + 20 timed launches.
 process): ``default`` (the chooser's pick), ``push`` (partial tiles pushed to the owner, shard sent
 peer by peer), ``pull`` (partials summed through the switch, shard sent by multicast), ``pair`` /
 ``single`` (2-CTA or single-CTA tiles), ``cwN`` (N communication warps), ``bnN`` (tile width),
-joined with ``+`` (``pull+pair+cw3``).
+``tma`` (pushes by TMA stores), joined with ``+`` (``pull+pair+cw3``).
 """
 from __future__ import annotations
 
@@ -80,10 +80,14 @@ def main(argv=None) -> int:
             return None
         t = choose(op, m, n, k, W, dtype)
         for part in variant.split("+"):
+            if part in ("push", "pull") and dtype == torch.int8:
+                continue      # int32 partial tiles are always pushed
             if part == "push":
                 t = t.with_(pull=0, use_multicast=(op == "matmul_allreduce" and t.use_multicast))
             elif part == "pull":
                 t = t.with_(pull=1, use_multicast=True)
+            elif part == "tma":
+                t = t.with_(push_tma=1)
             elif part == "pair":
                 t = t.with_(cta_pair=2, bn=max(128, t.effective_bn))
             elif part == "single":

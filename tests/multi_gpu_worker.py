@@ -364,6 +364,36 @@ elif mode == "prims":
     ctx.check("prims")
     ctx.finalize()
 
+elif mode == "checked":
+    # the fused ops under the bounds-checked build of the library (CATCOC_CHECKED=1 in the environment):
+    # pull and push flavours, both tile flavours, ragged shapes, all-gather by multicast and by peer stores
+    from mm_rs_with_catlass_b200 import _native as N
+    ctx = catcoc.init(heap_bytes=1 << 30)
+    report("checked_build_loaded", N.lib().catcoc_is_checked_build() == 1)
+    W = world
+    T = catcoc.TilingConfig
+    for (M, Nn, K) in [(256 * W, 512, 384), (2 * W * 23, 328, 136)]:
+        a, b = matmul_inputs(M, Nn, K, rank, torch.bfloat16, dev, seed=M)
+        gold = ref.matmul_allreduce(a, b, out_dtype=torch.float32)
+        mag = pmag(a, b)
+        rows = M // W
+        sl = slice(rank * rows, (rank + 1) * rows)
+        for ti, t in enumerate([T(bn=128, pull=0), T(bn=256, cta_pair=2, pull=1), T(bn=64, pull=1, comm_warps=1)]):
+            check("chk_rs_%d_t%d" % (M, ti), catcoc.matmul_reduce_scatter(a, b, tiling=t), gold[sl], K * W,
+                  torch.bfloat16, mag[sl])
+            check("chk_ar_%d_t%d" % (M, ti), catcoc.matmul_allreduce(a, b, tiling=t), gold, K * W, torch.bfloat16, mag)
+    for (m, Nn, K, mc) in [(256, 512, 512, True), (100, 328, 136, False), (64, 256, 6148, True)]:
+        a, b = matmul_inputs(m, Nn, K, rank, torch.bfloat16, dev, seed=m + K)
+        gold, gath = ref.allgather_matmul(a, b, out_dtype=torch.float32)
+        o, g = catcoc.allgather_matmul(a, b, tiling=T(bn=128, use_multicast=mc))
+        check("chk_ag_%dx%dx%d" % (m, Nn, K), o, gold, K, torch.bfloat16)
+        report("chk_ag_gathered_%d" % m, bool(torch.equal(g, gath)))
+    x1, x2, s1, s2, bias = quant_inputs(256 * W, 768, 384, rank, dev, seed=9)
+    gold = ref.quant_matmul_reduce_scatter(x1, x2, s1, s2, bias, out_dtype=torch.float32)
+    check("chk_qrs", catcoc.quant_matmul_reduce_scatter(x1, x2, s1, s2, bias, tiling=T(bn=256, cta_pair=2, rounds=2)),
+          gold, 512, torch.bfloat16)
+    ctx.finalize()
+
 elif mode == "mixed":
     # different geometries back to back, no synchronisation between the calls
     ctx = catcoc.init(heap_bytes=2 << 30, multicast=(os.environ.get("CATCOC_TEST_NVLS", "1") == "1"))
