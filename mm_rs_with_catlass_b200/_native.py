@@ -69,6 +69,7 @@ class OpArgs(C.Structure):
         ("scale_m", C.c_void_p), ("scale_n", C.c_void_p), ("bias", C.c_void_p),
         ("affine", C.c_int), ("alpha", C.c_float), ("beta", C.c_float),
         ("c_src", C.c_void_p), ("ldc_src", C.c_int64), ("bias_f", C.c_void_p),
+        ("act", C.c_int),
         ("num_groups", C.c_int), ("group_ends", C.c_void_p), ("group_rows", C.c_int),
         ("a_rows_total", C.c_int), ("a_k_total", C.c_int), ("b_n_total", C.c_int), ("b_k_total", C.c_int),
         ("g_a_row_back", C.c_int), ("g_a_k", C.c_int), ("g_b_row", C.c_int), ("g_b_k", C.c_int),

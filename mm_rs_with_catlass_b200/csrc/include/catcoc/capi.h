@@ -98,6 +98,8 @@ typedef struct CatcocOpArgs {
    * c_src has the format and row indexing of `out` (it may be `out` itself), bias_f is fp32 [N] */
   int affine; float alpha; float beta;
   const void* c_src; int64_t ldc_src; const float* bias_f;
+  int act;                                 /* activation on the finished values, in fp32: 0 none, 1 gelu (tanh form),
+                                              2 silu, 3 relu; floating-point outputs only (local GEMM, all-gather GEMM) */
 
   /* Group walk (mode LOCAL only, num_groups > 0): one launch runs num_groups products that share
    * N and K. M counts the rows of the whole output; group g owns rows [end_{g-1}, end_g), read from

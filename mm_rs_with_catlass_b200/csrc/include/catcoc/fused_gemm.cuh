@@ -171,6 +171,20 @@ CATCOC_DEVICE float2 unpack2(uint32_t u, int fmt) {
   return __half22float2(h);
 }
 
+// activation on a finished value (fp32 in, fp32 out)
+CATCOC_DEVICE float activate(float x, int act) {
+  if (act == ACT_GELU_TANH) {
+    // 0.5 x (1 + tanh(sqrt(2/pi) (x + 0.044715 x^3))), hardware tanh approximation (about 2^-11 relative)
+    const float u = 0.7978845608028654f * x * (1.0f + 0.044715f * x * x);
+    float t;
+    asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(u));
+    return 0.5f * x * (1.0f + t);
+  }
+  if (act == ACT_SILU) return x / (1.0f + __expf(-x));
+  if (act == ACT_RELU) return fmaxf(x, 0.0f);
+  return x;
+}
+
 // ---- epilogue staging -----------------------------------------------------------------
 // Each epilogue warp owns a 32 x 128 B staging area. Thread `lane` (one tile row) writes
 // 16-byte units at a position XOR-swizzled with the row so that neither the row-wise writes
@@ -904,7 +918,7 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
           }
 
           // convert this row's 32 values to the stored format and stage them
-          if (st_fmt == FMT_S32 || (st_fmt == FMT_F32 && !is_int && !(dequant && own) && !affine)) {
+          if (st_fmt == FMT_S32 || (st_fmt == FMT_F32 && !is_int && !(dequant && own) && !affine && !(kScale && p.act != ACT_NONE))) {
 #pragma unroll
             for (int u = 0; u < 8; ++u)
               stage_write(stg, lane, u,
@@ -984,6 +998,10 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
                   }
                 }
               }
+            }
+            if (kScale && p.act != ACT_NONE) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) f[j] = activate(f[j], p.act);
             }
             if (st_fmt == FMT_F32) {
 #pragma unroll

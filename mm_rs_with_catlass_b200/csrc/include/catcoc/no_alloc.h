@@ -27,6 +27,9 @@
  *     and the status words are re-zeroed on `stream`), so consecutive calls on one stream are
  *     safe. Calls whose GPU work may overlap (different streams, different host threads)
  *     race on the scratch and must be serialised by the caller.
+ *   - The per-device table of resolved scratch addresses is filled without a lock: two host
+ *     threads whose first calls on one device coincide both look the symbol up and store the
+ *     same address, which is harmless. It does not make their GPU work safe to overlap.
  */
 #pragma once
 #include <stdint.h>

@@ -39,6 +39,9 @@ enum EpiVariant {
                     // owned tiles through the switch (multimem.ld_reduce) and store / broadcast them
 };
 
+// Element-wise function on finished (owned) tiles, after scales / affine terms.
+enum Activation : int { ACT_NONE = 0, ACT_GELU_TANH = 1, ACT_SILU = 2, ACT_RELU = 3 };
+
 // Error codes written to status[0] by a kernel that gave up on a wait.
 enum StatusCode : uint32_t {
   STATUS_OK = 0,
@@ -153,6 +156,8 @@ struct alignas(64) FusedParams {
   const void* c_src;      // same element format and row indexing as `out`; may be null
   int64_t ldc_src;        // elements per row of c_src
   const float* bias_f;    // fp32 [N]; may be null
+  // activation applied last, in fp32, before the single rounding to the output format (Activation)
+  int act;
 
   // Group walk (MODE_LOCAL only; num_groups == 0: off). One launch covers several GEMMs that
   // share N and K: the output's rows [begin_g, end_g) belong to group g. It serves grouped

@@ -634,6 +634,12 @@ int catcoc_build_params(const CatcocOpArgs* args, FusedParams* p, int* kind_out,
       return CATCOC_E_BAD_ARG;
     }
   }
+  if (a.act != ACT_NONE) {
+    if (a.act < ACT_NONE || a.act > ACT_RELU) { set_error("unknown activation %d", a.act); return CATCOC_E_BAD_ARG; }
+    if (a.out_fmt == CATCOC_FMT_S32) { set_error("an activation needs a floating-point output"); return CATCOC_E_UNSUPPORTED; }
+    if (fused && a.mode != CATCOC_MODE_AG) { set_error("an activation cannot follow a partial sum (reduce-scatter / all-reduce)"); return CATCOC_E_UNSUPPORTED; }
+    p->act = a.act;
+  }
   p->epoch_ptr = a.epoch_ptr;
   p->cta_counter = a.cta_counter;
   p->status = a.status;
@@ -714,7 +720,7 @@ int max_active_pairs(int kind) {
 // The leanest epilogue variant that covers this launch.
 static int pick_epi(const FusedParams& p) {
   if (p.pull) return EPI_PULL;
-  if (p.scale_m != nullptr || p.scale_n != nullptr || p.bias != nullptr || p.affine != 0) return EPI_FULL;
+  if (p.scale_m != nullptr || p.scale_n != nullptr || p.bias != nullptr || p.affine != 0 || p.act != 0) return EPI_FULL;
   if (p.W > 1 && (p.mode == MODE_RS || p.mode == MODE_AR)) return EPI_REDUCE;
   return EPI_PLAIN;
 }

@@ -22,7 +22,10 @@ static __device__ __align__(256) unsigned char g_noalloc_scratch[CATCOC_NOALLOC_
 namespace {
 
 constexpr int kMaxDevices = 64;
-unsigned char* g_scratch_addr[kMaxDevices];   // per device, filled on first use
+// Per device, filled on first use. Two host threads that make their first call on the same device at
+// the same time both resolve the symbol and store the same address: the race is benign (an aligned
+// pointer store of one value), so the table carries no lock.
+unsigned char* g_scratch_addr[kMaxDevices];
 
 // Once per device, with that device current.
 int resolve_scratch(unsigned char** out) {
@@ -47,12 +50,29 @@ int resolve_scratch(unsigned char** out) {
 
 // Copies rows into a buffer with a 16-byte-multiple pitch and zero-fills the padding, so no
 // byte of the destination keeps what an earlier call left there.
+// Destination rows are 16-byte aligned (pitch a multiple of 16, base 256-byte aligned); a source row
+// that is 16- or 4-byte aligned is moved in units of that size, the ragged end and rows of any other
+// alignment byte by byte.
 __global__ void noalloc_pad_kernel(unsigned char* dst, long long dst_pitch, const unsigned char* src,
                                    long long src_pitch, long long rows, long long row_bytes) {
   for (long long r = blockIdx.x; r < rows; r += gridDim.x) {
     const unsigned char* s = src + r * src_pitch;
     unsigned char* d = dst + r * dst_pitch;
-    for (long long b = threadIdx.x; b < dst_pitch; b += blockDim.x) d[b] = (b < row_bytes) ? s[b] : static_cast<unsigned char>(0);
+    const unsigned long long sa = reinterpret_cast<unsigned long long>(s);
+    long long done = 0;
+    if ((sa & 15ull) == 0) {
+      const long long n16 = row_bytes >> 4;
+      for (long long i = threadIdx.x; i < n16; i += blockDim.x)
+        reinterpret_cast<uint4*>(d)[i] = reinterpret_cast<const uint4*>(s)[i];
+      done = n16 << 4;
+    } else if ((sa & 3ull) == 0) {
+      const long long n4 = row_bytes >> 2;
+      for (long long i = threadIdx.x; i < n4; i += blockDim.x)
+        reinterpret_cast<unsigned int*>(d)[i] = reinterpret_cast<const unsigned int*>(s)[i];
+      done = n4 << 2;
+    }
+    for (long long b = done + threadIdx.x; b < dst_pitch; b += blockDim.x)
+      d[b] = (b < row_bytes) ? s[b] : static_cast<unsigned char>(0);
   }
 }
 
@@ -120,7 +140,6 @@ extern "C" int catcoc_matmul_noalloc(const void* a, int64_t lda, const void* b, 
   args.b = b_pad; args.ldb = b_ld;
   args.out = out; args.ldc = ldc; args.out_fmt = out_fmt;
   args.partial_fmt = out_fmt;
-  args.tiling.bn = (elt == 1 && !trans_b) ? 256 : 0;
   args.rank = 0; args.W = 1;
   args.status = status;
   FusedParams p;

@@ -3,10 +3,13 @@
     x_shard [M/W, H]  --all-gather + GEMM-->  h [M, F/W]  --act-->  --GEMM + reduce-scatter-->  y_shard [M/W, H]
 
 with ``H`` = 8192 and ``F`` = 28672 in the benchmark configuration. Both halves are single
-fused kernels; only the activation between them is a separate elementwise launch.
+fused kernels. The activation runs in the epilogue of the first one (fp32, one rounding) where
+that kernel's epilogue variant can feed the link: on one GPU, and from 4 GPUs on, where the shard
+travels by multicast stores; on 2 GPUs it is a separate element-wise launch.
 """
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass
 from typing import Optional
 
@@ -42,7 +45,13 @@ class TPMLP:
         f = cfg.ffn // world
         self.w_up = (torch.randn((cfg.hidden, f), device=device, generator=g) * cfg.init_std).to(cfg.dtype)
         self.w_down = (torch.randn((f, cfg.hidden), device=device, generator=g) * cfg.init_std).to(cfg.dtype)
-        self.up = ColumnParallelLinear(self.w_up, ctx, tiling=up_tiling)
+        # fuse the activation into the up projection where its epilogue variant (one communication
+        # warp per CTA) does not starve the all-gather
+        self.fuse_act = cfg.activation != "none" and (world == 1 or (world >= 4 and bool(ctx.mc_base)))
+        if os.environ.get("CATCOC_FUSE_ACT") in ("0", "1"):
+            self.fuse_act = cfg.activation != "none" and os.environ["CATCOC_FUSE_ACT"] == "1"
+        self.up = ColumnParallelLinear(self.w_up, ctx, tiling=up_tiling,
+                                       activation=cfg.activation if self.fuse_act else None)
         self.down = RowParallelLinear(self.w_down, ctx, scatter=True, tiling=down_tiling)
 
     def _act(self, h: torch.Tensor) -> torch.Tensor:
@@ -57,7 +66,7 @@ class TPMLP:
 
     def forward(self, x_shard: torch.Tensor) -> torch.Tensor:
         h = self.up(x_shard)
-        return self.down(self._act(h))
+        return self.down(h if self.fuse_act else self._act(h))
 
     __call__ = forward
 

@@ -28,6 +28,29 @@ _OUT_FMT = {
 }
 
 
+_ACTIVATIONS = {None: 0, "none": 0, "gelu": 1, "gelu_tanh": 1, "silu": 2, "relu": 3}
+
+
+def act_code(name) -> int:
+    """Code of an epilogue activation: ``gelu`` (tanh form), ``silu``, ``relu`` or None."""
+    try:
+        return _ACTIVATIONS[name]
+    except KeyError:
+        raise ValueError("unknown activation %r (gelu, silu, relu or None)" % (name,)) from None
+
+
+def apply_activation(x: torch.Tensor, name) -> torch.Tensor:
+    """The same functions in PyTorch, for the paths that cannot fuse them and for goldens."""
+    code = act_code(name)
+    if code == 1:
+        return torch.nn.functional.gelu(x, approximate="tanh")
+    if code == 2:
+        return torch.nn.functional.silu(x)
+    if code == 3:
+        return torch.relu(x)
+    return x
+
+
 def in_fmt(dtype: torch.dtype) -> int:
     try:
         return _IN_FMT[dtype]

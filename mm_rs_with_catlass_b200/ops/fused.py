@@ -402,6 +402,7 @@ def matmul_allreduce(a: torch.Tensor, b: torch.Tensor, *, trans_a: bool = False,
 # ---------------------------------------------------------------------------------------
 def allgather_matmul(a_shard: torch.Tensor, b: torch.Tensor, *, trans_b: bool = False,
                      out: Optional[torch.Tensor] = None, tiling: Optional[TilingConfig] = None,
+                     activation: Optional[str] = None,
                      ctx: Optional[ShmemContext] = None) -> Tuple[torch.Tensor, torch.Tensor]:
     """Column-parallel linear on a row-sharded activation.
 
@@ -414,9 +415,14 @@ def allgather_matmul(a_shard: torch.Tensor, b: torch.Tensor, *, trans_b: bool = 
     while the tensor cores already work on the local rows; a remote row block is consumed as
     soon as its chunk stamps arrive. ``trans_a`` is not supported, as in the reference
     (examples/dynamic_tiling/impl/kernel_fp16.cpp:55-61).
+
+    ``activation`` (``"gelu"`` in its tanh form, ``"silu"``, ``"relu"``) is applied to the product
+    in the kernel's epilogue, in fp32, before the single rounding to the output dtype. The
+    epilogue variant that carries it has one communication warp per CTA, which is enough when
+    the shard travels by multicast stores.
     """
     ctx = _ctx(ctx)
-    key = ("ag", cm.tkey(a_shard), cm.tkey(b), trans_b, cm.tkey(out), tiling)
+    key = ("ag", cm.tkey(a_shard), cm.tkey(b), trans_b, cm.tkey(out), tiling, activation)
     plan = _plan_hit(ctx, key)
     if plan is not None:
         args, out_shape, out_dtype, gviews = plan
@@ -433,7 +439,7 @@ def allgather_matmul(a_shard: torch.Tensor, b: torch.Tensor, *, trans_b: bool = 
     if k != kb:
         raise ValueError("inner dimensions differ: A gives K=%d, B gives K=%d" % (k, kb))
     if ctx.world == 1:
-        o = _local_matmul(a_shard, b, trans_b=trans_b, out=out, tiling=tiling)
+        o = _local_matmul(a_shard, b, trans_b=trans_b, out=out, tiling=tiling, activation=activation)
         return o, a_shard
     if a_shard.dtype not in (torch.float16, torch.bfloat16):
         raise TypeError("allgather_matmul takes fp16 / bf16 operands")
@@ -469,6 +475,7 @@ def allgather_matmul(a_shard: torch.Tensor, b: torch.Tensor, *, trans_b: bool = 
         args.cta_counter = ctx.launch_state.data_ptr() + 4
         args.status = ctx.status.data_ptr()
         args.ag_m, args.ag_ld = m, ag_ld
+        args.act = cm.act_code(activation)
         gbuf, parity_bytes = _data_region(ctx, "gathered", W * m * ag_ld * elt)
         gfl = ctx.stamps(("gflags", m, ag_ld, W, elt, _pair(t)), int(lib.catcoc_gather_flag_words(m, ag_ld, W, elt)))
         args.gathered_parity_bytes = parity_bytes

@@ -34,7 +34,7 @@ def matmul(a: torch.Tensor, b: torch.Tensor, *, trans_a: bool = False, trans_b: 
            bias: Optional[torch.Tensor] = None, tiling: Optional[TilingConfig] = None,
            trace: Optional[torch.Tensor] = None, alpha: float = 1.0, beta: float = 0.0,
            c: Optional[torch.Tensor] = None, bias_f32: Optional[torch.Tensor] = None,
-           _group: Optional[dict] = None) -> torch.Tensor:
+           activation: Optional[str] = None, _group: Optional[dict] = None) -> torch.Tensor:
     """``out = alpha * (A @ B) + beta * C + bias_f32`` with fp32 (int32 for int8) accumulation.
 
     ``a`` is stored ``[M, K]`` (``[K, M]`` with ``trans_a``), ``b`` is stored ``[K, N]``
@@ -42,7 +42,8 @@ def matmul(a: torch.Tensor, b: torch.Tensor, *, trans_a: bool = False, trans_b: 
     ``scale_n`` (fp32 ``[N]``) dequantise in the epilogue, ``bias`` (int32 ``[N]``, int8 only)
     is added to the accumulator first. ``c`` (same dtype and shape as the output; it may be the
     output itself) and ``bias_f32`` (fp32 ``[N]``) enter after the dequantisation, in fp32,
-    before the single rounding to the output dtype.
+    before the single rounding to the output dtype. ``activation`` (``"gelu"`` in its tanh form,
+    ``"silu"``, ``"relu"``) is applied last, also in fp32, in the kernel's epilogue.
 
     ``_group`` is the group walk used by :mod:`.blas` (grouped, batched and split-K products in
     one launch): a dict with the logical ``m, n, k`` of the launch and the ``OpArgs`` group
@@ -54,7 +55,7 @@ def matmul(a: torch.Tensor, b: torch.Tensor, *, trans_a: bool = False, trans_b: 
     if _group is None:
         key = (a.device, cm.tkey(a), cm.tkey(b), trans_a, trans_b, cm.tkey(out), out_dtype, cm.tkey(scale_m),
                cm.tkey(scale_n), cm.tkey(bias), tiling, None if trace is None else trace.data_ptr(), alpha, beta,
-               cm.tkey(c), cm.tkey(bias_f32))
+               cm.tkey(c), cm.tkey(bias_f32), activation)
         plan = _plans.get(key)
         if plan is not None and cm.on_device(a.device):
             args, out_shape, plan_dtype = plan
@@ -120,6 +121,9 @@ def matmul(a: torch.Tensor, b: torch.Tensor, *, trans_a: bool = False, trans_b: 
                 if t.dtype != dt or t.numel() != length or not t.is_contiguous():
                     raise ValueError("%s must be a contiguous %s tensor of %d elements" % (name, dt, length))
                 setattr(args, name, t.data_ptr())
+        args.act = cm.act_code(activation)
+        if args.act and out_dtype == torch.int32:
+            raise ValueError("an activation needs a floating-point output")
         if affine:
             args.affine = 1
             args.alpha, args.beta = float(alpha), float(beta)

@@ -25,15 +25,16 @@ from .shmem import ShmemContext
 
 
 class ColumnParallelLinear:
-    """``y[W*m, N/W] = all_gather(x_shard)[W*m, K] @ weight[K, N/W]`` on every rank."""
+    """``y[W*m, N/W] = act(all_gather(x_shard)[W*m, K] @ weight[K, N/W])`` on every rank; the optional
+    activation runs in the GEMM's epilogue."""
 
     def __init__(self, weight: torch.Tensor, ctx: Optional[ShmemContext] = None, trans_b: bool = False,
-                 tiling: Optional[TilingConfig] = None):
-        self.weight, self.ctx, self.trans_b, self.tiling = weight, ctx, trans_b, tiling
+                 tiling: Optional[TilingConfig] = None, activation: Optional[str] = None):
+        self.weight, self.ctx, self.trans_b, self.tiling, self.activation = weight, ctx, trans_b, tiling, activation
 
     def __call__(self, x_shard: torch.Tensor, out: Optional[torch.Tensor] = None, return_gathered: bool = False):
         y, gathered = fused.allgather_matmul(x_shard, self.weight, trans_b=self.trans_b, out=out, tiling=self.tiling,
-                                             ctx=self.ctx)
+                                             activation=self.activation, ctx=self.ctx)
         return (y, gathered) if return_gathered else y
 
 

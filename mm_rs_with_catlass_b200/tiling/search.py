@@ -27,6 +27,8 @@ PAIR_SPACE = (1, 2)
 SWIZZLE_SPACE = (4, 8, 16)
 NUM_CTAS_SPACE = (0,)          # 0 = one CTA per SM
 ROUNDS_SPACE = (0,)            # 0 = the launcher's default
+PULL_SPACE = (0, 1)            # reduce-scatter / all-reduce: push to the owner, or pull through the switch
+COMM_WARPS_SPACE = (0,)        # 0 = all five communication / reducer warps
 NUM_SMS = 148
 
 
@@ -67,7 +69,10 @@ def workspace_bytes(p: Problem, t: TilingConfig) -> int:
     total = 0
     if p.op in ("matmul_allreduce", "matmul_reduce_scatter", "quant_matmul_reduce_scatter"):
         pelt = 4 if (p.op == "quant_matmul_reduce_scatter" or t.fp32_partials) else p.elt
-        total += 2 * p.world * tiles_per_seg * bm * bn * pelt            # staging, two parities
+        if t.pull == 1:
+            total += 2 * p.m * p.n * pelt                                 # local partial matrix, two parities
+        else:
+            total += 2 * p.world * tiles_per_seg * bm * bn * pelt        # staging slabs, two parities
         total += 4 * tiles_per_seg * p.world * (bm // 32)                 # arrival stamps
     if p.op == "matmul_allreduce":
         total += 2 * p.m * p.n * p.elt + 4 * tiles_per_seg * p.world * (bm // 32)
@@ -98,8 +103,19 @@ def infeasible_reason(p: Problem, t: TilingConfig) -> Optional[str]:
     if p.op == "matmul_allreduce" and p.world > 1 and t.seg_dim == 1 and not p.trans_b \
             and _seg_len(p, 1) % per16:
         return "column-split ownership needs 16-byte aligned segment origins"
-    if t.use_multicast and (p.op != "matmul_allreduce" or not p.multicast_available):
-        return "NVLS broadcast applies to matmul_allreduce on a heap with a multicast alias"
+    if t.use_multicast and (p.op not in ("matmul_allreduce", "allgather_matmul") or not p.multicast_available):
+        return "multicast stores apply to matmul_allreduce and allgather_matmul on a heap with a multicast alias"
+    if t.pull == 1:
+        if p.op not in ("matmul_allreduce", "matmul_reduce_scatter") or p.world <= 1:
+            return "the pull flavour exists for the 16-bit reduce-scatter and all-reduce"
+        if not p.multicast_available:
+            return "the pull flavour sums through the multicast alias"
+        if t.fp32_partials:
+            return "the pull flavour moves partial tiles in the operand dtype"
+        if p.n % 8 or (t.seg_dim == 1 and _seg_len(p, 1) % 8):
+            return "the pull flavour needs N (and the columns per rank) to be multiples of 8"
+    if t.comm_warps and p.op not in ("allgather_matmul", "matmul_allreduce", "matmul_reduce_scatter"):
+        return "only the all-gather and the pull flavours have communication warps"
     if t.seg_dim != -1 and p.op != "matmul_allreduce":
         return "ownership split is an all-reduce knob"
     if t.num_ctas and (t.num_ctas > NUM_SMS or (t.cta_pair == 2 and t.num_ctas % 2)):
@@ -111,20 +127,37 @@ def infeasible_reason(p: Problem, t: TilingConfig) -> Optional[str]:
 
 def candidates(p: Problem, bn_space: Sequence[int] = BN_SPACE, pair_space: Sequence[int] = PAIR_SPACE,
                swizzle_space: Sequence[int] = SWIZZLE_SPACE, num_ctas_space: Sequence[int] = NUM_CTAS_SPACE,
-               rounds_space: Sequence[int] = ROUNDS_SPACE) -> List[TilingConfig]:
+               rounds_space: Sequence[int] = ROUNDS_SPACE, pull_space: Sequence[int] = PULL_SPACE,
+               comm_warps_space: Sequence[int] = COMM_WARPS_SPACE) -> List[TilingConfig]:
     """Every feasible tiling of the search space for this problem, widest tiles first."""
     seg_space: Iterable[int] = (-1,)
     mc_space: Iterable[bool] = (False,)
-    if p.op == "matmul_allreduce" and p.world > 1:
+    fused = p.world > 1 and p.op != "matmul"
+    if p.op == "matmul_allreduce" and fused:
         seg_space = (0, 1)
-        mc_space = (False, True) if p.multicast_available else (False,)
+    if p.op in ("matmul_allreduce", "allgather_matmul") and fused and p.multicast_available:
+        mc_space = (False, True)
+    if not (fused and p.op in ("matmul_allreduce", "matmul_reduce_scatter") and p.multicast_available):
+        pull_space = (0,)
+    if not (fused and p.op in ("allgather_matmul", "matmul_allreduce", "matmul_reduce_scatter")):
+        comm_warps_space = (0,)
     out: List[TilingConfig] = []
-    if p.world <= 1 or p.op in ("matmul", "allgather_matmul"):
+    if not fused or p.op == "allgather_matmul":
         rounds_space = (0,)
-    for bn, pair, swz, nctas, seg, mc, rounds in itertools.product(bn_space, pair_space, swizzle_space,
-                                                                   num_ctas_space, seg_space, mc_space, rounds_space):
+    seen = set()
+    for bn, pair, swz, nctas, seg, mc, rounds, pull, cw in itertools.product(
+            bn_space, pair_space, swizzle_space, num_ctas_space, seg_space, mc_space, rounds_space, pull_space,
+            comm_warps_space):
+        if pull == 1:
+            rounds = 0                                   # the pull flavour has no lagged rounds ...
+            mc = p.op == "matmul_allreduce"              # ... and always broadcasts through the alias
+        elif cw and p.op != "allgather_matmul":
+            continue                                     # communication warps idle in the push flavours
         t = TilingConfig(bn=bn, cta_pair=pair, swizzle=swz, num_ctas=nctas, seg_dim=seg, use_multicast=mc,
-                         rounds=rounds)
+                         rounds=rounds, pull=pull, comm_warps=cw)
+        if t in seen:
+            continue
+        seen.add(t)
         if infeasible_reason(p, t) is None:
             out.append(t)
     return out

@@ -47,6 +47,10 @@ def main(argv=None) -> int:
     ap.add_argument("--ms", default="128,1024,8192,16384")
     ap.add_argument("--ops", default="ar,ag,rs,q", help="ar, ag, rs, q (int8), mx (block-scaled fp8)")
     ap.add_argument("--variants", default="default")
+    ap.add_argument("--table", default=None,
+                    help="append every measured (shape, tiling, time) as a row of a tiling table CSV "
+                         "(tiling/table.py); `python -m mm_rs_with_catlass_b200.tiling.tune --merge` folds such "
+                         "files into the table the chooser loads")
     ap.add_argument("--hidden", type=int, default=DEFAULT_HIDDEN, help="N of the row-parallel ops, K of the all-gather op")
     ap.add_argument("--ffn", type=int, default=DEFAULT_FFN, help="split over the ranks: K_local = ffn / W")
     ap.add_argument("--trace", action="store_true",
@@ -106,11 +110,15 @@ def main(argv=None) -> int:
 
     variants = [v for v in args.variants.split(",") if v]
     base_cache = {}
+    shape_of = {}
 
     def record(op, M, fused_of, base_fn, flops_rank, link_bytes, peak=peak_tflops, shape=None, dtype=torch.bfloat16):
         """``fused_of(tiling)`` returns the callable of the fused op with that tiling."""
+        shape_of[(op, M)] = shape
         for variant in variants:
             tiling = variant_tiling(op, *shape, dtype, variant) if shape else None
+            if tiling is None and shape and args.table:
+                tiling = choose(op, *shape, W, dtype)      # record what the default resolved to
             err = None
             try:
                 fused_fn = fused_of(tiling)
@@ -152,6 +160,11 @@ def main(argv=None) -> int:
         rows.append(row)
         if rank == 0:
             print(json.dumps(row), flush=True)
+            if args.table and tiling is not None and shape_of.get((op, M)) is not None:
+                from mm_rs_with_catlass_b200.tiling.table import Row, TilingTable
+                m_, n_, k_ = shape_of[(op, M)]
+                TilingTable.append_row(args.table, Row(op, m_, k_, n_, 0, 0, "int8" if "quant" in op else "bf16", W,
+                                                       tiling, 1e3 * t_f, 1e3 * t_b))
 
     kf = FFN // W
     for M in [int(x) for x in args.ms.split(",")]:

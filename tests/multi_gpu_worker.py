@@ -263,6 +263,13 @@ if mode == "ops":
                 tag = "%s_%dx%dx%d_%d_t%d" % (str(dtype)[6:], m, N, K, tb, ti)
                 check("ag_" + tag, o, gold, K, dtype)
                 report("ag_gathered_" + tag, bool(torch.equal(g, gath)))
+    # all-gather GEMM with the activation in its epilogue (shard by multicast and by peer stores)
+    from mm_rs_with_catlass_b200.ops._common import apply_activation
+    for act, mc in (("gelu", True), ("silu", False)):
+        a, b = matmul_inputs(200, 392, 264, rank, torch.bfloat16, dev, seed=71, b_std=0.2)
+        gold, _ = ref.allgather_matmul(a, b, out_dtype=torch.float32)
+        o, _ = catcoc.allgather_matmul(a, b, activation=act, tiling=catcoc.TilingConfig(bn=128, use_multicast=mc))
+        check("ag_%s_mc%d" % (act, mc), o, apply_activation(gold, act), 264, torch.bfloat16)
     for (M, N, K, tb, with_bias) in [(128 * W, 512, 512, False, True), (256 * W, 768, 384, True, True),
                                      (4 * W, 512, 128, False, False), (W * 23, 136, 72, True, True)]:
         for out_dtype in (torch.bfloat16, torch.float16):

@@ -238,3 +238,19 @@ def test_launch_plans_follow_the_data_not_the_first_call(catcoc, device):
     assert len(G._plans) == before
     assert_close(r2, av.float() @ b.float(), k=192)
     assert not torch.equal(r1, r2)
+
+
+@pytest.mark.parametrize("act", ["gelu", "silu", "relu"])
+@pytest.mark.parametrize("pair", [1, 2])
+def test_activation_in_the_epilogue(catcoc, act, pair):
+    """The activation runs on the fp32 accumulator, before the single rounding to the output dtype."""
+    from mm_rs_with_catlass_b200.ops._common import apply_activation
+    from mm_rs_with_catlass_b200.utils.verify import assert_close
+    dev = torch.device("cuda:0")
+    a = torch.randn(384, 256, device=dev).to(torch.bfloat16)
+    b = (torch.randn(256, 328, device=dev) * 0.2).to(torch.bfloat16)
+    out = catcoc.matmul(a, b, activation=act, tiling=catcoc.TilingConfig(bn=128, cta_pair=pair))
+    gold = apply_activation(a.float() @ b.float(), act)
+    assert_close(out, gold, k=256, dtype=torch.bfloat16, what="matmul + " + act)
+    with pytest.raises(ValueError):
+        catcoc.matmul(a, b, activation="tanh")

@@ -42,7 +42,12 @@ def test_infeasible_reasons():
     small = search.Problem("matmul_allreduce", 16384, 8192, 3584, 8, heap_bytes=64 << 20)
     assert "heap" in search.infeasible_reason(small, TilingConfig(seg_dim=0))
     nomc = search.Problem("matmul_allreduce", 1024, 1024, 256, 2)
-    assert "NVLS" in search.infeasible_reason(nomc, TilingConfig(use_multicast=True))
+    assert "multicast" in search.infeasible_reason(nomc, TilingConfig(use_multicast=True))
+    assert "multicast alias" in search.infeasible_reason(nomc, TilingConfig(pull=1))
+    q = search.Problem("quant_matmul_reduce_scatter", 1024, 1024, 256, 8, dtype="int8", multicast_available=True)
+    assert "16-bit" in search.infeasible_reason(q, TilingConfig(pull=1))
+    odd = search.Problem("matmul_reduce_scatter", 1024, 1004, 256, 4, multicast_available=True)
+    assert "multiples of 8" in search.infeasible_reason(odd, TilingConfig(pull=1))
 
 
 def test_workspace_estimate_matches_hand_count():
@@ -117,3 +122,18 @@ def test_mx_scale_packing_matches_the_tensor_core_block_layout():
     assert int(p[1, 1, (10 % 32) * 16 + 3 * 4 + 3]) == 127          # padding is the neutral scale
     with pytest.raises(ValueError):
         mx.quantize_mxf8(torch.randn(4, 40))
+
+
+def test_search_space_offers_both_data_paths_where_the_heap_has_a_multicast_alias():
+    rs = search.Problem("matmul_reduce_scatter", 8192, 8192, 3584, 8, multicast_available=True)
+    cands = search.candidates(rs)
+    assert {t.pull for t in cands} == {0, 1}
+    assert all(t.rounds == 0 for t in cands if t.pull == 1)
+    ag = search.Problem("allgather_matmul", 8192, 3584, 8192, 8, multicast_available=True)
+    assert {t.use_multicast for t in search.candidates(ag)} == {False, True}
+    ar = search.Problem("matmul_allreduce", 8192, 8192, 3584, 8, multicast_available=True)
+    assert all(t.use_multicast for t in search.candidates(ar) if t.pull == 1)
+    # without the alias only the push flavour and peer stores remain
+    rs_p2p = search.Problem("matmul_reduce_scatter", 8192, 8192, 3584, 8)
+    assert {t.pull for t in search.candidates(rs_p2p)} == {0}
+    assert len(set(cands)) == len(cands)

@@ -44,11 +44,17 @@ def test_noalloc_entry_matches_regular_entry_on_two_calls_in_a_row(device):
         b = (torch.randn((n, k) if tb else (k, n), device=device, generator=g) * 0.05).to(torch.bfloat16)
         expected = catcoc.matmul(a, b, trans_a=ta, trans_b=tb)            # regular entry point
         out = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device=device)
+        torch.cuda.synchronize(device)
         before = torch.cuda.memory_allocated(device)
+        free_before = torch.cuda.mem_get_info(device)[0]                   # cudaMemGetInfo: sees every allocation
         rc = _call(lib, a, b, out, m, n, k, N.IN_BF16, N.FMT_BF16, ta, tb)
         assert rc == 0, N.last_error()
         torch.cuda.synchronize(device)
         assert torch.cuda.memory_allocated(device) == before               # no torch allocation either
+        if i > 0:
+            # By the second call every kernel of the path is loaded (the driver may take memory when it
+            # loads one): the device's free memory must not move, whoever would have allocated.
+            assert torch.cuda.mem_get_info(device)[0] == free_before
         assert _status(lib)[0] == 0
         # same kernel and operands as the regular entry point (which may pick another tile shape)
         assert_close(out, expected.float(), k=k, dtype=torch.bfloat16)
