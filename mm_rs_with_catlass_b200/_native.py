@@ -79,6 +79,7 @@ class OpArgs(C.Structure):
         ("timeout_ns", C.c_uint64),
         ("withhold_signals", C.c_int),
         ("trace", C.c_void_p),
+        ("events", C.c_void_p), ("events_cap", C.c_uint32),
     ]
 
 

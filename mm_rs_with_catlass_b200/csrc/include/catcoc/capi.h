@@ -121,6 +121,7 @@ typedef struct CatcocOpArgs {
   uint64_t timeout_ns;
   int withhold_signals;
   unsigned long long* trace;               /* optional 16 x u64 cycle counters (see params.h), or NULL */
+  uint32_t* events; uint32_t events_cap;   /* optional event ring (4 + 4 * events_cap words, see params.h), or NULL */
 } CatcocOpArgs;
 
 const char* catcoc_last_error(void);

@@ -120,6 +120,25 @@ CATCOC_DEVICE bool bound_ok(const FusedParams& p, uint32_t site, int64_t end, in
 #define CATCOC_BOUND_ABS(p, site, end, lim) (true)
 #endif
 
+// One record of the optional event ring (see FusedParams::events); call from ONE lane of a role.
+// Compiled into the diagnostic build only (-DCATCOC_CHECKED, loaded with CATCOC_CHECKED=1): in the
+// register-capped 384-thread variants even the dormant call cost spills in the epilogue.
+CATCOC_DEVICE void emit_event(const FusedParams& p, uint32_t role, uint32_t phase, uint32_t tile) {
+#if !defined(CATCOC_CHECKED)
+  (void)p; (void)role; (void)phase; (void)tile;
+  return;
+#endif
+  if (p.events == nullptr) return;
+  const uint32_t slot = atomicAdd(p.events, 1u);
+  if (slot >= p.events_cap) return;
+  const uint64_t t = ptx::globaltimer_ns();
+  uint32_t* r = p.events + 4 + 4 * static_cast<size_t>(slot);
+  r[0] = static_cast<uint32_t>(t);
+  r[1] = static_cast<uint32_t>(t >> 32);
+  r[2] = (blockIdx.x << 16) | (role << 8) | phase;
+  r[3] = tile;
+}
+
 // Cycle accounting for the optional trace counters.
 struct Tick {
   long long t;
@@ -434,6 +453,7 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
           }
         }
       }
+      if (lane == 0) emit_event(p, EV_PRODUCER, EV_BEGIN, static_cast<uint32_t>(t));
       for (int kb = 0; kb < num_kb; ++kb) {
         tick.lap(c_issue);
         const bool got = ptx::mbar_wait(&tail->empty[stage], phase ^ 1u, p.timeout_ns, abort_flag);
@@ -541,6 +561,7 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
           break;
         }
         ptx::tcgen05_fence_after();
+        if (lane == 0) emit_event(p, EV_MMA, EV_BEGIN, static_cast<uint32_t>(t));
         const uint32_t tmem_d = tmem_base + static_cast<uint32_t>(acc) * acc_stride;
         for (int kb = 0; kb < num_kb; ++kb) {
           tick.lap(c_issue);
@@ -626,6 +647,7 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
           if (++stage == kStages) { stage = 0; phase ^= 1u; }
         }
         if (!ok) break;
+        if (lane == 0) emit_event(p, EV_MMA, EV_END, static_cast<uint32_t>(t));
         acc ^= 1;
         if (acc == 0) acc_phase ^= 1u;
       }
@@ -720,6 +742,7 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
         break;
       }
       ptx::tcgen05_fence_after();
+      if (lane == 0 && q == 0) emit_event(p, EV_EPILOGUE, EV_BEGIN, static_cast<uint32_t>(t));
       const long long tile_t0 = tr ? ptx::clock_cycles() : 0;
       const uint32_t taddr =
           tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(acc) * acc_stride;
@@ -1126,6 +1149,7 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
       }
 
       tick.lap(c_pub);
+      if (lane == 0 && q == 0) emit_event(p, EV_EPILOGUE, EV_END, static_cast<uint32_t>(t));
       if (tr) {
         const unsigned long long dt = static_cast<unsigned long long>(ptx::clock_cycles() - tile_t0);
         if (own) c_tile_own += dt; else c_tile_push += dt;
@@ -1245,6 +1269,7 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
       const int64_t total_units = mcast ? units_per_peer : static_cast<int64_t>(p.W) * units_per_peer;
       const int slice_bytes = gp.slice_cols * p.elt_bytes_a;   // <= 512
       const int64_t row_bytes = static_cast<int64_t>(gp.K) * p.elt_bytes_a;
+      if (lane == 0) emit_event(p, EV_COMM, EV_BEGIN, static_cast<uint32_t>(cw));
       for (int64_t u = static_cast<int64_t>(blockIdx.x) * ncw + cw; u < total_units;
            u += static_cast<int64_t>(gridDim.x) * ncw) {
         if (*abort_flag) break;
@@ -1295,6 +1320,7 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
           else ptx::st_release_sys_u32(p.gflags[peer] + fi, epoch);
         }
       }
+      if (lane == 0) emit_event(p, EV_COMM, EV_END, static_cast<uint32_t>(cw));
     } else if (kPull && pull) {
       // Reducer warps of the pull flavour. Task j = (i-th tile of MY segment in visiting order, a
       // 32-row quarter of it, an 8-row strip of the quarter), dealt out round-robin over all reducer
@@ -1338,6 +1364,7 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
           ok = __all_sync(0xffffffffu, ok);
           if (!ok) break;
           ptx::fence_acq_rel_sys();   // the other lanes' acquires order this lane's loads too
+          if (lane == 0) emit_event(p, EV_REDUCER, EV_BEGIN, static_cast<uint32_t>(j));
           const int upr = (ti.cols * 2 + 15) >> 4;          // 16-byte units per row
           const int total_units = rows_valid * upr;
           const int64_t src_row0 = (static_cast<int64_t>(ti.m0 + row0) * p.ldp + ti.n0) * 2;
@@ -1373,6 +1400,7 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
             }
           }
         }
+        if (lane == 0 && rows_valid > 0) emit_event(p, EV_REDUCER, EV_END, static_cast<uint32_t>(j));
         if (ar) {
           // the reduced rows are in every rank's output: stamp them everywhere
           __syncwarp();

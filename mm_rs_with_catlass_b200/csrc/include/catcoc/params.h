@@ -193,6 +193,15 @@ struct alignas(64) FusedParams {
   // [11] epilogue TMEM loads      [12] convert + stage to shared         [13] flush to global / peers
   // [14] epilogue time on owned tiles (accumulator ready -> tile done)   [15] the same on pushed tiles
   unsigned long long* trace;
+  // Optional event ring (null = off): word 0 of `events` is the write cursor, records of four 32-bit
+  // words follow from word 4 on: {globaltimer low, globaltimer high, cta << 16 | role << 8 | phase, tile}.
+  // One lane per role writes a record at the start and at the end of every tile (EventRole / EventPhase);
+  // the host turns the ring into a Chrome trace (utils/trace.py).
+  uint32_t* events;
+  uint32_t events_cap;       // records the ring can hold
 };
+
+enum EventRole : uint32_t { EV_PRODUCER = 0, EV_MMA = 1, EV_EPILOGUE = 2, EV_COMM = 3, EV_REDUCER = 4 };
+enum EventPhase : uint32_t { EV_BEGIN = 0, EV_END = 1, EV_WAIT_PEER = 2 };
 
 }  // namespace catcoc

@@ -648,6 +648,8 @@ int catcoc_build_params(const CatcocOpArgs* args, FusedParams* p, int* kind_out,
   p->timeout_ns = a.timeout_ns ? a.timeout_ns : 10000000000ull;
   p->withhold_signals = a.withhold_signals;
   p->trace = a.trace;
+  p->events = a.events;
+  p->events_cap = a.events != nullptr ? a.events_cap : 0u;
 
   int device = 0;
   cudaGetDevice(&device);

@@ -172,6 +172,7 @@ def launch(args: N.OpArgs, device: torch.device, timeout_ns: Optional[int] = Non
     The wait budget is re-read on every launch so that a cached argument block follows
     ``CATCOC_TIMEOUT_MS``."""
     args.timeout_ns = timeout_ns if timeout_ns is not None else default_timeout_ns()
+    args.events, args.events_cap = _event_ring
     if _raw_stream is not None and device.index is not None:
         stream = _raw_stream(device.index)
     else:
@@ -184,6 +185,14 @@ def launch(args: N.OpArgs, device: torch.device, timeout_ns: Optional[int] = Non
 
 
 _launches = 0
+_event_ring = (None, 0)
+
+
+def set_event_ring(ptr, capacity: int) -> None:
+    """Device address and record capacity of the event ring every launch from now on writes to
+    (None switches it off); see utils/trace.py."""
+    global _event_ring
+    _event_ring = (ptr, int(capacity) if ptr else 0)
 
 
 def launch_count() -> int:

@@ -119,3 +119,31 @@ def test_fused_ops_on_two_gpus_pass_under_the_checked_build(gpu_count):
     from test_fused_multi_gpu import _run
     cases = _run(2, "checked", {"CATCOC_CHECKED": "1", "CATCOC_TIMEOUT_MS": "3000"}, timeout=600)
     assert len(cases) >= 12
+
+
+def test_event_ring_gives_a_chrome_trace_with_matched_begin_and_end_records(tmp_path):
+    path = str(tmp_path / "trace.json")
+    out = _child("""
+        import json, torch
+        import mm_rs_with_catlass_b200 as catcoc
+        from mm_rs_with_catlass_b200.utils.trace import EventTrace
+        dev = torch.device("cuda:0")
+        a = torch.randn(1024, 512, device=dev).bfloat16()
+        b = torch.randn(512, 1024, device=dev).bfloat16()
+        with EventTrace(capacity=4096) as tr:
+            catcoc.matmul(a, b, tiling=catcoc.TilingConfig(bn=256, cta_pair=1))
+        recs = tr.records()
+        n = tr.dump_chrome(%r)
+        by = {}
+        for r in recs:
+            by.setdefault((r["cta"], r["role"], r["tile"]), []).append(r["phase"])
+        epi = [k for k in by if k[1] == 2]
+        print(json.dumps({"events": n, "dropped": tr.dropped, "epilogue_tiles": len(epi),
+                          "paired": all(sorted(by[k]) == [0, 1] for k in epi),
+                          "ordered": all(x["t_ns"] <= y["t_ns"] for x, y in zip(recs, recs[1:]))}))
+    """ % path)
+    r = out[-1]
+    assert r["epilogue_tiles"] == 32 and r["paired"] and r["ordered"] and r["dropped"] == 0, r   # 8 x 4 tiles
+    with open(path) as fh:
+        trace = json.load(fh)
+    assert len([e for e in trace["traceEvents"] if e.get("ph") in ("B", "E")]) == r["events"]
