@@ -32,10 +32,12 @@ from . import _common as cm
 from .gemm import matmul as _local_matmul
 
 _SEG_ROWS, _SEG_COLS = 0, 1
-# Smallest world size at which a tiling that leaves the choice open (pull = -1) takes the pull flavour.
-# Measured at M = 8192 (K = 28672 / W): on 2 and 4 GPUs pushing the partial tiles is 5-7 % faster (the
-# pushes hide behind a long K loop and the owner's last tiles need no further round trip).
-_PULL_MIN_WORLD = 8
+# Smallest world size at which a tiling that leaves the choice open (pull = -1) takes the pull flavour
+# (CATCOC_PULL=1 forces it, a tiling with pull=1 asks for it). In the sweeps on 2 and 4 GPUs pushing the
+# partial tiles won at every M (3-15 % faster: the pushes hide behind a long K loop and the owner's last
+# tiles need no further round trip), so the open choice resolves to the push flavour; the measured table
+# names the flavour per shape where it was swept.
+_PULL_MIN_WORLD = 9
 _NVTX = os.environ.get("CATCOC_NVTX", "0") == "1"   # NVTX range around every fused launch
 
 

@@ -61,8 +61,8 @@ def heuristic(op: str, m: int, n: int, k: int, world: int, dtype: torch.dtype) -
     for pair in (2, 1):
         if forced in ("1", "2") and pair != int(forced):
             continue
-        if pair == 2 and (allreduce or seg_rows < 256 or seg_rows % 256 != 0):
-            continue   # ragged 256-row tiles are mostly padding; the all-reduce runs single CTAs (measured)
+        if pair == 2 and (seg_rows < 256 or seg_rows % 256 != 0):
+            continue   # ragged 256-row tiles are mostly padding
         for bn in (256, 128, 64):
             if pair == 2 and bn < 128:
                 continue
@@ -76,13 +76,15 @@ def heuristic(op: str, m: int, n: int, k: int, world: int, dtype: torch.dtype) -
     _, bn, pair = best
     tiles_m = max(1, math.ceil(rows / 128))
     # column-group width: keep the concurrently running tiles roughly square in (rows, cols)
-    swizzle = 8 if tiles_m >= 8 else max(1, min(16, _NUM_SMS // max(1, tiles_m)))
+    # (measured on 8192 x 28672 x 8192 and 8192 x 8192 x 28672: groups of 3-4 column tiles run 3-5 % faster
+    # than groups of 8 or 16)
+    swizzle = 4 if tiles_m >= 8 else max(1, min(16, _NUM_SMS // max(1, tiles_m)))
     # measured at W = 8: the int32 partials of the quantised op are link bound, lagged owner
     # rounds overlap its owner-side reduce; the all-reduce gains from the NVLS broadcast (the op
     # layer drops the flag when the heap has no multicast alias) and from column ownership
     rounds = 4 if (op == "quant_matmul_reduce_scatter" and world > 1 and rows >= 2048) else 0
     if allreduce:
-        return TilingConfig(bn=bn, swizzle=swizzle, cta_pair=1, use_multicast=True, seg_dim=1 if ar_cols else -1)
+        return TilingConfig(bn=bn, swizzle=swizzle, cta_pair=pair, use_multicast=True, seg_dim=1 if ar_cols else -1)
     # the all-gather broadcasts its shard by multicast stores when the heap has the alias (measured at
     # M = 8192: 6 % faster than peer-by-peer stores on 4 GPUs, 7 % slower on 2, where one store per
     # 16 bytes reaches one peer either way)

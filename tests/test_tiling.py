@@ -137,3 +137,23 @@ def test_search_space_offers_both_data_paths_where_the_heap_has_a_multicast_alia
     rs_p2p = search.Problem("matmul_reduce_scatter", 8192, 8192, 3584, 8)
     assert {t.pull for t in search.candidates(rs_p2p)} == {0}
     assert len(set(cands)) == len(cands)
+
+
+def test_shipped_table_covers_every_benchmark_configuration():
+    """Every LLM tensor-parallel configuration of the benchmark (hidden 8192, FFN 28672, sharded over 2, 4 and
+    8 GPUs) resolves to a measured row: an exact hit or a neighbour within a factor of two per dimension."""
+    import torch
+    from mm_rs_with_catlass_b200.tiling import table
+    tbl = table.TilingTable.load(table.DEFAULT_TABLE_PATH).best()
+    H, F = 8192, 28672
+    ops = {"matmul_allreduce": (128, 1024, 8192), "allgather_matmul": (1024, 8192, 16384),
+           "matmul_reduce_scatter": (1024, 8192, 16384), "quant_matmul_reduce_scatter": (128, 1024, 8192, 16384)}
+    missing = []
+    for W in (2, 4, 8):
+        for op, Ms in ops.items():
+            for M in Ms:
+                m, n, k = (M, F // W, H) if op == "allgather_matmul" else (M, H, F // W)
+                dt = torch.int8 if op.startswith("quant") else torch.bfloat16
+                if tbl.lookup(op, m, n, k, W, dt) is None:
+                    missing.append((W, op, M))
+    assert not missing, missing
