@@ -371,6 +371,39 @@ elif mode == "prims":
     ctx.check("prims")
     ctx.finalize()
 
+elif mode == "bench_shapes":
+    # the shapes and tilings that ship: every fused op at the benchmark's LLM tensor-parallel shape (M = 8192,
+    # hidden 8192, FFN 28672 / W) with the tiling the chooser picks, against an fp32 golden computed on the GPUs
+    ctx = catcoc.init(heap_bytes=6 << 30)
+    W, M, H, F = world, 8192, 8192, 28672
+    kf = F // W
+    bf = torch.bfloat16
+    a, b = matmul_inputs(M, H, kf, rank, bf, dev, seed=1, b_std=0.02)
+    gold = ref.matmul_allreduce(a, b, out_dtype=torch.float32)
+    mag = pmag(a, b)
+    rows = M // W
+    sl = slice(rank * rows, (rank + 1) * rows)
+    check("bench_rs", catcoc.matmul_reduce_scatter(a, b), gold[sl], F, bf, mag[sl])
+    check("bench_ar", catcoc.matmul_allreduce(a, b), gold, F, bf, mag)
+    for name, t in (("pull", catcoc.TilingConfig(bn=256, cta_pair=2, pull=1, use_multicast=True)),
+                    ("push_tma", catcoc.TilingConfig(bn=256, cta_pair=2, pull=0, push_tma=1))):
+        check("bench_rs_" + name, catcoc.matmul_reduce_scatter(a, b, tiling=t), gold[sl], F, bf, mag[sl])
+        check("bench_ar_" + name, catcoc.matmul_allreduce(a, b, tiling=t), gold, F, bf, mag)
+    del gold, mag
+    x1, x2, s1, s2, bias = quant_inputs(M, H, kf, rank, dev, seed=3)
+    goldq = ref.quant_matmul_reduce_scatter(x1, x2, s1, s2, bias, out_dtype=torch.float32)
+    check("bench_quant", catcoc.quant_matmul_reduce_scatter(x1, x2, s1, s2, bias), goldq, 512, bf)
+    del x1, x2, goldq, a, b
+    torch.cuda.empty_cache()
+    a, b = matmul_inputs(M // W, kf, H, rank, bf, dev, seed=2, b_std=0.02)
+    golda, gath = ref.allgather_matmul(a, b, out_dtype=torch.float32)
+    for name, t in (("default", None), ("multicast", catcoc.TilingConfig(bn=256, cta_pair=2, use_multicast=True)),
+                    ("peer_stores", catcoc.TilingConfig(bn=256, cta_pair=2, use_multicast=False))):
+        o, g = catcoc.allgather_matmul(a, b, tiling=t)
+        check("bench_ag_" + name, o, golda, H, bf)
+        report("bench_ag_gathered_" + name, bool(torch.equal(g, gath)))
+    ctx.finalize()
+
 elif mode == "checked":
     # the fused ops under the bounds-checked build of the library (CATCOC_CHECKED=1 in the environment):
     # pull and push flavours, both tile flavours, ragged shapes, all-gather by multicast and by peer stores

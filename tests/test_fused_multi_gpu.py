@@ -61,6 +61,16 @@ def test_mixed_geometries_back_to_back(world, gpu_count):
     _run(world, "mixed", {"CATCOC_TIMEOUT_MS": "2000"}, timeout=600)
 
 
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_benchmark_shapes_match_goldens(world, gpu_count):
+    """Every fused op at the benchmark shape (M = 8192, hidden 8192, FFN 28672 / W) with the tiling the
+    chooser ships, plus the pull, TMA-push, multicast and peer-store variants, against fp32 goldens."""
+    if gpu_count < world:
+        pytest.skip("needs %d GPUs" % world)
+    cases = _run(world, "bench_shapes", {"CATCOC_TIMEOUT_MS": "3000"}, timeout=900)
+    assert len(cases) >= 13
+
+
 def test_fused_ops_on_plain_peer_stores_without_nvls(gpu_count):
     if gpu_count < 2:
         pytest.skip("needs 2 GPUs")
