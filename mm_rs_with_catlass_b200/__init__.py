@@ -26,6 +26,8 @@ from .ops.blas import (gemm, matmul_bias, matmul_add, optimized_matmul, batched_
 from .ops.mx import (mxf8_matmul, mxf8_matmul_reduce_scatter, quantize_mxf8, dequantize_mxf8,  # noqa: F401
                      pack_scales)
 
+from .ops.attention import flash_attention  # noqa: F401
+
 from .ops import torch_ops  # noqa: F401  (registers torch.ops.catcoc.*)
 
 __version__ = "0.1.0"

@@ -40,6 +40,7 @@ SOURCES = [
     "kernels/shmem_prims.cu",
     "kernels/no_alloc.cu",
     "kernels/blas_prims.cu",
+    "kernels/flash_attn.cu",
     "shmem/host.cu",
     "oracle/oracle.cpp",
 ]

@@ -158,6 +158,7 @@ def _declare(lib) -> None:
         "catcoc_splitk_reduce": (i32, [vp, i32, i64, i32, i32, vp, i64, i32, C.c_float, C.c_float, vp, i64, vp, vp]),
         "catcoc_gemv_workspace_floats": (i64, [i32, i32, i32]),
         "catcoc_gemv": (i32, [vp, i64, i32, i32, i32, i32, vp, vp, vp, C.c_float, C.c_float, vp, vp]),
+        "catcoc_flash_attention": (i32, [vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, C.c_float, vp, u64, vp]),
         "catcoc_matmul_noalloc": (i32, [vp, i64, vp, i64, vp, i64, i32, i32, i32, i32, i32, i32, i32, vp]),
         "catcoc_matmul_noalloc_status": (i32, [P(u32)]),
     }

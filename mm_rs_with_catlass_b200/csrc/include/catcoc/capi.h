@@ -251,6 +251,15 @@ int64_t catcoc_gemv_workspace_floats(int rows, int cols, int trans);
 int catcoc_gemv(const void* A, int64_t lda, int fmt, int rows, int cols, int trans, const void* x, void* y,
                 const void* y_in, float alpha, float beta, float* workspace, void* stream);
 
+/* ---- flash attention forward (csrc/kernels/flash_attn.cu) ----
+ * out[b, h, i, :] = softmax_j(scale * q[b, h, i, :] . k[b, g(h), j, :]) v[b, g(h), j, :] with q [B, Hq, Sq, D],
+ * k / v [B, Hk, Sk, D] and out [B, Hq, Sq, D], all contiguous fp16 or bf16 (fmt = CATCOC_FMT_*), D = 64 or 128,
+ * Hq a multiple of Hk (grouped-query heads share a key / value head). causal: key j is visible to query i when
+ * j <= i + (Sk - Sq). `status`: 8 device words as for the GEMM kernels. */
+int catcoc_flash_attention(const void* q, const void* k, const void* v, void* out, int B, int Hq, int Hk, int Sq,
+                           int Sk, int D, int fmt, int causal, float scale, uint32_t* status, uint64_t timeout_ns,
+                           void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1286,8 +1286,8 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
         uint8_t* dstp = (mcast ? p.gathered_mc : p.gathered[peer]) +
                         static_cast<int64_t>(parity) * p.gathered_parity_bytes +
                         (static_cast<int64_t>(p.rank) * gp.m + r0) * p.gathered_pitch + cb;
-        const int64_t dst_end = static_cast<int64_t>(parity) * p.gathered_parity_bytes +
-                                (static_cast<int64_t>(p.rank) * gp.m + r0 + nrows - 1) * p.gathered_pitch + cb + 16;
+        [[maybe_unused]] const int64_t dst_end = static_cast<int64_t>(parity) * p.gathered_parity_bytes +
+                                                 (static_cast<int64_t>(p.rank) * gp.m + r0 + nrows - 1) * p.gathered_pitch + cb + 16;
         if (col_ok && nrows > 0 && CATCOC_BOUND(p, SITE_GATHER_PUSH, dst_end, LIM_GATHERED)) {
           // 16 rows (8 KiB per warp) in flight per round trip: the copy is latency bound, which is
           // why several warps per CTA share it
@@ -1369,7 +1369,7 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
           const int total_units = rows_valid * upr;
           const int64_t src_row0 = (static_cast<int64_t>(ti.m0 + row0) * p.ldp + ti.n0) * 2;
           const int64_t dst_row0 = (static_cast<int64_t>(ti.m0 + row0 - (ar ? 0 : p.out_row_shift)) * p.ldc + ti.n0) * 2;
-          const int64_t row_span = static_cast<int64_t>(upr) * 16;
+          [[maybe_unused]] const int64_t row_span = static_cast<int64_t>(upr) * 16;
           const bool io_ok =
               CATCOC_BOUND(p, SITE_PART_REDUCE, static_cast<int64_t>(parity) * p.part_parity_bytes + src_row0 +
                                                     static_cast<int64_t>(rows_valid - 1) * p.ldp * 2 + row_span, LIM_PART) &&

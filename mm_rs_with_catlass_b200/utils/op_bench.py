@@ -53,6 +53,11 @@ def main(argv=None) -> int:
                          "files into the table the chooser loads")
     ap.add_argument("--hidden", type=int, default=DEFAULT_HIDDEN, help="N of the row-parallel ops, K of the all-gather op")
     ap.add_argument("--ffn", type=int, default=DEFAULT_FFN, help="split over the ranks: K_local = ffn / W")
+    ap.add_argument("--shapes-csv", default=None,
+                    help="rows M,K,N of un-sharded layers (the reference's shape files, e.g. "
+                         "tiling/shapes/reference_shapes.csv) instead of --ms / --hidden / --ffn: the row-parallel ops "
+                         "run [M, K / W] x [K / W, N], the all-gather op [M / W, N] x [N, K / W]; rows whose K or M do "
+                         "not divide by the world size are skipped")
     ap.add_argument("--trace", action="store_true",
                     help="after timing an op, run one more launch with the kernel's cycle counters on and print "
                          "them per CTA (FusedParams::trace in csrc/include/catcoc/params.h)")
@@ -111,10 +116,13 @@ def main(argv=None) -> int:
     variants = [v for v in args.variants.split(",") if v]
     base_cache = {}
     shape_of = {}
+    layer_of = {}
+    layer_now = [None]
 
     def record(op, M, fused_of, base_fn, flops_rank, link_bytes, peak=peak_tflops, shape=None, dtype=torch.bfloat16):
         """``fused_of(tiling)`` returns the callable of the fused op with that tiling."""
         shape_of[(op, M)] = shape
+        layer_of[(op, M)] = layer_now[0]
         for variant in variants:
             tiling = variant_tiling(op, *shape, dtype, variant) if shape else None
             if tiling is None and shape and args.table:
@@ -133,14 +141,14 @@ def main(argv=None) -> int:
                                   "error": str(err)[:300] if err is not None else "failed on another rank"}), flush=True)
                 ctx.reset_after_error()
                 continue
-            if (op, M) not in base_cache:
-                base_cache[(op, M)] = timing.time_steps(base_fn, args.iters, args.warmup, dev)
-            t_b = base_cache[(op, M)]
+            if (op, M, layer_now[0]) not in base_cache:
+                base_cache[(op, M, layer_now[0])] = timing.time_steps(base_fn, args.iters, args.warmup, dev)
+            t_b = base_cache[(op, M, layer_now[0])]
             one_record(op, M, variant, tiling, fused_fn, t_f, t_b, flops_rank, link_bytes, peak)
 
     def one_record(op, M, variant, tiling, fused_fn, t_f, t_b, flops_rank, link_bytes, peak):
         roof_ms = max(flops_rank / (peak * 1e12), link_bytes / (LINK_GBS * 1e9)) * 1e3
-        row = {"op": op, "W": W, "M": M, "variant": variant, "fused_us": 1e3 * t_f, "cublas_nccl_us": 1e3 * t_b,
+        row = {"op": op, "W": W, "M": M, "N": layer_now[0][0], "K_total": layer_now[0][1], "variant": variant, "fused_us": 1e3 * t_f, "cublas_nccl_us": 1e3 * t_b,
                "speedup": t_b / t_f, "tflops_per_gpu": flops_rank / (t_f * 1e-3) / 1e12, "roofline_us": 1e3 * roof_ms,
                "roofline_frac": roof_ms / t_f, "peak_source": peak_src,
                "fallbacks": dict(ctx.fallbacks)}
@@ -166,9 +174,16 @@ def main(argv=None) -> int:
                 TilingTable.append_row(args.table, Row(op, m_, k_, n_, 0, 0, "int8" if "quant" in op else "bf16", W,
                                                        tiling, 1e3 * t_f, 1e3 * t_b))
 
-    kf = FFN // W
-    for M in [int(x) for x in args.ms.split(",")]:
-        if "ar" in args.ops and M <= 8192:
+    if args.shapes_csv:
+        from mm_rs_with_catlass_b200.tiling.tune import read_shapes
+        layers = [(m, k, n) for (m, k, n, ta, tb) in read_shapes(args.shapes_csv)
+                  if k % W == 0 and m % W == 0 and (k // W) % 8 == 0 and n % 8 == 0 and m >= 128]
+    else:
+        layers = [(int(x), FFN, HIDDEN) for x in args.ms.split(",")]
+    for (M, FFN, HIDDEN) in layers:
+        kf = FFN // W
+        layer_now[0] = (HIDDEN, FFN)
+        if "ar" in args.ops and (M <= 8192 or args.shapes_csv):
             a, b = matmul_inputs(M, HIDDEN, kf, rank, torch.bfloat16, dev, seed=1, b_std=0.02)
             out = torch.empty((M, HIDDEN), dtype=torch.bfloat16, device=dev)
             S = M * HIDDEN * 2
