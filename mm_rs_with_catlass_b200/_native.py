@@ -64,7 +64,7 @@ class OpArgs(C.Structure):
         ("gathered", C.c_void_p * MAX_WORLD),
         ("gathered_parity_bytes", C.c_int64),
         ("gflags", C.c_void_p * MAX_WORLD),
-        ("ag_m", C.c_int), ("ag_ld", C.c_int),
+        ("ag_m", C.c_int), ("ag_ld", C.c_int), ("ag_raw", C.c_int),
         ("sfa", C.c_void_p), ("sfb", C.c_void_p), ("sf_k_blocks", C.c_int),
         ("scale_m", C.c_void_p), ("scale_n", C.c_void_p), ("bias", C.c_void_p),
         ("affine", C.c_int), ("alpha", C.c_float), ("beta", C.c_float),

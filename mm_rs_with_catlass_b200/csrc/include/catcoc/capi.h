@@ -85,6 +85,9 @@ typedef struct CatcocOpArgs {
   uint32_t* gflags[CATCOC_MAX_WORLD];
   int ag_m;                                /* all-gather: rows of one shard              */
   int ag_ld;                               /* all-gather: row pitch (elements) of the gathered buffer, >= K, 16-byte multiple */
+  int ag_raw;                              /* all-gather: 1 = `a` may have any alignment and any pitch >= K (it is fetched by
+                                              the communication warps, never by TMA); then W == 1 is allowed too: the padding
+                                              prologue of a local GEMM (`gathered[0]` is the padded copy, an output)          */
 
   /* block-scaled fp8 (CATCOC_IN_MX*): scale factors packed in 512-byte blocks of 128 rows x 4
    * K-blocks (row r, K-block s at (r % 32) * 16 + (r / 32) * 4 + s), block (row_tile, k128) at

@@ -204,6 +204,26 @@ CATCOC_DEVICE float activate(float x, int act) {
   return x;
 }
 
+// 16 bytes from an address that is only `vec`-byte aligned (vec = 8, 4 or 2), of which the first
+// `valid` (even, possibly <= 0) hold data; the rest reads as zero and is never touched in memory.
+CATCOC_DEVICE uint4 load16_pieces(const uint8_t* src, int vec, int valid) {
+  uint32_t w[4] = {0u, 0u, 0u, 0u};
+  int b = 0;
+  if (vec >= 8) {
+    for (; b + 8 <= valid; b += 8) {
+      const uint2 v = *reinterpret_cast<const uint2*>(src + b);
+      w[b >> 2] = v.x;
+      w[(b >> 2) + 1] = v.y;
+    }
+  }
+  if (vec >= 4) {
+    for (; b + 4 <= valid; b += 4) w[b >> 2] = *reinterpret_cast<const uint32_t*>(src + b);
+  }
+  for (; b + 2 <= valid; b += 2)
+    w[b >> 2] |= static_cast<uint32_t>(*reinterpret_cast<const uint16_t*>(src + b)) << ((b & 2) * 8);
+  return make_uint4(w[0], w[1], w[2], w[3]);
+}
+
 // ---- epilogue staging -----------------------------------------------------------------
 // Each epilogue warp owns a 32 x 128 B staging area. Thread `lane` (one tile row) writes
 // 16-byte units at a position XOR-swizzled with the row so that neither the row-wise writes
@@ -320,7 +340,8 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
   const int kps = (!CTA2 && BN <= 64) ? 2 : kKPS;
   const int sub_bytes = (kps != kKPS) ? (kABytes + BN * 128) : kSubBytes;
   const int num_kb = ceil_div(p.K, p.bk * kps);   // pipeline stages per tile
-  const bool fused = (p.mode != MODE_LOCAL) && (p.W > 1);
+  // (a raw-shard all-gather runs on one rank too: the padding prologue of a local GEMM)
+  const bool fused = (p.mode != MODE_LOCAL) && (p.W > 1 || (p.mode == MODE_AG && p.ag_raw != 0));
   const bool pull = kPull && fused && (p.pull != 0) && (p.mode == MODE_RS || p.mode == MODE_AR);
   // Pair flavour: `sub` is this CTA's half of the 256-row tile, work is dealt out per pair.
   const int sub = CTA2 ? static_cast<int>(ptx::cluster_ctarank()) : 0;
@@ -350,7 +371,8 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
     tail->abort_flag = 0;
     // A fused launch that finds an earlier failure latched in the status block does nothing: the
     // ranks' epochs no longer agree, so every wait would only run into its time limit again.
-    tail->dead = (p.mode != MODE_LOCAL && p.W > 1 && ptx::ld_relaxed_sys_u32(p.status) != 0u) ? 1u : 0u;
+    tail->dead = (p.mode != MODE_LOCAL && (p.W > 1 || (p.mode == MODE_AG && p.ag_raw != 0)) &&
+                  ptx::ld_relaxed_sys_u32(p.status) != 0u) ? 1u : 0u;
     ptx::mbar_fence_init();
     ptx::prefetch_tmap(&p.tm_a);
     ptx::prefetch_tmap(&p.tm_b);
@@ -403,8 +425,8 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
         a_row -= ti.seg * p.g_a_row_back;
         a_k_off = ti.seg * p.g_a_k;
       }
-      if (p.mode == MODE_AG && p.W > 1) {
-        if (ti.seg == p.rank) {
+      if (p.mode == MODE_AG && fused) {
+        if (ti.seg == p.rank && p.ag_raw == 0) {
           a_row = ti.mi * sched.BM + sub * kBM;  // row inside the local shard
         } else {
           // Every K-slice of this row chunk of source `seg` must have landed here. The stamps
@@ -438,7 +460,7 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
         const int tn = t + num_workers;
         if (tn < sched.total_tiles) {
           const TileInfo tin = get_tile(sched, tn);
-          if (tin.seg != p.rank) {
+          if (tin.seg != p.rank || p.ag_raw != 0) {
             const uint32_t* fl = p.gflags[p.rank];
             bool okl = true;
             for (int s = lane; s < p.gp.n_slices; s += 32) {
@@ -1281,7 +1303,12 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
         const int r0 = chunk * gp.chunk_rows;
         const int nrows = min(gp.chunk_rows, gp.m - r0);
         const int64_t cb = static_cast<int64_t>(slice) * slice_bytes + lane * 16;
+        // bytes of this lane's 16-byte unit that hold shard data (a raw shard may end inside the unit; the
+        // rest of a gathered row is padding that nobody reads, zero-filled here)
+        const int64_t src_row_bytes = p.ag_raw ? p.a_row_bytes : row_bytes;
+        const int valid = static_cast<int>(min(static_cast<int64_t>(16), src_row_bytes - cb));
         const bool col_ok = (lane * 16 < slice_bytes) && (cb + 16 <= row_bytes);
+        const bool plain = (p.ag_raw == 0) || (p.a_vec == 16 && valid == 16);
         const uint8_t* src = p.a_local + static_cast<int64_t>(r0) * p.a_local_pitch + cb;
         uint8_t* dstp = (mcast ? p.gathered_mc : p.gathered[peer]) +
                         static_cast<int64_t>(parity) * p.gathered_parity_bytes +
@@ -1295,8 +1322,10 @@ fused_gemm_kernel(const __grid_constant__ FusedParams p) {
             uint4 buf[16];
 #pragma unroll
             for (int i = 0; i < 16; ++i)
-              if (r + i < nrows)
-                buf[i] = ptx::ld_global_nc_v4(src + static_cast<int64_t>(r + i) * p.a_local_pitch);
+              if (r + i < nrows) {
+                const uint8_t* sp = src + static_cast<int64_t>(r + i) * p.a_local_pitch;
+                buf[i] = plain ? ptx::ld_global_nc_v4(sp) : load16_pieces(sp, p.a_vec, valid);
+              }
             if (mcast) {
 #pragma unroll
               for (int i = 0; i < 16; ++i)

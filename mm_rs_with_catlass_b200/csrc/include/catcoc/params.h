@@ -139,6 +139,14 @@ struct alignas(64) FusedParams {
   int64_t gathered_parity_bytes;
   int64_t gathered_pitch;        // bytes per row of the gathered buffer
   uint32_t* gflags[kMaxWorld];   // per-rank chunk stamps
+  // Raw shard (ag_raw != 0): the shard may start at any element and have any row pitch, so TMA never reads
+  // it. The communication warps fetch it in units of a_vec bytes (the largest power of two that divides
+  // base address and pitch) and also copy this rank's own rows into its gathered buffer, from where the
+  // producer loads the local tiles like the remote ones. With W == 1 this is the padding prologue of a
+  // local GEMM whose A has a pitch TMA cannot take: pad and product in one launch.
+  int ag_raw;
+  int a_vec;                     // 16, 8, 4 or 2
+  int64_t a_row_bytes;           // valid bytes per shard row (K elements)
   uint8_t* gathered_mc;          // multicast aliases: one multimem.st lands a piece of the shard (and its
   uint32_t* gflags_mc;           //   stamp) on every rank; null => one store per peer
   GatherPlan gp;

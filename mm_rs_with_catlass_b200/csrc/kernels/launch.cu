@@ -194,7 +194,7 @@ static bool wants_ag_multicast(const CatcocOpArgs& a) {
 }
 
 static TileSched build_sched(const CatcocOpArgs& a, int bm, int bn, int seg_dim) {
-  const bool fused = a.mode != CATCOC_MODE_LOCAL && a.W > 1;
+  const bool fused = a.mode != CATCOC_MODE_LOCAL && (a.W > 1 || (a.mode == CATCOC_MODE_AG && a.ag_raw != 0));
   const int W = fused ? a.W : 1;
   int first = 0;
   if (fused) first = (a.mode == CATCOC_MODE_AG) ? a.rank : (a.rank + 1) % W;
@@ -308,8 +308,9 @@ int catcoc_build_params(const CatcocOpArgs* args, FusedParams* p, int* kind_out,
     set_error("bad mode %d", a.mode);
     return CATCOC_E_BAD_ARG;
   }
-  const bool fused = a.mode != CATCOC_MODE_LOCAL && a.W > 1;
-  if (fused && (a.W > kMaxWorld || a.rank < 0 || a.rank >= a.W)) {
+  const bool ag_raw = (a.mode == CATCOC_MODE_AG) && (a.ag_raw != 0);
+  const bool fused = a.mode != CATCOC_MODE_LOCAL && (a.W > 1 || ag_raw);
+  if (fused && (a.W > kMaxWorld || a.W < 1 || a.rank < 0 || a.rank >= a.W)) {
     set_error("bad rank/world %d/%d", a.rank, a.W);
     return CATCOC_E_BAD_ARG;
   }
@@ -427,11 +428,16 @@ int catcoc_build_params(const CatcocOpArgs* args, FusedParams* p, int* kind_out,
   if (a.mode == CATCOC_MODE_AG && fused) {
     if (a.trans_a) { set_error("allgather_matmul supports trans_a=False only"); return CATCOC_E_UNSUPPORTED; }
     if (a.ag_m <= 0 || a.ag_m * a.W != a.M) { set_error("allgather: M must be W * m"); return CATCOC_E_BAD_ARG; }
-    rc = encode_2d(&p->tm_a, a.a, rf.elt, rf.dt, a.ag_m, a.K, a.lda, rf.bk, kBM);
-    if (rc != 0) return rc;
+    if (!ag_raw) {
+      rc = encode_2d(&p->tm_a, a.a, rf.elt, rf.dt, a.ag_m, a.K, a.lda, rf.bk, kBM);
+      if (rc != 0) return rc;
+    } else if (a.a == nullptr || a.lda < a.K || (reinterpret_cast<uintptr_t>(a.a) % rf.elt) != 0) {
+      set_error("allgather: a raw shard needs an element-aligned base and a pitch of at least K elements");
+      return CATCOC_E_BAD_ARG;
+    }
     const int ag_ld = a.ag_ld > 0 ? a.ag_ld : a.K;
     const int64_t gpitch = static_cast<int64_t>(ag_ld) * rf.elt;
-    if ((gpitch & 15) != 0 || ag_ld < a.K || a.lda < ag_ld) {
+    if ((gpitch & 15) != 0 || ag_ld < a.K || (!ag_raw && a.lda < ag_ld)) {
       set_error("allgather: gathered pitch must be >= K, <= lda and a multiple of 16 bytes (K=%d ag_ld=%d lda=%lld)",
                 a.K, ag_ld, static_cast<long long>(a.lda));
       return CATCOC_E_ALIGNMENT;
@@ -443,7 +449,15 @@ int catcoc_build_params(const CatcocOpArgs* args, FusedParams* p, int* kind_out,
     }
     p->a_local = static_cast<const uint8_t*>(a.a);
     p->a_local_pitch = a.lda * rf.elt;
-    if ((p->a_local_pitch & 15) != 0) { set_error("allgather: A pitch must be a multiple of 16 bytes"); return CATCOC_E_ALIGNMENT; }
+    if (!ag_raw && (p->a_local_pitch & 15) != 0) { set_error("allgather: A pitch must be a multiple of 16 bytes"); return CATCOC_E_ALIGNMENT; }
+    if (ag_raw) {
+      // widest load that both the base address and the pitch allow
+      const uint64_t bits = reinterpret_cast<uintptr_t>(a.a) | static_cast<uint64_t>(p->a_local_pitch) | 16u;
+      p->ag_raw = 1;
+      p->a_vec = static_cast<int>(bits & (~bits + 1));       // lowest set bit: 16, 8, 4 or 2
+      if (p->a_vec < 2) { set_error("allgather: a raw shard must be 2-byte aligned"); return CATCOC_E_ALIGNMENT; }
+      p->a_row_bytes = static_cast<int64_t>(a.K) * rf.elt;
+    }
     p->gathered_parity_bytes = a.gathered_parity_bytes;
     p->gathered_pitch = gpitch;
     if (wants_ag_multicast(a)) {
@@ -666,6 +680,7 @@ int catcoc_build_params(const CatcocOpArgs* args, FusedParams* p, int* kind_out,
     tiles_bound = static_cast<int>(mt * nt > (1 << 30) ? (1 << 30) : mt * nt);
   }
   if (!(fused && a.mode == CATCOC_MODE_AG)) grid = imin(grid, tiles_bound * per_tile);
+  // (an all-gather keeps every CTA: their communication warps share the copy of the shard)
   if (pair) {
     grid = imin(grid, 2 * max_active_pairs(rf.kind));
     grid &= ~1;

@@ -458,11 +458,15 @@ def allgather_matmul(a_shard: torch.Tensor, b: torch.Tensor, *, trans_b: bool = 
         # shard is copied row by row with that width, so it needs a TMA-legal pitch itself.
         per16 = 16 // elt
         ag_ld = (k + per16 - 1) // per16 * per16
+        # A shard whose base or pitch TMA cannot take is not copied first: the communication warps fetch
+        # it with narrower loads and the kernel reads the local rows from the gathered buffer as well
         a_src = a_shard
-        if a_shard.stride(-1) != 1 or (a_shard.stride(0) * elt) % 16 or a_shard.data_ptr() % 16 \
-                or a_shard.stride(0) < ag_ld:
-            a_src = cm.pad_rows(a_shard)
+        raw = False
+        if a_shard.stride(-1) != 1 or a_shard.stride(0) < k or a_shard.data_ptr() % elt:
+            a_src = a_shard.contiguous()
             ctx.counters["pad_copies"] += 1
+        if (a_src.stride(0) * elt) % 16 or a_src.data_ptr() % 16 or a_src.stride(0) < ag_ld:
+            raw = True
         ob = cm.as_operand(b, trans_b)
         args = N.OpArgs()
         args.mode = N.MODE_AG
@@ -477,6 +481,7 @@ def allgather_matmul(a_shard: torch.Tensor, b: torch.Tensor, *, trans_b: bool = 
         args.cta_counter = ctx.launch_state.data_ptr() + 4
         args.status = ctx.status.data_ptr()
         args.ag_m, args.ag_ld = m, ag_ld
+        args.ag_raw = int(raw)
         args.act = cm.act_code(activation)
         gbuf, parity_bytes = _data_region(ctx, "gathered", W * m * ag_ld * elt)
         gfl = ctx.stamps(("gflags", m, ag_ld, W, elt, _pair(t)), int(lib.catcoc_gather_flag_words(m, ag_ld, W, elt)))

@@ -20,6 +20,80 @@ from ..tiling.config import TilingConfig
 from . import _common as cm
 
 
+def _wants_pad_prologue(a: torch.Tensor) -> bool:
+    """A 2-D operand stored row-major with K contiguous whose base or pitch is not 16-byte aligned
+    (what ``_common.as_operand`` would otherwise copy into a fresh padded buffer first)."""
+    elt = a.element_size()
+    if a.dim() != 2 or a.stride(-1) != 1 or a.shape[0] < 1 or a.stride(0) < a.shape[1]:
+        return False
+    if a.data_ptr() % elt or elt > 2:
+        return False
+    bits = a.data_ptr() | (a.stride(0) * elt)
+    if bits % 2:
+        return False                       # 1-byte aligned int8 rows: narrower than the kernel's smallest load
+    return bool((a.stride(0) * elt) % 16 or a.data_ptr() % 16)
+
+
+class _PadState:
+    """Per-device workspace of the padding prologue: the padded copy of A (two parity halves, as in
+    the all-gather), its chunk stamps per geometry, and the launch counter the stamps are compared
+    with. Plain device tensors: nothing here is shared with other ranks."""
+
+    def __init__(self, device: torch.device):
+        self.device = device
+        self.state = torch.zeros(2, dtype=torch.int32, device=device)    # [0] launches completed, [1] CTA counter
+        self.buf = None
+        self.half = 0
+        self.flags = {}
+        self.cur = None
+
+    def attach(self, a: torch.Tensor, m: int, k: int) -> "_PadState":
+        elt = a.element_size()
+        per16 = 16 // elt
+        ld = (k + per16 - 1) // per16 * per16
+        half = (m * ld * elt + 1023) // 1024 * 1024
+        if self.buf is None or self.half < half:
+            self.buf = torch.empty(2 * half, dtype=torch.uint8, device=self.device)
+            self.half = half
+            _plans.clear()                 # plans hold the old workspace address
+        key = (m, ld, elt)
+        fl = self.flags.get(key)
+        if fl is None:
+            words = int(N.lib().catcoc_gather_flag_words(m, ld, 1, elt))
+            fl = torch.zeros(max(1, words), dtype=torch.int32, device=self.device)
+            if len(self.flags) >= 64:
+                self.flags.clear()
+                _plans.clear()
+            self.flags[key] = fl
+        self.cur = (m, ld, fl)
+        return self
+
+    def fill(self, args) -> None:
+        m, ld, fl = self.cur
+        args.mode = N.MODE_AG
+        args.rank, args.W = 0, 1
+        args.ag_m, args.ag_ld, args.ag_raw = m, ld, 1
+        args.gathered[0] = self.buf.data_ptr()
+        args.gathered_parity_bytes = self.half
+        args.gflags[0] = fl.data_ptr()
+        args.epoch_ptr = self.state.data_ptr()
+        args.cta_counter = self.state.data_ptr() + 4
+        args.limit[N.LIM_GATHERED] = self.buf.numel()
+        args.limit[N.LIM_GFLAGS] = fl.numel()
+
+
+_pad_states: dict = {}
+
+
+def _pad_state(device: torch.device) -> _PadState:
+    key = device.index or 0
+    st = _pad_states.get(key)
+    if st is None:
+        st = _PadState(device)
+        _pad_states[key] = st
+    return st
+
+
 # Launch plans of :func:`matmul`: argument blocks keyed by where the operands live and how they
 # are laid out. A plan holds addresses, never tensors, so it keeps no memory alive; an entry can
 # only be hit again by tensors at the same addresses with the same layout, for which the block is
@@ -101,7 +175,16 @@ def matmul(a: torch.Tensor, b: torch.Tensor, *, trans_a: bool = False, trans_b: 
         from ..tiling.chooser import choose
         tiling = choose("matmul", m, n, k, 1, a.dtype)
     with torch.cuda.device(dev):
-        oa = cm.as_operand(a, trans_a)
+        # An A stored [M, K] whose base or row pitch TMA cannot take is padded INSIDE the launch: the
+        # kernel's communication warps copy it row chunk by row chunk into a 16-byte-pitched workspace and
+        # the TMA producer follows chunk by chunk (the one-rank form of the all-gather kernel). No extra
+        # launch, no allocation per call, and the call can be planned like any other.
+        pad = None
+        if _group is None and not trans_a and _wants_pad_prologue(a):
+            pad = _pad_state(dev).attach(a, m, k)
+            oa = cm.Operand(a, a.data_ptr(), a.stride(0), False)
+        else:
+            oa = cm.as_operand(a, trans_a)
         ob = cm.as_operand(b, trans_b)
         args = N.OpArgs()
         args.mode = N.MODE_LOCAL
@@ -141,6 +224,8 @@ def matmul(a: torch.Tensor, b: torch.Tensor, *, trans_a: bool = False, trans_b: 
         args.status = cm.local_status(dev).data_ptr()
         if trace is not None:  # int64[16] device tensor: per-role cycle counters (see params.h)
             args.trace = trace.data_ptr()
+        if pad is not None:
+            pad.fill(args)
         cm.launch(args, dev)
         if key is not None and not oa.copied and not ob.copied:
             if len(_plans) >= _MAX_PLANS:

@@ -207,8 +207,8 @@ def test_flagship_block_world1(catcoc, device):
 
 def test_launch_plans_follow_the_data_not_the_first_call(catcoc, device):
     """A repeated call reuses its argument block (a launch plan): new contents at the same
-    addresses must give new results, a new output must be written, and operands that need a
-    padded copy are rebuilt on every call."""
+    addresses must give new results, a new output must be written, and an operand that needs a
+    padded copy is re-read on every call."""
     from mm_rs_with_catlass_b200.ops import gemm as G
     from mm_rs_with_catlass_b200.utils.verify import assert_close
     a = torch.randn(256, 192, device=device).bfloat16()
@@ -227,7 +227,8 @@ def test_launch_plans_follow_the_data_not_the_first_call(catcoc, device):
     assert catcoc.matmul(a, b, out=out) is out
     _check_status(device, "plan hit with out")
     assert_close(out, a.float() @ b.float(), k=192)
-    # a pitch TMA cannot address goes through the pad kernel: never planned, always current
+    # an A whose base TMA cannot address is padded inside the launch (from the caller's memory, on every
+    # call): planned like any other operand, and still always current
     big = torch.randn(256, 200, device=device).bfloat16()
     av = big[:, 3:195]
     before = len(G._plans)
@@ -235,8 +236,19 @@ def test_launch_plans_follow_the_data_not_the_first_call(catcoc, device):
     big.mul_(2.0)
     r2 = catcoc.matmul(av, b)
     _check_status(device, "padded operand")
-    assert len(G._plans) == before
+    assert len(G._plans) == before + 1
     assert_close(r2, av.float() @ b.float(), k=192)
+    assert not torch.equal(r1, r2)
+    # a B that needs a padded copy still goes through the pad kernel: never planned, always current
+    bbig = torch.randn(192, 330, device=device).bfloat16()
+    bv = bbig[:, 5:325]
+    before = len(G._plans)
+    r1 = catcoc.matmul(a, bv)
+    bbig.mul_(2.0)
+    r2 = catcoc.matmul(a, bv)
+    _check_status(device, "padded B")
+    assert len(G._plans) == before
+    assert_close(r2, a.float() @ bv.float(), k=192)
     assert not torch.equal(r1, r2)
 
 
@@ -254,3 +266,30 @@ def test_activation_in_the_epilogue(catcoc, act, pair):
     assert_close(out, gold, k=256, dtype=torch.bfloat16, what="matmul + " + act)
     with pytest.raises(ValueError):
         catcoc.matmul(a, b, activation="tanh")
+
+
+def test_unaligned_a_is_padded_inside_the_launch(catcoc):
+    """An A whose row pitch (or base) is not a multiple of 16 bytes is padded by the kernel's own
+    communication warps while the product already runs: no padded copy is made beforehand, the
+    call is planned, and repeated calls (alternating workspace halves) stay correct."""
+    from mm_rs_with_catlass_b200.ops import gemm as G
+    from mm_rs_with_catlass_b200.utils.verify import assert_close
+    dev = torch.device("cuda:0")
+    for (m, n, k, off) in [(300, 256, 6148 // 4, 0), (513, 136, 250, 0), (129, 64, 72, 1), (64, 512, 1030, 3)]:
+        storage = torch.randn(m * k + 8, device=dev).to(torch.bfloat16)
+        a = storage[off:off + m * k].view(m, k)          # `off` elements into the storage: 2-byte aligned base
+        b = (torch.randn(k, n, device=dev) * 0.1).to(torch.bfloat16)
+        assert G._wants_pad_prologue(a)
+        plans_before = len(G._plans)
+        for rep in range(3):
+            out = catcoc.matmul(a, b)
+            assert_close(out, a.float() @ b.float(), k=k, dtype=torch.bfloat16, what="pad prologue %dx%dx%d" % (m, n, k))
+        assert len(G._plans) == plans_before + 1          # planned once, hit afterwards
+    _check_status(dev, "pad prologue")
+    # with scales (int8) the same path feeds the quantised epilogue
+    x1 = torch.randint(-127, 128, (200, 300), device=dev, dtype=torch.int32).to(torch.int8)   # 300-byte rows
+    x2 = torch.randint(-127, 128, (300, 256), device=dev, dtype=torch.int32).to(torch.int8)
+    assert G._wants_pad_prologue(x1)
+    out = catcoc.matmul(x1, x2)
+    assert torch.equal(out.cpu().long(), x1.cpu().long() @ x2.cpu().long())
+    _check_status(dev, "pad prologue int8")
