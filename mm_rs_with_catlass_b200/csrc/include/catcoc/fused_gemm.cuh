@@ -4,13 +4,19 @@
 //                                (all-gather: waits for the peers' chunk stamps first)
 //   warp 1      MMA issuer     : one elected lane issues tcgen05.mma into a double-buffered TMEM
 //                                accumulator, tcgen05.commit frees smem stages / publishes tiles
-//   warps 2..5  epilogue       : tcgen05.ld -> convert -> smem staging -> coalesced 16 B stores
-//                                to local memory, to a peer's staging slab (NVLink P2P) or to
-//                                every rank's output (P2P or multimem.st); owner tiles fold the
-//                                peers' partials into the fp32 / int32 accumulator first
+//   warps 2..5  epilogue       : tcgen05.ld -> convert (bias / dequant / alpha, beta / activation in the
+//                                fuller variants) -> smem staging -> one TMA store per window for local
+//                                outputs, coalesced 16 B stores to a peer's staging slab (NVLink P2P) or to
+//                                every rank's output (P2P or multimem.st); in the push flavour owner tiles
+//                                fold the peers' partials into the fp32 / int32 accumulator first, in the
+//                                pull flavour every tile is stored locally and its owner is stamped
 //   warp 6      TMA producer B : K-slices of B into the same ring (one warp cannot issue both
 //                                operands' copies fast enough)
-//   warp 7      communication  : all-gather only: push this rank's A shard to the peers
+//   warps 7..11 (384-thread variants; warp 7 alone in the 256-thread ones)
+//               communication  : all-gather: send this rank's A shard, peer by peer or once by multimem.st
+//                                (raw shards of any pitch; with one rank this is the padding prologue);
+//               reducers       : pull flavour: wait for a tile's W stamps, read the sum of all ranks' partials
+//                                through the switch (multimem.ld_reduce), store it or broadcast it + done stamp
 //
 // The collective is expressed inside the tile loop (see sched.h for the visiting order), so
 // transfers overlap the tensor-core work tile by tile and no NCCL call is involved.

@@ -1,10 +1,11 @@
 """Flash attention forward on the library's own tcgen05 kernel (``csrc/kernels/flash_attn.cu``).
 
-One CTA per 128 query rows of one (batch, head): ``S = Q K^T`` and ``O += P V`` run on the
-tensor cores with both accumulators in TMEM, the softmax warps keep the running row maximum
-and sum, write ``P`` back as the operand of the second product and rescale ``O`` in TMEM when
-the maximum moves (online softmax). K and V stream through a two-stage TMA ring; the scores of
-block ``j + 1`` are issued right behind ``P V`` of block ``j``.
+One CTA per 256 query rows (two tiles of 128) of one (batch, head): ``S = Q K^T`` and
+``O += P V`` run on the tensor cores with all four accumulators in TMEM. The softmax warps of a
+tile read its scores with ``tcgen05.ld``, keep the row maximum and sum, write ``P`` back over the
+scores (``tcgen05.st``) where the second product reads it as its TMEM operand, and rescale ``O``
+in TMEM only when the maximum moved by more than 2^8 (lazy online softmax). While one tile is in
+its softmax the tensor core runs the other tile's products. K and V stream through one TMA ring.
 
 The reference carries the same computation as vendored template kernels for its own
 accelerator (3rdparty/catlass/include/catlass/gemm/block/block_mmad_fa_qk.hpp and
@@ -57,6 +58,8 @@ def flash_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, causal
         raise ValueError("out must be a contiguous tensor shaped like q")
     if scale is None:
         scale = 1.0 / math.sqrt(d)
+    if not scale > 0.0:
+        raise ValueError("the softmax scale must be positive")
     with torch.cuda.device(dev):
         stream = torch.cuda.current_stream(dev).cuda_stream
         N.check(N.lib().catcoc_flash_attention(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), b, hq, hk, sq,
