@@ -27,6 +27,7 @@ from .ops.mx import (mxf8_matmul, mxf8_matmul_reduce_scatter, quantize_mxf8, deq
                      pack_scales)
 
 from .ops.attention import flash_attention  # noqa: F401
+from .ops.mla import mla_decode  # noqa: F401
 
 from .ops import torch_ops  # noqa: F401  (registers torch.ops.catcoc.*)
 

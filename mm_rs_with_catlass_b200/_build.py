@@ -41,6 +41,7 @@ SOURCES = [
     "kernels/no_alloc.cu",
     "kernels/blas_prims.cu",
     "kernels/flash_attn.cu",
+    "kernels/mla_decode.cu",
     "shmem/host.cu",
     "oracle/oracle.cpp",
 ]

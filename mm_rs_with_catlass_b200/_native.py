@@ -159,6 +159,8 @@ def _declare(lib) -> None:
         "catcoc_gemv_workspace_floats": (i64, [i32, i32, i32]),
         "catcoc_gemv": (i32, [vp, i64, i32, i32, i32, i32, vp, vp, vp, C.c_float, C.c_float, vp, vp]),
         "catcoc_flash_attention": (i32, [vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, C.c_float, vp, u64, vp]),
+        "catcoc_mla_workspace_bytes": (i64, [i32, i32, i32, i32]),
+        "catcoc_mla_decode": (i32, [vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, C.c_float, i32, vp, u64, vp]),
         "catcoc_matmul_noalloc": (i32, [vp, i64, vp, i64, vp, i64, i32, i32, i32, i32, i32, i32, i32, vp]),
         "catcoc_matmul_noalloc_status": (i32, [P(u32)]),
     }

@@ -263,6 +263,18 @@ int catcoc_flash_attention(const void* q, const void* k, const void* v, void* ou
                            int Sk, int D, int fmt, int causal, float scale, uint32_t* status, uint64_t timeout_ns,
                            void* stream);
 
+/* ---- multi-head latent attention, decode step over a paged cache (csrc/kernels/mla_decode.cu) ----
+ * q_nope [T, H, 512], q_rope [T, H, 64] (T = B * q_len new tokens, q_len 1..4), latent cache [num_pages, 128, 512],
+ * rotary cache [num_pages, 128, 64], block_table [B, max_pages] and kv_lens [B] (device int32), out [T, H, 512]; all
+ * contiguous, fp16 or bf16. Keys are [latent, rotary] (576 wide), values the latent. causal: new token t does not see
+ * the new tokens behind it. `splits` slices per sequence (flash decoding); more than one needs `workspace` of
+ * catcoc_mla_workspace_bytes(...) bytes. `status`: 8 device words as for the GEMM kernels. */
+int64_t catcoc_mla_workspace_bytes(int B, int q_len, int H, int splits);
+int catcoc_mla_decode(const void* q_nope, const void* q_rope, const void* ckv, const void* krope, const int* block_table,
+                      const int* kv_lens, void* out, void* workspace, int B, int q_len, int H, int num_pages,
+                      int max_pages, int fmt, int causal, float scale, int splits, uint32_t* status,
+                      uint64_t timeout_ns, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
