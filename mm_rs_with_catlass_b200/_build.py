@@ -40,6 +40,7 @@ SOURCES = [
     "kernels/shmem_prims.cu",
     "kernels/no_alloc.cu",
     "kernels/blas_prims.cu",
+    "kernels/small_allreduce.cu",
     "kernels/flash_attn.cu",
     "kernels/mla_decode.cu",
     "shmem/host.cu",

@@ -254,6 +254,17 @@ int64_t catcoc_gemv_workspace_floats(int rows, int cols, int trans);
 int catcoc_gemv(const void* A, int64_t lda, int fmt, int rows, int cols, int trans, const void* x, void* y,
                 const void* y_in, float alpha, float beta, float* workspace, void* stream);
 
+/* ---- split-K product + one-shot all-reduce (csrc/kernels/small_allreduce.cu) ----
+ * out[rows, cols] (fp16 / bf16, pitch ldc) = sum over ranks of round(sum over `slices` fp32 planes of this rank). The
+ * rounded local sum goes to heap offset part_off (the parity half of this launch's epoch, rows * cols * 2 bytes), the
+ * stamps to catcoc_splitk_allreduce_flag_words(...) words at flags_off (zeroed once, never reset). cols and ldc must be
+ * multiples of 8. epoch_ptr / cta_counter / status: the launch bookkeeping of the fused kernels (CatcocOpArgs). */
+int64_t catcoc_splitk_allreduce_flag_words(int rows, int cols, int W);
+int catcoc_splitk_allreduce(const CatcocShmemCtx* ctx, const float* parts, int slices, int64_t slice_elems, int rows,
+                            int cols, void* out, int64_t ldc, int fmt, int64_t part_off, int64_t flags_off,
+                            int use_multicast, uint32_t* epoch_ptr, uint32_t* cta_counter, uint32_t* status,
+                            uint64_t timeout_ns, void* stream);
+
 /* ---- flash attention forward (csrc/kernels/flash_attn.cu) ----
  * out[b, h, i, :] = softmax_j(scale * q[b, h, i, :] . k[b, g(h), j, :]) v[b, g(h), j, :] with q [B, Hq, Sq, D],
  * k / v [B, Hk, Sk, D] and out [B, Hq, Sq, D], all contiguous fp16 or bf16 (fmt = CATCOC_FMT_*), D = 64 or 128,

@@ -265,6 +265,60 @@ def pick_split_k(m: int, n: int, k: int, elt: int) -> int:
     return max(1, min(want, most, 32))
 
 
+def slice_k(k: int, split_k: int, elt: int):
+    """K per slice (whole pipeline stages of 256 bytes) and the number of slices that leaves."""
+    stage_k = 256 // elt
+    ks = math.ceil(math.ceil(k / max(1, split_k)) / stage_k) * stage_k
+    return ks, math.ceil(k / ks)
+
+
+def splitk_plan(m: int, n: int, k: int, elt: int):
+    """``(split_k, bn)`` for a product with few output tiles: the tile width and slice count that
+    fill the SMs with the fewest bytes per CTA. A CTA streams ``(128 + bn) * K / split_k`` operand
+    elements whatever M is, and a CTA's intake (not HBM) bounds such a product, so wide tiles cut
+    into more slices beat narrow ones: the A rows are re-read once per tile column."""
+    best = None
+    for bn in (256, 128):
+        if n < bn and bn > 128:
+            continue
+        tiles = math.ceil(m / 128) * math.ceil(n / bn)
+        want = max(1, _NUM_SMS // max(1, tiles))
+        most = max(1, k // (4 * (256 // elt)))
+        s = max(1, min(want, most, 32))
+        ks, s = slice_k(k, s, elt)
+        waves = math.ceil(tiles * s / _NUM_SMS)
+        cost = waves * (128 + bn) * ks
+        if best is None or cost < best[0]:
+            best = (cost, s, bn)
+    return best[1], best[2]
+
+
+def splitk_partials(a: torch.Tensor, b: torch.Tensor, *, split_k: int, trans_a: bool = False, trans_b: bool = False,
+                    tiling: Optional[TilingConfig] = None, part: Optional[torch.Tensor] = None,
+                    _args_out: Optional[list] = None):
+    """The first half of a split-K product: the K slices run as the groups of ONE launch, slice
+    ``i`` writing its fp32 partial ``[M, N]`` to rows ``[i * M, (i + 1) * M)`` of the returned
+    workspace. Returns ``(part, slices)``."""
+    dev = cm.require_cuda(a, b, part)
+    m, n, k = cm.logical_shape(a, trans_a, b, trans_b)
+    elt = a.element_size()
+    ks, s = slice_k(k, split_k, elt)
+    if trans_a and (m * elt) % 16 != 0:
+        a, trans_a = a.t().contiguous(), False   # slice origins along M must stay TMA-addressable
+    if part is None:
+        part = torch.empty((s * m, n), dtype=torch.float32, device=dev)
+    group = dict(m=s * m, n=n, k=ks, num_groups=s, group_rows=m, a_rows_total=m, a_k_total=k, b_n_total=n,
+                 b_k_total=k, g_a_row_back=m, g_a_k=ks, g_b_k=ks)
+    if tiling is None:
+        from ..tiling.chooser import heuristic
+        tiling = heuristic("matmul", s * m, n, ks, 1, a.dtype).with_(cta_pair=1)
+        if m % 128 != 0 and tiling.bn > 128:
+            tiling = tiling.with_(bn=128)
+    matmul(a, b, trans_a=trans_a, trans_b=trans_b, out=part, out_dtype=torch.float32, tiling=tiling, _group=group,
+           _args_out=_args_out)
+    return part, s
+
+
 def splitk_matmul(a: torch.Tensor, b: torch.Tensor, *, split_k: Optional[int] = None, trans_a: bool = False,
                   trans_b: bool = False, out: Optional[torch.Tensor] = None,
                   out_dtype: Optional[torch.dtype] = None, alpha: float = 1.0, beta: float = 0.0,
@@ -283,10 +337,7 @@ def splitk_matmul(a: torch.Tensor, b: torch.Tensor, *, split_k: Optional[int] = 
         out_dtype = out.dtype if out is not None else (a.dtype if a.dtype in (torch.float16, torch.bfloat16)
                                                        else torch.bfloat16)
     s = split_k if split_k is not None else pick_split_k(m, n, k, elt)
-    stage_k = 256 // elt
-    ks = math.ceil(math.ceil(k / s) / stage_k) * stage_k      # K per slice, whole pipeline stages
-    s = math.ceil(k / ks)
-    if s <= 1:
+    if slice_k(k, s, elt)[1] <= 1:
         return matmul(a, b, trans_a=trans_a, trans_b=trans_b, out=out, out_dtype=out_dtype, tiling=tiling,
                       alpha=alpha, beta=beta, c=c, bias_f32=bias_f32)
     if out is None:
@@ -295,17 +346,7 @@ def splitk_matmul(a: torch.Tensor, b: torch.Tensor, *, split_k: Optional[int] = 
         raise ValueError("out must be a row-major floating-point [%d, %d] tensor" % (m, n))
     if c is not None and (c.shape != (m, n) or c.dtype != out.dtype or c.stride(-1) != 1):
         raise ValueError("c must match the output's shape and dtype")
-    if trans_a and (m * elt) % 16 != 0:
-        a, trans_a = a.t().contiguous(), False   # slice origins along M must stay TMA-addressable
-    part = torch.empty((s * m, n), dtype=torch.float32, device=dev)
-    group = dict(m=s * m, n=n, k=ks, num_groups=s, group_rows=m, a_rows_total=m, a_k_total=k, b_n_total=n,
-                 b_k_total=k, g_a_row_back=m, g_a_k=ks, g_b_k=ks)
-    if tiling is None:
-        from ..tiling.chooser import heuristic
-        tiling = heuristic("matmul", s * m, n, ks, 1, a.dtype).with_(cta_pair=1)
-        if m % 128 != 0 and tiling.bn > 128:
-            tiling = tiling.with_(bn=128)
-    matmul(a, b, trans_a=trans_a, trans_b=trans_b, out=part, out_dtype=torch.float32, tiling=tiling, _group=group)
+    part, s = splitk_partials(a, b, split_k=s, trans_a=trans_a, trans_b=trans_b, tiling=tiling)
     with torch.cuda.device(dev):
         stream = torch.cuda.current_stream(dev).cuda_stream
         bias_ptr = None

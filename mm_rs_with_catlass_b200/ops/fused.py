@@ -18,6 +18,7 @@ the same kernel.
 """
 from __future__ import annotations
 
+import ctypes as C
 import os
 from typing import Optional, Tuple
 
@@ -331,6 +332,100 @@ def matmul_reduce_scatter(a: torch.Tensor, b: torch.Tensor, *, trans_a: bool = F
 
 
 # ---------------------------------------------------------------------------------------
+# Small M: split-K product + one-shot all-reduce (two launches of this library's kernels).
+_SMALL_AR_MAX_M = int(os.environ.get("CATCOC_SMALL_AR_MAX_M", "256"))
+
+
+def _small_allreduce_wanted(m: int, n: int, k: int, elt: int) -> bool:
+    """True where the fused tile loop has nothing to overlap (a single wave of tiles) and a CTA's
+    intake bounds the product: few rows, a K long enough to cut, rows of whole 16-byte vectors."""
+    if m > _SMALL_AR_MAX_M or n % 8 or n < 128:
+        return False
+    from .blas import splitk_plan
+    return splitk_plan(m, n, k, elt)[0] >= 2
+
+
+def _small_allreduce_call(ctx: ShmemContext, plan, out: torch.Tensor) -> torch.Tensor:
+    """Queues the two launches of a planned small all-reduce and advances the host mirror of the epoch."""
+    gemm_args, fixed, part_base, parity_bytes, flags_off, meta = plan
+    dev = ctx.device
+    cm.launch(gemm_args, dev)
+    epoch = ctx.epoch + 1
+    stream = torch.cuda.current_stream(dev).cuda_stream
+    nctx, parts_ptr, s, slice_elems, m, n, fmt = fixed
+    code = N.lib().catcoc_splitk_allreduce(C.byref(nctx), parts_ptr, s, slice_elems, m, n, out.data_ptr(), out.stride(0), fmt,
+                                           part_base + (epoch & 1) * parity_bytes, flags_off, 1 if ctx.mc_base else 0,
+                                           ctx.launch_state.data_ptr(), ctx.launch_state.data_ptr() + 4,
+                                           ctx.status.data_ptr(), cm.default_timeout_ns(), C.c_void_p(stream))
+    if code < 0:
+        N.check(code)
+    ctx.epoch = epoch
+    ctx.counters["launches"] += 2
+    ctx.counters["bytes_out"] += meta["bytes_out"]
+    ctx.last_call = meta
+    return out
+
+
+def _small_allreduce(ctx: ShmemContext, a: torch.Tensor, b: torch.Tensor, trans_a: bool, trans_b: bool,
+                     m: int, n: int, k: int, out: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
+    """``sum_r A_r @ B_r`` for few rows: the GEMM kernel in its split-K form (every SM streams a
+    share of B, fp32 partial planes), then ``splitk_allreduce_kernel``: fold the planes, publish
+    the rounded sum in the heap, stamp every rank, and read the sum over all ranks through the
+    switch (``multimem.ld_reduce``; peer loads in rank order without a multicast mapping).
+    Returns None when the output cannot take 16-byte stores (the caller then runs the fused kernel)."""
+    from .blas import splitk_plan, splitk_partials
+    dev = a.device
+    elt = a.element_size()
+    if out is None:
+        out = torch.empty((m, n), dtype=a.dtype, device=dev)
+    if out.stride(-1) != 1 or out.stride(0) % 8 or out.data_ptr() % 16:
+        return None
+    s, bn = splitk_plan(m, n, k, elt)
+    if m % 128 and bn > 128:
+        bn = 128
+    lib = N.lib()
+    with torch.cuda.device(dev):
+        scratch = ctx.__dict__.setdefault("local_scratch", {})
+        ws = scratch.get("small_ar_planes")
+        if ws is None or ws.numel() < s * m * n:
+            ws = torch.empty(max(s * m * n, 1 << 22), dtype=torch.float32, device=dev)
+            scratch["small_ar_planes"] = ws             # local memory, reused in stream order
+            _plans_of(ctx).clear()                      # plans hold the old workspace address
+        buf, parity_bytes = _data_region(ctx, "small_ar", m * n * elt)
+        flags = ctx.stamps(("small_ar", m, n, ctx.world), int(lib.catcoc_splitk_allreduce_flag_words(m, n, ctx.world)))
+        # the first call runs the product through the op layer (checks, tensor maps) and keeps its argument block
+        kept: list = []
+        part, s = splitk_partials(a, b, split_k=s, trans_a=trans_a, trans_b=trans_b,
+                                  tiling=TilingConfig(bn=bn, cta_pair=1), part=ws[:s * m * n].view(s * m, n), _args_out=kept)
+        meta = dict(op="matmul_allreduce", path="split-K + one-shot all-reduce", split_k=s, bn=bn,
+                    multicast=bool(ctx.mc_base), m=m, n=n, k=k,
+                    bytes_out=(ctx.world - 1) * m * n * elt)     # every peer reads this rank's copy once
+        copied = kept[0] is None or (trans_a and (m * elt) % 16 != 0)      # the product read a temporary copy of A
+        plan = (kept[0], (ctx.native_ctx(), part.data_ptr(), s, m * n, m, n, cm.out_fmt(a.dtype)), buf.offset, parity_bytes,
+                flags.offset, meta)
+        # the product is already queued: only the second launch is left for this call
+        _small_allreduce_tail(ctx, plan, out)
+    return out, (None if copied else plan)
+
+
+def _small_allreduce_tail(ctx: ShmemContext, plan, out: torch.Tensor) -> None:
+    """The second launch alone (the first call of a shape queues its product through the op layer)."""
+    _, fixed, part_base, parity_bytes, flags_off, meta = plan
+    epoch = ctx.epoch + 1
+    stream = torch.cuda.current_stream(ctx.device).cuda_stream
+    nctx, parts_ptr, s, slice_elems, m, n, fmt = fixed
+    N.check(N.lib().catcoc_splitk_allreduce(C.byref(nctx), parts_ptr, s, slice_elems, m, n, out.data_ptr(), out.stride(0),
+                                            fmt, part_base + (epoch & 1) * parity_bytes, flags_off,
+                                            1 if ctx.mc_base else 0, ctx.launch_state.data_ptr(),
+                                            ctx.launch_state.data_ptr() + 4, ctx.status.data_ptr(),
+                                            cm.default_timeout_ns(), C.c_void_p(stream)))
+    ctx.epoch = epoch
+    ctx.counters["launches"] += 2
+    ctx.counters["bytes_out"] += meta["bytes_out"]
+    ctx.last_call = meta
+
+
+# ---------------------------------------------------------------------------------------
 def matmul_allreduce(a: torch.Tensor, b: torch.Tensor, *, trans_a: bool = False, trans_b: bool = False,
                      out: Optional[torch.Tensor] = None, tiling: Optional[TilingConfig] = None,
                      ctx: Optional[ShmemContext] = None) -> torch.Tensor:
@@ -345,6 +440,14 @@ def matmul_allreduce(a: torch.Tensor, b: torch.Tensor, *, trans_a: bool = False,
     """
     ctx = _ctx(ctx)
     key = ("ar", cm.tkey(a), cm.tkey(b), trans_a, trans_b, tiling)
+    if tiling is None:
+        small = _plan_hit(ctx, ("ar_small",) + key[1:])
+        if small is not None:
+            if out is None:
+                out = torch.empty((small[1][4], small[1][5]), dtype=a.dtype, device=ctx.device)
+            if out.stride(-1) == 1 and out.stride(0) % 8 == 0 and out.data_ptr() % 16 == 0 and \
+                    tuple(out.shape) == (small[1][4], small[1][5]) and out.dtype == a.dtype:
+                return _small_allreduce_call(ctx, small, out)
     plan = _plan_hit(ctx, key)
     if plan is not None and (out is None or (out.shape == plan[1][0].shape and out.dtype == plan[1][0].dtype)):
         args, views = plan
@@ -362,6 +465,12 @@ def matmul_allreduce(a: torch.Tensor, b: torch.Tensor, *, trans_a: bool = False,
         raise TypeError("matmul_allreduce takes fp16 / bf16 operands")
     if out is not None and (tuple(out.shape) != (m, n) or out.dtype != a.dtype):
         raise ValueError("out must be a [%d, %d] %s tensor" % (m, n, a.dtype))
+    if tiling is None and _small_allreduce_wanted(m, n, k, a.element_size()):
+        res = _small_allreduce(ctx, a, b, trans_a, trans_b, m, n, k, out)
+        if res is not None:
+            if res[1] is not None:
+                _plan_put(ctx, ("ar_small",) + key[1:], res[1])
+            return res[0]
     t = _resolve_tiling("matmul_allreduce", m, n, k, ctx.world, a.dtype, tiling)
     if t.use_multicast and not ctx.mc_base:
         t = t.with_(use_multicast=False)
@@ -495,6 +604,9 @@ def allgather_matmul(a_shard: torch.Tensor, b: torch.Tensor, *, trans_b: bool = 
         # the alias and the tiling or CATCOC_AG_MULTICAST asks for it
         want_mc = t.use_multicast if os.environ.get("CATCOC_AG_MULTICAST") is None \
             else os.environ["CATCOC_AG_MULTICAST"] == "1"
+        if args.act and os.environ.get("CATCOC_AG_MULTICAST") is None:
+            want_mc = True      # the epilogue variant with the activation has ONE communication warp: enough for
+            #                     multicast stores (the shard leaves once), not for W - 1 peer copies
         if want_mc and ctx.mc_base:
             args.gathered_mc, args.gflags_mc = gbuf.mc_ptr(), gfl.mc_ptr()
             args.tiling.use_multicast = 1

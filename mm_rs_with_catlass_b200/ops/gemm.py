@@ -108,7 +108,8 @@ def matmul(a: torch.Tensor, b: torch.Tensor, *, trans_a: bool = False, trans_b: 
            bias: Optional[torch.Tensor] = None, tiling: Optional[TilingConfig] = None,
            trace: Optional[torch.Tensor] = None, alpha: float = 1.0, beta: float = 0.0,
            c: Optional[torch.Tensor] = None, bias_f32: Optional[torch.Tensor] = None,
-           activation: Optional[str] = None, _group: Optional[dict] = None) -> torch.Tensor:
+           activation: Optional[str] = None, _group: Optional[dict] = None,
+           _args_out: Optional[list] = None) -> torch.Tensor:
     """``out = alpha * (A @ B) + beta * C + bias_f32`` with fp32 (int32 for int8) accumulation.
 
     ``a`` is stored ``[M, K]`` (``[K, M]`` with ``trans_a``), ``b`` is stored ``[K, N]``
@@ -226,6 +227,9 @@ def matmul(a: torch.Tensor, b: torch.Tensor, *, trans_a: bool = False, trans_b: 
             args.trace = trace.data_ptr()
         if pad is not None:
             pad.fill(args)
+        if _args_out is not None:
+            # a caller that keeps its own plan of a group launch (ops/fused.py); None: the block points at a temporary copy
+            _args_out.append(None if (oa.copied or ob.copied) else args)
         cm.launch(args, dev)
         if key is not None and not oa.copied and not ob.copied:
             if len(_plans) >= _MAX_PLANS:

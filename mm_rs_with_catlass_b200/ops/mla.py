@@ -29,10 +29,18 @@ _workspaces: dict = {}
 
 
 def _pick_splits(batch: int, rows_per_item: int, max_pages: int, sms: int = 148) -> int:
-    """Slices per sequence: enough CTAs for every SM, never more slices than 128-key pages."""
-    ctas = 2 * batch * ((rows_per_item + 127) // 128)
-    want = max(1, (2 * sms + ctas - 1) // ctas)
-    return int(max(1, min(want, max_pages, 64)))
+    """Slices per sequence. One CTA fits an SM, so the grid runs in waves of ``sms`` CTAs and a
+    slice count is judged by waves x steps per CTA (a few steps of fixed cost for the Q load, the
+    pipeline fill and the epilogue included); never more slices than 128-key pages."""
+    base = 2 * batch * ((rows_per_item + 127) // 128)          # CTAs with one slice
+    steps = 4 * max_pages                                       # 32-key steps of the longest sequence
+    best, best_cost = 1, None
+    for s in range(1, int(min(max_pages, 64)) + 1):
+        waves = (base * s + sms - 1) // sms
+        cost = waves * ((steps + s - 1) // s + 6)
+        if best_cost is None or cost < best_cost:
+            best, best_cost = s, cost
+    return best
 
 
 def mla_decode(q_nope: torch.Tensor, q_rope: torch.Tensor, ckv_cache: torch.Tensor, krope_cache: torch.Tensor,

@@ -165,6 +165,13 @@ def run_mixed_geometries(ctx, W, iters, name):
     t_ar_rows = T(bn=128, seg_dim=0, pull=0)
     cases.append(("ar_rows", lambda: catcoc.matmul_allreduce(a5, b5, tiling=t_ar_rows).clone(),
                   _DeviceCheck(gold5, 128 * W, bf, mag5)))
+    # few rows and a long K: the split-K product + one-shot all-reduce path (its own buffer halves and stamps, the
+    # same epoch counter as the fused kernels)
+    a6, b6 = matmul_inputs(128, 1024, 2048, rank, bf, dev, seed=206)
+    gold6 = ref.matmul_allreduce(a6, b6, out_dtype=torch.float32)
+    cases.append(("ar_small", lambda: catcoc.matmul_allreduce(a6, b6), _DeviceCheck(gold6, 2048 * W, bf, pmag(a6, b6))))
+    catcoc.matmul_allreduce(a6, b6)
+    assert ctx.last_call.get("path", "").startswith("split-K"), ctx.last_call
     # the all-reduce result lives in the heap: the next call of another shape must not touch it
     keep = catcoc.matmul_allreduce(a2, b2, tiling=t_ar_cols)
     catcoc.matmul_allreduce(a5, b5, tiling=t_ar_rows)
@@ -227,6 +234,24 @@ if mode == "ops":
         gold = ref.matmul_allreduce(a, b, out_dtype=torch.float32)
         mag = pmag(a, b)
         check("ar_smallM_%s" % str(dtype)[6:], catcoc.matmul_allreduce(a, b), gold, 256 * W, dtype, mag)
+        # few rows and a long K: split-K product + one-shot all-reduce (auto tiling only); an explicit tiling keeps the
+        # fused kernel on the same shape
+        for (M2, N2, K2, tb2) in [(128, 1024, 2048, False), (96, 520, 4096, True), (256, 2048, 3072, False), (1, 128, 8192, False)]:
+            a, b = matmul_inputs(M2, N2, K2, rank, dtype, dev, trans_b=tb2, seed=M2 + K2)
+            gold = ref.matmul_allreduce(a, b, trans_b=tb2, out_dtype=torch.float32)
+            mag = pmag(a, b, trans_b=tb2)
+            tag = "%s_%dx%dx%d_%d" % (str(dtype)[6:], M2, N2, K2, tb2)
+            o = catcoc.matmul_allreduce(a, b, trans_b=tb2)
+            small = ctx.last_call.get("path", "").startswith("split-K")
+            check("ar_oneshot_" + tag, o, gold, K2 * W, dtype, mag)
+            report("ar_oneshot_path_" + tag, small, str(ctx.last_call))
+            given = torch.empty_like(o)
+            check("ar_oneshot_out_" + tag, catcoc.matmul_allreduce(a, b, trans_b=tb2, out=given), gold, K2 * W, dtype, mag)
+            check("ar_fused_" + tag, catcoc.matmul_allreduce(a, b, trans_b=tb2, tiling=catcoc.TilingConfig(bn=128)), gold,
+                  K2 * W, dtype, mag)
+        a, b = matmul_inputs(96, 1024, 256, rank, dtype, dev, seed=11)
+        gold = ref.matmul_allreduce(a, b, out_dtype=torch.float32)
+        mag = pmag(a, b)
         for seg in (0, 1):
             check("ar_seg%d_%s" % (seg, str(dtype)[6:]),
                   catcoc.matmul_allreduce(a, b, tiling=catcoc.TilingConfig(bn=64, seg_dim=seg)), gold, 256 * W, dtype,

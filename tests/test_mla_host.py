@@ -37,9 +37,12 @@ def test_golden_accepts_a_singleton_head_dimension_and_empty_sequences():
     assert torch.count_nonzero(out[0]) == 0 and torch.isfinite(out).all() and torch.count_nonzero(out[1]) > 0
 
 
-def test_slices_fill_the_gpu_without_exceeding_the_pages():
+def test_slices_fill_whole_waves_without_exceeding_the_pages():
     assert _pick_splits(batch=1, rows_per_item=16, max_pages=1) == 1          # a 128-key sequence cannot be cut
     assert _pick_splits(batch=1, rows_per_item=16, max_pages=64) == 64        # one sequence: as many slices as allowed
-    assert _pick_splits(batch=256, rows_per_item=128, max_pages=32) == 1      # enough CTAs already
-    s = _pick_splits(batch=8, rows_per_item=128, max_pages=32)
-    assert 2 * 8 * s >= 2 * 148 and s <= 32
+    assert _pick_splits(batch=256, rows_per_item=128, max_pages=32) <= 2      # several waves already
+    s = _pick_splits(batch=32, rows_per_item=16, max_pages=32)                # 64 CTAs per slice count
+    assert s == 2 and 64 * s <= 148                                           # one full wave beats 2.2 waves of 5 slices
+    for batch, rows, pages in [(8, 128, 32), (3, 64, 17), (128, 16, 16)]:
+        s = _pick_splits(batch, rows, pages)
+        assert 1 <= s <= pages
