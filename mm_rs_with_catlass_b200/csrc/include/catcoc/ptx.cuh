@@ -168,6 +168,16 @@ CATCOC_DEVICE void tma_load_3d(void* smem_dst, const void* tmap, uint64_t* bar, 
       : "memory");
 }
 
+// 4-D form (a paged array whose columns are cut into 128-byte blocks: {block column, row, block, page})
+CATCOC_DEVICE void tma_load_4d(void* smem_dst, const void* tmap, uint64_t* bar, int x, int y, int z, int w) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4, %5, %6}], [%2];"
+      ::"r"(smem_u32(smem_dst)),
+      "l"(reinterpret_cast<uint64_t>(tmap)), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z), "r"(w)
+      : "memory");
+}
+
 // ---------------------------------------------------------------------------------------
 // tcgen05 / TMEM
 // ---------------------------------------------------------------------------------------

@@ -6,8 +6,9 @@
 //
 //   warps 0..3  softmax      : one query row per thread: tcgen05.ld 32 scores, exp2, row sum, P written back over the
 //                              scores (tcgen05.st), O rescaled in TMEM when the reference maximum moved
-//   warp 4      TMA producer : the Q rows once (9 blocks of 64 columns), then 32 keys per step through a ring of
-//                              slots; the page of every step comes from the block table
+//   warp 4      TMA producer : the Q rows once, then 32 keys per step through a ring of slots (two copies per step:
+//                              the eight latent blocks at once, the rotary block); the page of every step comes from
+//                              the block table
 //   warp 5      MMA issuer   : S = Q K^T (36 MMAs over the 576 columns) one step ahead of O += P V (P from TMEM,
 //                              V = this CTA's 256 latent columns of the same slot, MN-major)
 //
@@ -48,8 +49,10 @@ constexpr uint32_t kOCol = 64;
 constexpr float kLazyRescale = 8.0f;
 
 struct MlaParams {
-  CUtensorMap tm_qn, tm_qr;       // q_nope {512, rows} / q_rope {64, rows}, box {64, QR}
-  CUtensorMap tm_kn, tm_kr;       // latent cache {512, 128, pages} / rope cache {64, 128, pages}, box {64, 32, 1}
+  // The 512 latent columns are described as {64, rows, 8 blocks} (the block stride is 128 bytes, smaller than the row
+  // stride): ONE copy then fills all eight 64-column blocks of a tile, block-major, each 128-byte swizzled.
+  CUtensorMap tm_qn, tm_qr;       // q_nope {64, rows, 8}, box {64, QR, 8} / q_rope {64, rows}, box {64, QR}
+  CUtensorMap tm_kn, tm_kr;       // latent cache {64, 128, 8, pages}, box {64, 32, 8, 1} / rope cache {64, 128, pages}, box {64, 32, 1}
   const int* block_table;         // [B, max_pages]
   const int* kv_lens;             // [B]
   void* out;                      // [rows, 512] operand dtype
@@ -133,7 +136,7 @@ __global__ void __launch_bounds__(kThreads, 1) mla_decode_kernel(const __grid_co
     // ------------------------------ TMA producer ------------------------------
     if (nsteps > 0 && ptx::elect_one()) {
       ptx::mbar_expect_tx(&bars->q_full, kQBytes);
-      for (int c = 0; c < kChunks - 1; ++c) ptx::tma_load_2d(sq + c * kQChunkBytes, &p.tm_qn, &bars->q_full, c * 64, grow0);
+      ptx::tma_load_3d(sq, &p.tm_qn, &bars->q_full, 0, grow0, 0);
       ptx::tma_load_2d(sq + (kChunks - 1) * kQChunkBytes, &p.tm_qr, &bars->q_full, 0, grow0);
     }
     __syncwarp();
@@ -156,7 +159,7 @@ __global__ void __launch_bounds__(kThreads, 1) mla_decode_kernel(const __grid_co
         const int prow = key0 % kPage;
         uint8_t* dst = skv + slot * kSlotBytes;
         ptx::mbar_expect_tx(&bars->kv_full[slot], kSlotBytes);
-        for (int c = 0; c < kChunks - 1; ++c) ptx::tma_load_3d(dst + c * kKChunkBytes, &p.tm_kn, &bars->kv_full[slot], c * 64, prow, page);
+        ptx::tma_load_4d(dst, &p.tm_kn, &bars->kv_full[slot], 0, prow, 0, page);
         ptx::tma_load_3d(dst + (kChunks - 1) * kKChunkBytes, &p.tm_kr, &bars->kv_full[slot], 0, prow, page);
       }
       __syncwarp();
@@ -381,16 +384,24 @@ using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t
                                    const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                    CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
-// rank 2: [rows, cols] with a {64, box_rows} box; rank 3: [pages, 128, cols] with a {64, box_rows, 1} box. cols contiguous.
-int encode(CUtensorMap* tm, const void* base, CUtensorMapDataType dt, int rank, int64_t cols, int64_t rows, int64_t pages,
+// A [pages, rows, cols] array (cols contiguous, 16-bit elements) as a tensor map with a {64, box_rows, ...} box.
+// blocks == 1: {cols, rows, pages} (rank 2 when pages == 0). blocks > 1: the columns are cut into `blocks` blocks of
+// 64 that become a dimension of their own behind the rows, {64, rows, blocks, pages}, so that one copy lays the
+// blocks out one after the other in shared memory.
+int encode(CUtensorMap* tm, const void* base, CUtensorMapDataType dt, int64_t cols, int64_t rows, int64_t pages, int blocks,
            int box_rows) {
   static EncodeTiledFn fn = driver_fn<EncodeTiledFn>("cuTensorMapEncodeTiled");
   if (fn == nullptr) return CATCOC_E_DRIVER;
   if (reinterpret_cast<uintptr_t>(base) & 15) { set_error("mla_decode operands must be 16-byte aligned"); return CATCOC_E_ALIGNMENT; }
-  cuuint64_t gdim[3] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows), static_cast<cuuint64_t>(pages)};
-  cuuint64_t gstride[2] = {static_cast<cuuint64_t>(cols) * 2, static_cast<cuuint64_t>(rows) * cols * 2};
-  cuuint32_t box[3] = {64, static_cast<cuuint32_t>(box_rows), 1};
-  cuuint32_t estr[3] = {1, 1, 1};
+  cuuint64_t gdim[4];
+  cuuint64_t gstride[3];
+  cuuint32_t box[4];
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  int rank = 0;
+  gdim[rank] = blocks > 1 ? 64 : static_cast<cuuint64_t>(cols); box[rank++] = 64;
+  gdim[rank] = static_cast<cuuint64_t>(rows); gstride[rank - 1] = static_cast<cuuint64_t>(cols) * 2; box[rank++] = static_cast<cuuint32_t>(box_rows);
+  if (blocks > 1) { gdim[rank] = static_cast<cuuint64_t>(blocks); gstride[rank - 1] = 128; box[rank++] = static_cast<cuuint32_t>(blocks); }
+  if (pages > 0) { gdim[rank] = static_cast<cuuint64_t>(pages); gstride[rank - 1] = static_cast<cuuint64_t>(rows) * cols * 2; box[rank++] = 1; }
   CUresult r = fn(tm, dt, static_cast<cuuint32_t>(rank), const_cast<void*>(base), gdim, gstride, box, estr,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -427,10 +438,10 @@ extern "C" int catcoc_mla_decode(const void* q_nope, const void* q_rope, const v
   const int64_t total_rows = static_cast<int64_t>(B) * rows_per_item;
   if (total_rows > (1 << 30)) { set_error("mla_decode: too many query rows"); return CATCOC_E_BAD_ARG; }
   const int qr = rows_per_item <= 64 ? 64 : 128;
-  int rc = encode(&p.tm_qn, q_nope, dt, 2, mla::kDV, total_rows, 1, qr);
-  if (rc == 0) rc = encode(&p.tm_qr, q_rope, dt, 2, mla::kDR, total_rows, 1, qr);
-  if (rc == 0) rc = encode(&p.tm_kn, ckv, dt, 3, mla::kDV, mla::kPage, num_pages, mla::kBKV);
-  if (rc == 0) rc = encode(&p.tm_kr, krope, dt, 3, mla::kDR, mla::kPage, num_pages, mla::kBKV);
+  int rc = encode(&p.tm_qn, q_nope, dt, mla::kDV, total_rows, 0, mla::kDV / 64, qr);
+  if (rc == 0) rc = encode(&p.tm_qr, q_rope, dt, mla::kDR, total_rows, 0, 1, qr);
+  if (rc == 0) rc = encode(&p.tm_kn, ckv, dt, mla::kDV, mla::kPage, num_pages, mla::kDV / 64, mla::kBKV);
+  if (rc == 0) rc = encode(&p.tm_kr, krope, dt, mla::kDR, mla::kPage, num_pages, 1, mla::kBKV);
   if (rc != 0) return rc;
   p.block_table = block_table; p.kv_lens = kv_lens; p.out = out;
   p.B = B; p.q_len = q_len; p.H = H; p.max_pages = max_pages; p.num_pages = num_pages; p.splits = splits;
