@@ -333,7 +333,8 @@ def matmul_reduce_scatter(a: torch.Tensor, b: torch.Tensor, *, trans_a: bool = F
 
 # ---------------------------------------------------------------------------------------
 # Small M: split-K product + one-shot all-reduce (two launches of this library's kernels).
-_SMALL_AR_MAX_M = int(os.environ.get("CATCOC_SMALL_AR_MAX_M", "256"))
+# measured on 2 and 4 GPUs: the two-launch path wins at M = 128 (81 vs 103 us, 70 vs 87 us) and loses at M = 256
+_SMALL_AR_MAX_M = int(os.environ.get("CATCOC_SMALL_AR_MAX_M", "128"))
 
 
 def _small_allreduce_wanted(m: int, n: int, k: int, elt: int) -> bool:
