@@ -227,8 +227,7 @@ def run(args) -> int:
     # ---- end to end through the public model API: pinned host input -> device -> block -> loss -> host.
     # Every step copies its own input shard from pinned host memory (on a copy stream, one step
     # ahead of the compute, as a data loader does) and reads its own scalar result back. ----
-    e2e = None
-    if not args.no_e2e:
+    def end_to_end():
         _State.phase = "end to end"
         if ours:
             mlp = TPMLP(TPMLPConfig(hidden=HIDDEN, ffn=FFN), ctx, dev)
@@ -309,6 +308,19 @@ def run(args) -> int:
             e2e.update({"cublas_nccl_ms": ms_b, "cublas_nccl_value": flops_e2e / (ms_b * 1e-3) / 1e12,
                         "speedup": ms_b / ms_e})
         check("end to end")
+        return e2e
+
+    e2e = None
+    if not args.no_e2e:
+        try:
+            e2e = end_to_end()
+        except Exception as exc:   # the headline above is already measured: report it, with the failure beside it
+            e2e = {"error": "%s: %s" % (type(exc).__name__, str(exc)[:400]), "phase": _State.phase}
+            try:
+                if ctx is not None:
+                    ctx.reset_after_error()
+            except Exception:
+                pass
 
     vs = (base_step_ms / ms_step) if (ours and base_step_ms) else None
     clocks = sampler.summary() if sampler is not None else {}

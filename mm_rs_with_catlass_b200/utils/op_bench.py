@@ -194,7 +194,7 @@ def main(argv=None) -> int:
                    lambda: base.matmul_allreduce(a, b, out=out), 2.0 * M * HIDDEN * kf, ar_bytes,
                    shape=(M, HIDDEN, kf))
             del a, b, out
-        if M % W == 0 and M >= 1024:
+        if M % W == 0 and M >= 128:
             if "ag" in args.ops:
                 a, b = matmul_inputs(M // W, kf, HIDDEN, rank, torch.bfloat16, dev, seed=2, b_std=0.02)
                 out = torch.empty((M, kf), dtype=torch.bfloat16, device=dev)
