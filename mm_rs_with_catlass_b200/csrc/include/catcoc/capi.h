@@ -255,13 +255,16 @@ int catcoc_gemv(const void* A, int64_t lda, int fmt, int rows, int cols, int tra
                 const void* y_in, float alpha, float beta, float* workspace, void* stream);
 
 /* ---- split-K product + one-shot all-reduce (csrc/kernels/small_allreduce.cu) ----
- * out[rows, cols] (fp16 / bf16, pitch ldc) = sum over ranks of round(sum over `slices` fp32 planes of this rank). The
+ * out[out_rows, cols] (fp16 / bf16, pitch ldc) = rows [out_row0, out_row0 + out_rows) of the sum over ranks of
+ * round(sum over `slices` fp32 planes [rows, cols] of this rank): all rows for an all-reduce, the rank's share for a
+ * reduce-scatter. The
  * rounded local sum goes to heap offset part_off (the parity half of this launch's epoch, rows * cols * 2 bytes), the
  * stamps to catcoc_splitk_allreduce_flag_words(...) words at flags_off (zeroed once, never reset). cols and ldc must be
  * multiples of 8. epoch_ptr / cta_counter / status: the launch bookkeeping of the fused kernels (CatcocOpArgs). */
 int64_t catcoc_splitk_allreduce_flag_words(int rows, int cols, int W);
 int catcoc_splitk_allreduce(const CatcocShmemCtx* ctx, const float* parts, int slices, int64_t slice_elems, int rows,
-                            int cols, void* out, int64_t ldc, int fmt, int64_t part_off, int64_t flags_off,
+                            int cols, int out_row0, int out_rows, void* out, int64_t ldc, int fmt, int64_t part_off,
+                            int64_t flags_off,
                             int use_multicast, uint32_t* epoch_ptr, uint32_t* cta_counter, uint32_t* status,
                             uint64_t timeout_ns, void* stream);
 

@@ -3,7 +3,8 @@
 // partial planes in a local workspace), so that every SM streams a share of B. This kernel then
 //   phase A  sums the planes of a chunk, rounds to the operand dtype, stores the chunk into this rank's symmetric
 //            buffer and stamps (chunk, rank) on every rank (one multimem.st through the switch, or a store per peer);
-//   phase B  waits for the W stamps of a chunk and reads the sum of all ranks' copies through the switch
+//   phase B  waits for the W stamps of a chunk of its output rows (all rows for an all-reduce, its own share for a
+//            reduce-scatter) and reads the sum of all ranks' copies through the switch
 //            (multimem.ld_reduce, fp32 accumulation) or, without a multicast mapping, from the peers in rank order,
 //            and writes this rank's output. Every rank reduces every chunk itself: no broadcast, no second hop.
 // A one-wave GEMM has nothing to overlap a collective with, so at these sizes the fused tile loop buys nothing and
@@ -35,8 +36,9 @@ struct SmallArParams {
   int slices;
   int64_t slice_elems;
   int64_t total;              // rows * cols
+  int64_t out_first, out_count;   // the elements this rank reduces and stores: all of them (all-reduce) or its rows (reduce-scatter)
   int cols;
-  void* out;                  // local [rows, cols], pitch ldc elements
+  void* out;                  // local output: element out_first lands at out[0]; rows of `cols` elements, pitch ldc
   int64_t ldc;
   int fmt;                    // FMT_F16 / FMT_BF16
   int rank, W;
@@ -92,9 +94,10 @@ __global__ void __launch_bounds__(kThreads) splitk_allreduce_kernel(const SmallA
     }
   }
 
-  // ---- phase B: every rank sums every chunk ----
+  // ---- phase B: this rank sums the chunks of its output range (all of them for an all-reduce) ----
   bool failed = false;
-  for (int64_t c = blockIdx.x; c < chunks && !failed; c += gridDim.x) {
+  const int64_t c_lo = p.out_first / kChunkElems, c_hi = (p.out_first + p.out_count + kChunkElems - 1) / kChunkElems;
+  for (int64_t c = c_lo + blockIdx.x; c < c_hi && !failed; c += gridDim.x) {
     if (tid < p.W) {
       const uint32_t* f = p.flags[p.rank] + c * p.W + tid;
       const uint64_t t0 = ptx::globaltimer_ns();
@@ -114,7 +117,7 @@ __global__ void __launch_bounds__(kThreads) splitk_allreduce_kernel(const SmallA
     __syncthreads();
     if (s_fail[0] != 0u) { failed = true; break; }
     const int64_t e0 = c * kChunkElems + static_cast<int64_t>(tid) * kPer;
-    if (e0 < p.total) {
+    if (e0 >= p.out_first && e0 < p.out_first + p.out_count) {
       uint4 r;
       if (p.part_mc != nullptr) {
         r = (p.fmt == FMT_BF16) ? ptx::multimem_ld_reduce_add_bf16x2_v4(p.part_mc + e0 * 2)
@@ -130,7 +133,8 @@ __global__ void __launch_bounds__(kThreads) splitk_allreduce_kernel(const SmallA
         r = make_uint4(pack2(acc[0], acc[1], p.fmt), pack2(acc[2], acc[3], p.fmt), pack2(acc[4], acc[5], p.fmt),
                        pack2(acc[6], acc[7], p.fmt));
       }
-      const int64_t row = e0 / p.cols, col = e0 - row * p.cols;     // cols % 8 == 0: a vector never crosses a row
+      const int64_t eo = e0 - p.out_first;
+      const int64_t row = eo / p.cols, col = eo - row * p.cols;     // cols % 8 == 0: a vector never crosses a row
       ptx::st_global_v4(static_cast<uint8_t*>(p.out) + (row * p.ldc + col) * 2, r);
     }
   }
@@ -161,11 +165,13 @@ __global__ void __launch_bounds__(kThreads) splitk_allreduce_kernel(const SmallA
 using namespace catcoc;
 
 extern "C" int catcoc_splitk_allreduce(const CatcocShmemCtx* ctx, const float* parts, int slices, int64_t slice_elems,
-                                       int rows, int cols, void* out, int64_t ldc, int fmt, int64_t part_off,
+                                       int rows, int cols, int out_row0, int out_rows, void* out, int64_t ldc, int fmt,
+                                       int64_t part_off,
                                        int64_t flags_off, int use_multicast, uint32_t* epoch_ptr, uint32_t* cta_counter,
                                        uint32_t* status, uint64_t timeout_ns, void* stream) {
   if (ctx == nullptr || parts == nullptr || out == nullptr || epoch_ptr == nullptr || cta_counter == nullptr ||
-      status == nullptr || slices <= 0 || rows <= 0 || cols <= 0 || ctx->W < 2 || ctx->W > 8) {
+      status == nullptr || slices <= 0 || rows <= 0 || cols <= 0 || ctx->W < 2 || ctx->W > 8 || out_row0 < 0 ||
+      out_rows <= 0 || out_row0 + out_rows > rows) {
     host::set_error("splitk_allreduce: bad argument");
     return CATCOC_E_BAD_ARG;
   }
@@ -178,6 +184,7 @@ extern "C" int catcoc_splitk_allreduce(const CatcocShmemCtx* ctx, const float* p
   SmallArParams p;
   p.parts = parts; p.slices = slices; p.slice_elems = slice_elems;
   p.total = static_cast<int64_t>(rows) * cols; p.cols = cols;
+  p.out_first = static_cast<int64_t>(out_row0) * cols; p.out_count = static_cast<int64_t>(out_rows) * cols;
   p.out = out; p.ldc = ldc; p.fmt = fmt;
   p.rank = ctx->rank; p.W = ctx->W;
   for (int q = 0; q < 8; ++q) {

@@ -293,6 +293,12 @@ def matmul_reduce_scatter(a: torch.Tensor, b: torch.Tensor, *, trans_a: bool = F
     """
     ctx = _ctx(ctx)
     key = ("rs", cm.tkey(a), cm.tkey(b), trans_a, trans_b, cm.tkey(out), tiling)
+    if tiling is None:
+        small = _plan_hit(ctx, ("rs_small",) + key[1:])
+        if small is not None:
+            if out is None:
+                out = torch.empty((small[1][7], small[1][5]), dtype=a.dtype, device=ctx.device)
+            return _small_allreduce_call(ctx, small, out)
     plan = _plan_hit(ctx, key)
     if plan is not None:
         args, out_shape, out_dtype = plan
@@ -315,6 +321,12 @@ def matmul_reduce_scatter(a: torch.Tensor, b: torch.Tensor, *, trans_a: bool = F
         out = torch.empty((rows, n), dtype=a.dtype, device=dev)
     if tuple(out.shape) != (rows, n) or out.stride(-1) != 1 or out.dtype != a.dtype:
         raise ValueError("out must be a row-major [%d, %d] %s tensor" % (rows, n, a.dtype))
+    if tiling is None and _small_allreduce_wanted(m, n, k, a.element_size()):
+        res = _small_allreduce(ctx, a, b, trans_a, trans_b, m, n, k, out, scatter=True)
+        if res is not None:
+            if res[1] is not None:
+                _plan_put(ctx, ("rs_small",) + key[1:], res[1])
+            return res[0]
     t = _resolve_tiling("matmul_reduce_scatter", m, n, k, ctx.world, a.dtype, tiling)
     with torch.cuda.device(dev):
         args, keep = _base_args(ctx, N.MODE_RS, a, trans_a, b, trans_b, m, n, k, t, seg_rows=rows)
@@ -353,8 +365,9 @@ def _small_allreduce_call(ctx: ShmemContext, plan, out: torch.Tensor) -> torch.T
     cm.launch(gemm_args, dev)
     epoch = ctx.epoch + 1
     stream = torch.cuda.current_stream(dev).cuda_stream
-    nctx, parts_ptr, s, slice_elems, m, n, fmt = fixed
-    code = N.lib().catcoc_splitk_allreduce(C.byref(nctx), parts_ptr, s, slice_elems, m, n, out.data_ptr(), out.stride(0), fmt,
+    nctx, parts_ptr, s, slice_elems, m, n, row0, rows, fmt = fixed
+    code = N.lib().catcoc_splitk_allreduce(C.byref(nctx), parts_ptr, s, slice_elems, m, n, row0, rows, out.data_ptr(),
+                                           out.stride(0), fmt,
                                            part_base + (epoch & 1) * parity_bytes, flags_off, 1 if ctx.mc_base else 0,
                                            ctx.launch_state.data_ptr(), ctx.launch_state.data_ptr() + 4,
                                            ctx.status.data_ptr(), cm.default_timeout_ns(), C.c_void_p(stream))
@@ -368,17 +381,21 @@ def _small_allreduce_call(ctx: ShmemContext, plan, out: torch.Tensor) -> torch.T
 
 
 def _small_allreduce(ctx: ShmemContext, a: torch.Tensor, b: torch.Tensor, trans_a: bool, trans_b: bool,
-                     m: int, n: int, k: int, out: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
+                     m: int, n: int, k: int, out: Optional[torch.Tensor], scatter: bool = False):
     """``sum_r A_r @ B_r`` for few rows: the GEMM kernel in its split-K form (every SM streams a
     share of B, fp32 partial planes), then ``splitk_allreduce_kernel``: fold the planes, publish
     the rounded sum in the heap, stamp every rank, and read the sum over all ranks through the
     switch (``multimem.ld_reduce``; peer loads in rank order without a multicast mapping).
-    Returns None when the output cannot take 16-byte stores (the caller then runs the fused kernel)."""
+    With ``scatter`` every rank reduces and keeps only its own ``m / W`` rows (reduce-scatter).
+    Returns ``(out, plan)``, or None when the output cannot take 16-byte stores (the caller then
+    runs the fused kernel)."""
     from .blas import splitk_plan, splitk_partials
     dev = a.device
     elt = a.element_size()
+    rows = m // ctx.world if scatter else m
+    row0 = ctx.rank * rows if scatter else 0
     if out is None:
-        out = torch.empty((m, n), dtype=a.dtype, device=dev)
+        out = torch.empty((rows, n), dtype=a.dtype, device=dev)
     if out.stride(-1) != 1 or out.stride(0) % 8 or out.data_ptr() % 16:
         return None
     s, bn = splitk_plan(m, n, k, elt)
@@ -398,12 +415,14 @@ def _small_allreduce(ctx: ShmemContext, a: torch.Tensor, b: torch.Tensor, trans_
         kept: list = []
         part, s = splitk_partials(a, b, split_k=s, trans_a=trans_a, trans_b=trans_b,
                                   tiling=TilingConfig(bn=bn, cta_pair=1), part=ws[:s * m * n].view(s * m, n), _args_out=kept)
-        meta = dict(op="matmul_allreduce", path="split-K + one-shot all-reduce", split_k=s, bn=bn,
+        meta = dict(op="matmul_reduce_scatter" if scatter else "matmul_allreduce",
+                    path="split-K + one-shot " + ("reduce-scatter" if scatter else "all-reduce"), split_k=s, bn=bn,
                     multicast=bool(ctx.mc_base), m=m, n=n, k=k,
-                    bytes_out=(ctx.world - 1) * m * n * elt)     # every peer reads this rank's copy once
+                    # every peer reads this rank's copy of the rows it keeps
+                    bytes_out=(ctx.world - 1) * (rows if scatter else m) * n * elt)
         copied = kept[0] is None or (trans_a and (m * elt) % 16 != 0)      # the product read a temporary copy of A
-        plan = (kept[0], (ctx.native_ctx(), part.data_ptr(), s, m * n, m, n, cm.out_fmt(a.dtype)), buf.offset, parity_bytes,
-                flags.offset, meta)
+        plan = (kept[0], (ctx.native_ctx(), part.data_ptr(), s, m * n, m, n, row0, rows, cm.out_fmt(a.dtype)), buf.offset,
+                parity_bytes, flags.offset, meta)
         # the product is already queued: only the second launch is left for this call
         _small_allreduce_tail(ctx, plan, out)
     return out, (None if copied else plan)
@@ -414,9 +433,9 @@ def _small_allreduce_tail(ctx: ShmemContext, plan, out: torch.Tensor) -> None:
     _, fixed, part_base, parity_bytes, flags_off, meta = plan
     epoch = ctx.epoch + 1
     stream = torch.cuda.current_stream(ctx.device).cuda_stream
-    nctx, parts_ptr, s, slice_elems, m, n, fmt = fixed
-    N.check(N.lib().catcoc_splitk_allreduce(C.byref(nctx), parts_ptr, s, slice_elems, m, n, out.data_ptr(), out.stride(0),
-                                            fmt, part_base + (epoch & 1) * parity_bytes, flags_off,
+    nctx, parts_ptr, s, slice_elems, m, n, row0, rows, fmt = fixed
+    N.check(N.lib().catcoc_splitk_allreduce(C.byref(nctx), parts_ptr, s, slice_elems, m, n, row0, rows, out.data_ptr(),
+                                            out.stride(0), fmt, part_base + (epoch & 1) * parity_bytes, flags_off,
                                             1 if ctx.mc_base else 0, ctx.launch_state.data_ptr(),
                                             ctx.launch_state.data_ptr() + 4, ctx.status.data_ptr(),
                                             cm.default_timeout_ns(), C.c_void_p(stream)))

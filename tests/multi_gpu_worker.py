@@ -172,6 +172,9 @@ def run_mixed_geometries(ctx, W, iters, name):
     cases.append(("ar_small", lambda: catcoc.matmul_allreduce(a6, b6), _DeviceCheck(gold6, 2048 * W, bf, pmag(a6, b6))))
     catcoc.matmul_allreduce(a6, b6)
     assert ctx.last_call.get("path", "").startswith("split-K"), ctx.last_call
+    sl6 = slice(rank * (128 // W), (rank + 1) * (128 // W))
+    cases.append(("rs_small", lambda: catcoc.matmul_reduce_scatter(a6, b6),
+                  _DeviceCheck(gold6[sl6], 2048 * W, bf, pmag(a6, b6)[sl6])))
     # the all-reduce result lives in the heap: the next call of another shape must not touch it
     keep = catcoc.matmul_allreduce(a2, b2, tiling=t_ar_cols)
     catcoc.matmul_allreduce(a5, b5, tiling=t_ar_rows)
@@ -244,11 +247,20 @@ if mode == "ops":
             o = catcoc.matmul_allreduce(a, b, trans_b=tb2)
             small = ctx.last_call.get("path", "").startswith("split-K")
             check("ar_oneshot_" + tag, o, gold, K2 * W, dtype, mag)
-            report("ar_oneshot_path_" + tag, small, str(ctx.last_call))
+            from mm_rs_with_catlass_b200.ops.fused import _SMALL_AR_MAX_M
+            report("ar_oneshot_path_" + tag, small == (M2 <= _SMALL_AR_MAX_M), str(ctx.last_call))
             given = torch.empty_like(o)
             check("ar_oneshot_out_" + tag, catcoc.matmul_allreduce(a, b, trans_b=tb2, out=given), gold, K2 * W, dtype, mag)
             check("ar_fused_" + tag, catcoc.matmul_allreduce(a, b, trans_b=tb2, tiling=catcoc.TilingConfig(bn=128)), gold,
                   K2 * W, dtype, mag)
+            if M2 % W == 0:
+                rws = M2 // W
+                sl2 = slice(rank * rws, (rank + 1) * rws)
+                o = catcoc.matmul_reduce_scatter(a, b, trans_b=tb2)
+                report("rs_oneshot_path_" + tag, ctx.last_call.get("path", "").endswith("reduce-scatter") == (M2 <= _SMALL_AR_MAX_M),
+                       str(ctx.last_call))
+                check("rs_oneshot_" + tag, o, gold[sl2], K2 * W, dtype, mag[sl2])
+                check("rs_oneshot_again_" + tag, catcoc.matmul_reduce_scatter(a, b, trans_b=tb2), gold[sl2], K2 * W, dtype, mag[sl2])
         a, b = matmul_inputs(96, 1024, 256, rank, dtype, dev, seed=11)
         gold = ref.matmul_allreduce(a, b, out_dtype=torch.float32)
         mag = pmag(a, b)

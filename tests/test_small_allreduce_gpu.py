@@ -35,11 +35,11 @@ def _setup(device, peer_stamped):
     return lib, N, ctx, heap, parts, out, state, status, part_bytes
 
 
-def _launch(lib, N, ctx, parts, out, state, status, part_bytes, timeout_ns):
+def _launch(lib, N, ctx, parts, out, state, status, part_bytes, timeout_ns, row0=0):
     stream = torch.cuda.current_stream(out.device).cuda_stream
-    return lib.catcoc_splitk_allreduce(C.byref(ctx), parts.data_ptr(), SLICES, ROWS * COLS, ROWS, COLS, out.data_ptr(),
-                                       out.stride(0), N.FMT_BF16, 0, part_bytes, 0, state.data_ptr(), state.data_ptr() + 4,
-                                       status.data_ptr(), timeout_ns, C.c_void_p(stream))
+    return lib.catcoc_splitk_allreduce(C.byref(ctx), parts.data_ptr(), SLICES, ROWS * COLS, ROWS, COLS, row0, out.shape[0],
+                                       out.data_ptr(), out.stride(0), N.FMT_BF16, 0, part_bytes, 0, state.data_ptr(),
+                                       state.data_ptr() + 4, status.data_ptr(), timeout_ns, C.c_void_p(stream))
 
 
 def test_sum_over_ranks_by_peer_loads_and_epoch_advance(device):
@@ -78,7 +78,19 @@ def test_argument_checks(device):
     lib, N, ctx, heap, parts, out, state, status, part_bytes = _setup(device, peer_stamped=True)
     odd = torch.empty((ROWS, 521), dtype=torch.bfloat16, device=device)
     stream = torch.cuda.current_stream(device).cuda_stream
-    rc = lib.catcoc_splitk_allreduce(C.byref(ctx), parts.data_ptr(), SLICES, ROWS * 521, ROWS, 521, odd.data_ptr(), 521,
-                                     N.FMT_BF16, 0, part_bytes, 0, state.data_ptr(), state.data_ptr() + 4,
+    rc = lib.catcoc_splitk_allreduce(C.byref(ctx), parts.data_ptr(), SLICES, ROWS * 521, ROWS, 521, 0, ROWS, odd.data_ptr(),
+                                     521, N.FMT_BF16, 0, part_bytes, 0, state.data_ptr(), state.data_ptr() + 4,
                                      status.data_ptr(), 0, C.c_void_p(stream))
     assert rc == N.E_ALIGNMENT                                     # rows of whole 16-byte vectors only
+    assert _launch(lib, N, ctx, parts, out[:10], state, status, part_bytes, 0, row0=ROWS - 5) == N.E_BAD_ARG   # rows past the end
+
+
+def test_reduce_scatter_keeps_a_row_range(device):
+    lib, N, ctx, heap, parts, out, state, status, part_bytes = _setup(device, peer_stamped=True)
+    row0, rows = 37, 29                                            # a range that starts and ends inside chunks
+    mine = torch.full((rows, COLS), float("nan"), dtype=torch.bfloat16, device=device)
+    assert _launch(lib, N, ctx, parts, mine, state, status, part_bytes, 2_000_000_000, row0=row0) == 0, N.last_error()
+    torch.cuda.synchronize(device)
+    assert status.tolist()[0] == 0 and state.tolist()[0] == 1
+    local = parts.sum(0).to(torch.bfloat16)
+    assert torch.equal(mine, (local[row0:row0 + rows].float() * 2).to(torch.bfloat16))
