@@ -146,7 +146,7 @@ def main(argv=None) -> int:
                 k, n = (n_full, k_full // world) if op == "allgather_matmul" else (k_full // world, n_full)
                 if op == "matmul_allreduce" and m > 8192:
                     continue
-                if op in ("allgather_matmul", "matmul_reduce_scatter") and m < 1024:
+                if op in ("allgather_matmul", "matmul_reduce_scatter") and m < 128:
                     continue
             prob = search.Problem(op, m_op, n, k, world, dname, bool(ta), bool(tb), bool(ctx.mc_base), ctx.heap_bytes)
             cands = search.candidates(prob, ints(args.bns), ints(args.pairs), ints(args.swizzles),
