@@ -158,6 +158,8 @@ def _declare(lib) -> None:
         "catcoc_splitk_reduce": (i32, [vp, i32, i64, i32, i32, vp, i64, i32, C.c_float, C.c_float, vp, i64, vp, vp]),
         "catcoc_splitk_allreduce_flag_words": (i64, [i32, i32, i32]),
         "catcoc_splitk_allreduce": (i32, [P(ShmemCtx), vp, i32, i64, i32, i32, i32, i32, vp, i64, i32, i64, i64, i32, vp, vp, vp, u64, vp]),
+        "catcoc_small_allgather_flag_words": (i64, [i32, i64, i32]),
+        "catcoc_small_allgather": (i32, [P(ShmemCtx), vp, i64, i32, i64, i64, i64, i64, i32, vp, vp, vp, u64, vp]),
         "catcoc_gemv_workspace_floats": (i64, [i32, i32, i32]),
         "catcoc_gemv": (i32, [vp, i64, i32, i32, i32, i32, vp, vp, vp, C.c_float, C.c_float, vp, vp]),
         "catcoc_flash_attention": (i32, [vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, C.c_float, vp, u64, vp]),

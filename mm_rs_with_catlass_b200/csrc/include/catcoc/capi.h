@@ -268,6 +268,15 @@ int catcoc_splitk_allreduce(const CatcocShmemCtx* ctx, const float* parts, int s
                             int use_multicast, uint32_t* epoch_ptr, uint32_t* cta_counter, uint32_t* status,
                             uint64_t timeout_ns, void* stream);
 
+/* All-gather of a small row-sharded activation (same file): this rank's shard [m rows of row_bytes bytes, pitch
+ * shard_pitch_bytes] lands in rows [rank * m, (rank + 1) * m) of every rank's buffer at heap offset gathered_off (pitch
+ * gathered_pitch_bytes; the parity half of this launch's epoch), and the call's kernel returns when all W shards have
+ * arrived in this rank's buffer. Stamps: catcoc_small_allgather_flag_words(...) words at flags_off. */
+int64_t catcoc_small_allgather_flag_words(int m, int64_t row_bytes, int W);
+int catcoc_small_allgather(const CatcocShmemCtx* ctx, const void* shard, int64_t shard_pitch_bytes, int m, int64_t row_bytes,
+                           int64_t gathered_off, int64_t gathered_pitch_bytes, int64_t flags_off, int use_multicast,
+                           uint32_t* epoch_ptr, uint32_t* cta_counter, uint32_t* status, uint64_t timeout_ns, void* stream);
+
 /* ---- flash attention forward (csrc/kernels/flash_attn.cu) ----
  * out[b, h, i, :] = softmax_j(scale * q[b, h, i, :] . k[b, g(h), j, :]) v[b, g(h), j, :] with q [B, Hq, Sq, D],
  * k / v [B, Hk, Sk, D] and out [B, Hq, Sq, D], all contiguous fp16 or bf16 (fmt = CATCOC_FMT_*), D = 64 or 128,

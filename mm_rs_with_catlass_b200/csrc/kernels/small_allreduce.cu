@@ -1,5 +1,5 @@
-// All-reduce for products with few output tiles and a long K (M up to a few hundred rows): the second half of a
-// two-launch path. The first launch is the GEMM kernel in its split-K form (K slices as the groups of one launch, fp32
+// Collectives for products with few output tiles and a long K (M up to a few hundred rows). First, the all-reduce /
+// reduce-scatter: the second half of a two-launch path. The first launch is the GEMM kernel in its split-K form (K slices as the groups of one launch, fp32
 // partial planes in a local workspace), so that every SM streams a share of B. This kernel then
 //   phase A  sums the planes of a chunk, rounds to the operand dtype, stores the chunk into this rank's symmetric
 //            buffer and stamps (chunk, rank) on every rank (one multimem.st through the switch, or a store per peer);
@@ -159,6 +159,101 @@ __global__ void __launch_bounds__(kThreads) splitk_allreduce_kernel(const SmallA
   }
 }
 
+
+// ---------------------------------------------------------------------------------------------------------------
+// All-gather of a small row-sharded activation, the first launch of the all-gather GEMM for few rows: every rank
+// copies its shard [m, row_bytes] into rows [rank m, (rank + 1) m) of EVERY rank's gathered buffer (one multimem.st
+// per 16 bytes, or a store per peer), stamps (chunk, rank) everywhere, then waits until the chunks of all W sources
+// have landed in its own buffer. The split-K product that follows reads the gathered rows from local memory.
+struct SmallAgParams {
+  const uint8_t* shard;       // [m rows], pitch shard_pitch bytes, 16-byte aligned rows
+  int64_t shard_pitch;
+  int m;
+  int64_t row_bytes;          // bytes copied per row (a multiple of 16)
+  int64_t dst_pitch;          // pitch of the gathered buffer
+  int rank, W;
+  uint8_t* gathered[8];       // every rank's buffer half of this epoch
+  uint8_t* gathered_mc;
+  uint32_t* flags[8];         // stamp words [chunk][source]
+  uint32_t* flags_mc;
+  uint32_t* epoch_ptr;
+  uint32_t* cta_counter;
+  uint32_t* status;
+  uint64_t timeout_ns;
+};
+
+__global__ void __launch_bounds__(kThreads) small_allgather_kernel(const SmallAgParams p) {
+  __shared__ uint32_t s_fail[4];
+  const int tid = threadIdx.x;
+  if (*p.status != 0u) return;
+  const uint32_t epoch = ptx::ld_relaxed_sys_u32(p.epoch_ptr) + 1u;
+  const int64_t vec_per_row = p.row_bytes >> 4;
+  const int64_t total = vec_per_row * p.m;                       // 16-byte vectors of the shard
+  const int64_t chunks = (total + kThreads - 1) / kThreads;      // one vector per thread and chunk
+  if (tid == 0) s_fail[0] = 0u;
+  __syncthreads();
+
+  // ---- phase A: send the shard ----
+  for (int64_t c = blockIdx.x; c < chunks; c += gridDim.x) {
+    const int64_t v = c * kThreads + tid;
+    if (v < total) {
+      const int64_t row = v / vec_per_row, u = v - row * vec_per_row;
+      const uint4 x = ptx::ld_global_nc_v4(p.shard + row * p.shard_pitch + (u << 4));
+      const int64_t off = (static_cast<int64_t>(p.rank) * p.m + row) * p.dst_pitch + (u << 4);
+      if (p.gathered_mc != nullptr) ptx::multimem_st_v4(p.gathered_mc + off, x);
+      else
+        for (int q = 0; q < p.W; ++q) ptx::st_global_v4(p.gathered[q] + off, x);
+    }
+    __syncthreads();
+    if (p.flags_mc != nullptr) {
+      if (tid == 0) { ptx::fence_acq_rel_sys(); ptx::multimem_st_release_u32(p.flags_mc + c * p.W + p.rank, epoch); }
+    } else if (tid < p.W) {
+      ptx::fence_acq_rel_sys();
+      ptx::st_release_sys_u32(p.flags[tid] + c * p.W + p.rank, epoch);
+    }
+  }
+
+  // ---- phase B: wait for every source's chunks ----
+  bool failed = false;
+  for (int64_t c = blockIdx.x; c < chunks && !failed; c += gridDim.x) {
+    if (tid < p.W) {
+      const uint32_t* f = p.flags[p.rank] + c * p.W + tid;
+      const uint64_t t0 = ptx::globaltimer_ns();
+      uint32_t spins = 0;
+      while (true) {
+        const uint32_t v = ptx::ld_acquire_sys_u32(f);
+        if (static_cast<int32_t>(v - epoch) >= 0) break;
+        if ((++spins & 0xf) == 0) {
+          if (ptx::globaltimer_ns() - t0 > p.timeout_ns || *reinterpret_cast<volatile uint32_t*>(p.status) != 0u) {
+            if (atomicCAS(&s_fail[0], 0u, 1u) == 0u) { s_fail[1] = tid; s_fail[2] = v; s_fail[3] = static_cast<uint32_t>(c); }
+            break;
+          }
+          __nanosleep(64);
+        }
+      }
+    }
+    __syncthreads();
+    if (s_fail[0] != 0u) failed = true;
+  }
+  if (failed && tid == 0) {
+    if (atomicCAS(p.status, 0u, static_cast<uint32_t>(STATUS_TIMEOUT_GATHER)) == 0u) {
+      p.status[1] = epoch; p.status[2] = 301u; p.status[3] = epoch; p.status[4] = s_fail[2]; p.status[5] = s_fail[1];
+      p.status[6] = blockIdx.x; p.status[7] = s_fail[3];
+      __threadfence_system();
+    }
+  }
+  __syncthreads();
+  if (tid == 0) {
+    __threadfence();
+    const uint32_t prev = atomicAdd(p.cta_counter, 1u);
+    if (prev == gridDim.x - 1) {
+      *p.cta_counter = 0;
+      __threadfence();
+      if (*p.status == 0u) *p.epoch_ptr = epoch;
+    }
+  }
+}
+
 }  // namespace
 }  // namespace catcoc
 
@@ -206,4 +301,44 @@ extern "C" int catcoc_splitk_allreduce(const CatcocShmemCtx* ctx, const float* p
 extern "C" int64_t catcoc_splitk_allreduce_flag_words(int rows, int cols, int W) {
   const int64_t total = static_cast<int64_t>(rows) * cols;
   return (total + kChunkElems - 1) / kChunkElems * W;
+}
+
+extern "C" int64_t catcoc_small_allgather_flag_words(int m, int64_t row_bytes, int W) {
+  const int64_t total = (row_bytes >> 4) * m;
+  return (total + kThreads - 1) / kThreads * W;
+}
+
+extern "C" int catcoc_small_allgather(const CatcocShmemCtx* ctx, const void* shard, int64_t shard_pitch_bytes, int m,
+                                      int64_t row_bytes, int64_t gathered_off, int64_t gathered_pitch_bytes,
+                                      int64_t flags_off, int use_multicast, uint32_t* epoch_ptr, uint32_t* cta_counter,
+                                      uint32_t* status, uint64_t timeout_ns, void* stream) {
+  if (ctx == nullptr || shard == nullptr || epoch_ptr == nullptr || cta_counter == nullptr || status == nullptr || m <= 0 ||
+      row_bytes <= 0 || ctx->W < 2 || ctx->W > 8) {
+    host::set_error("small_allgather: bad argument");
+    return CATCOC_E_BAD_ARG;
+  }
+  if ((row_bytes & 15) != 0 || (shard_pitch_bytes & 15) != 0 || (gathered_pitch_bytes & 15) != 0 || (gathered_off & 15) != 0 ||
+      (reinterpret_cast<uintptr_t>(shard) & 15) != 0 || (flags_off & 3) != 0 || gathered_pitch_bytes < row_bytes ||
+      shard_pitch_bytes < row_bytes) {
+    host::set_error("small_allgather: rows of whole 16-byte vectors and 16-byte aligned buffers are required");
+    return CATCOC_E_ALIGNMENT;
+  }
+  SmallAgParams p;
+  p.shard = static_cast<const uint8_t*>(shard); p.shard_pitch = shard_pitch_bytes; p.m = m; p.row_bytes = row_bytes;
+  p.dst_pitch = gathered_pitch_bytes;
+  p.rank = ctx->rank; p.W = ctx->W;
+  for (int q = 0; q < 8; ++q) {
+    p.gathered[q] = q < ctx->W ? static_cast<uint8_t*>(ctx->base[q]) + gathered_off : nullptr;
+    p.flags[q] = q < ctx->W ? reinterpret_cast<uint32_t*>(static_cast<uint8_t*>(ctx->base[q]) + flags_off) : nullptr;
+  }
+  const bool mc = use_multicast && ctx->mc_base != nullptr;
+  p.gathered_mc = mc ? static_cast<uint8_t*>(ctx->mc_base) + gathered_off : nullptr;
+  p.flags_mc = mc ? reinterpret_cast<uint32_t*>(static_cast<uint8_t*>(ctx->mc_base) + flags_off) : nullptr;
+  p.epoch_ptr = epoch_ptr; p.cta_counter = cta_counter; p.status = status;
+  p.timeout_ns = timeout_ns ? timeout_ns : 10000000000ull;
+  const int64_t chunks = ((row_bytes >> 4) * m + kThreads - 1) / kThreads;
+  const int grid = static_cast<int>(chunks < 148 * 4 ? chunks : 148 * 4);
+  small_allgather_kernel<<<grid, kThreads, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  CATCOC_CUDA_OK(cudaGetLastError());
+  return CATCOC_OK;
 }

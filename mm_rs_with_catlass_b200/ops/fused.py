@@ -531,6 +531,92 @@ def matmul_allreduce(a: torch.Tensor, b: torch.Tensor, *, trans_a: bool = False,
 
 
 # ---------------------------------------------------------------------------------------
+# Few rows: gather kernel + split-K product + plane reduction (three launches of this library's kernels).
+_SMALL_AG_MAX_M = int(os.environ.get("CATCOC_SMALL_AG_MAX_M", "256"))
+
+
+def _small_allgather_wanted(m_total: int, n: int, k: int, elt: int, a_shard: torch.Tensor) -> bool:
+    """As for the all-reduce: one wave of tiles (N_local / bn CTAs, each streaming all of the gathered A)
+    leaves most SMs idle, so the product is cut along K instead and the shard travels first."""
+    if m_total > _SMALL_AG_MAX_M or n % 8 or n < 128 or (k * elt) % 16:
+        return False
+    if a_shard.stride(-1) != 1 or (a_shard.stride(0) * elt) % 16 or a_shard.data_ptr() % 16:
+        return False
+    from .blas import splitk_plan
+    return splitk_plan(m_total, n, k, elt)[0] >= 2
+
+
+def _small_allgather_run(ctx: ShmemContext, plan: dict, a_shard: torch.Tensor, b: torch.Tensor, out: torch.Tensor):
+    from .blas import splitk_partials
+    lib = N.lib()
+    dev = ctx.device
+    epoch = ctx.epoch + 1
+    par = epoch & 1
+    stream = torch.cuda.current_stream(dev).cuda_stream
+    code = lib.catcoc_small_allgather(C.byref(plan["nctx"]), a_shard.data_ptr(), a_shard.stride(0) * plan["elt"], plan["m"],
+                                      plan["k"] * plan["elt"], plan["g_off"] + par * plan["parity_bytes"],
+                                      plan["k"] * plan["elt"], plan["flags_off"], 1 if ctx.mc_base else 0,
+                                      ctx.launch_state.data_ptr(), ctx.launch_state.data_ptr() + 4, ctx.status.data_ptr(),
+                                      cm.default_timeout_ns(), C.c_void_p(stream))
+    if code < 0:
+        N.check(code)
+    ctx.epoch = epoch
+    gview = plan["views"][par]
+    if plan["gemm"][par] is None:
+        kept: list = []
+        splitk_partials(gview, b, split_k=plan["s"], trans_b=plan["trans_b"], tiling=TilingConfig(bn=plan["bn"], cta_pair=1),
+                        part=plan["part"], _args_out=kept)
+        if plan["plannable"]:
+            plan["gemm"][par] = kept[0]
+    else:
+        cm.launch(plan["gemm"][par], dev)
+    mt, n = plan["mt"], plan["n"]
+    code = lib.catcoc_splitk_reduce(plan["part"].data_ptr(), plan["s"], mt * n, mt, n, out.data_ptr(), out.stride(0),
+                                    cm.out_fmt(out.dtype), 1.0, 0.0, None, n, None, C.c_void_p(stream))
+    if code < 0:
+        N.check(code)
+    ctx.counters["launches"] += 3
+    ctx.counters["bytes_out"] += plan["meta"]["bytes_out"]
+    ctx.last_call = plan["meta"]
+    return out, gview
+
+
+def _small_allgather(ctx: ShmemContext, a_shard: torch.Tensor, b: torch.Tensor, trans_b: bool, m: int, n: int, k: int,
+                     out: torch.Tensor):
+    """``cat_q(A_q) @ B_r`` for few rows: ``small_allgather_kernel`` sends the shard to every rank
+    (multicast stores, or a store per peer) and waits for the other shards, the GEMM kernel runs in
+    its split-K form on the gathered rows, a third kernel folds the planes. Returns ``(out, gathered, plan)``."""
+    from .blas import splitk_plan
+    lib = N.lib()
+    dev = a_shard.device
+    elt = a_shard.element_size()
+    W = ctx.world
+    mt = W * m
+    s, bn = splitk_plan(mt, n, k, elt)
+    if mt % 128 and bn > 128:
+        bn = 128
+    with torch.cuda.device(dev):
+        scratch = ctx.__dict__.setdefault("local_scratch", {})
+        ws = scratch.get("small_ar_planes")
+        if ws is None or ws.numel() < s * mt * n:
+            ws = torch.empty(max(s * mt * n, 1 << 22), dtype=torch.float32, device=dev)
+            scratch["small_ar_planes"] = ws
+            _plans_of(ctx).clear()
+        gbuf, parity_bytes = _data_region(ctx, "gathered_small", mt * k * elt)
+        flags = ctx.stamps(("small_ag", m, k * elt, W), int(lib.catcoc_small_allgather_flag_words(m, k * elt, W)))
+        ob = cm.as_operand(b, trans_b)
+        plan = dict(nctx=ctx.native_ctx(), elt=elt, m=m, mt=mt, n=n, k=k, s=s, bn=bn, trans_b=trans_b, g_off=gbuf.offset,
+                    parity_bytes=parity_bytes, flags_off=flags.offset, part=ws[:s * mt * n].view(s * mt, n),
+                    views=[gbuf.tensor(a_shard.dtype, (mt, k), byte_offset=par * parity_bytes) for par in (0, 1)],
+                    gemm=[None, None], plannable=not ob.copied,
+                    meta=dict(op="allgather_matmul", path="gather kernel + split-K product", split_k=s, bn=bn,
+                              multicast=bool(ctx.mc_base), m=mt, n=n, k=k,
+                              bytes_out=(1 if ctx.mc_base else W - 1) * m * k * elt))
+        o, g = _small_allgather_run(ctx, plan, a_shard, b, out)
+    return o, g, plan
+
+
+# ---------------------------------------------------------------------------------------
 def allgather_matmul(a_shard: torch.Tensor, b: torch.Tensor, *, trans_b: bool = False,
                      out: Optional[torch.Tensor] = None, tiling: Optional[TilingConfig] = None,
                      activation: Optional[str] = None,
@@ -554,6 +640,12 @@ def allgather_matmul(a_shard: torch.Tensor, b: torch.Tensor, *, trans_b: bool = 
     """
     ctx = _ctx(ctx)
     key = ("ag", cm.tkey(a_shard), cm.tkey(b), trans_b, cm.tkey(out), tiling, activation)
+    if tiling is None and activation is None:
+        small = _plan_hit(ctx, ("ag_small",) + key[1:])
+        if small is not None:
+            if out is None:
+                out = torch.empty((small["mt"], small["n"]), dtype=a_shard.dtype, device=ctx.device)
+            return _small_allgather_run(ctx, small, a_shard, b, out)
     plan = _plan_hit(ctx, key)
     if plan is not None:
         args, out_shape, out_dtype, gviews = plan
@@ -580,6 +672,11 @@ def allgather_matmul(a_shard: torch.Tensor, b: torch.Tensor, *, trans_b: bool = 
     if tuple(out.shape) != (W * m, n) or out.stride(-1) != 1 or out.dtype != a_shard.dtype:
         raise ValueError("out must be a row-major [%d, %d] %s tensor" % (W * m, n, a_shard.dtype))
     elt = a_shard.element_size()
+    if tiling is None and activation is None and _small_allgather_wanted(W * m, n, k, elt, a_shard):
+        o, g, small = _small_allgather(ctx, a_shard, b, trans_b, m, n, k, out)
+        if small["plannable"]:
+            _plan_put(ctx, ("ag_small",) + key[1:], small)
+        return o, g
     t = _resolve_tiling("allgather_matmul", W * m, n, k, W, a_shard.dtype, tiling)
     lib = N.lib()
     with torch.cuda.device(dev):

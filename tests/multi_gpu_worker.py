@@ -175,6 +175,13 @@ def run_mixed_geometries(ctx, W, iters, name):
     sl6 = slice(rank * (128 // W), (rank + 1) * (128 // W))
     cases.append(("rs_small", lambda: catcoc.matmul_reduce_scatter(a6, b6),
                   _DeviceCheck(gold6[sl6], 2048 * W, bf, pmag(a6, b6)[sl6])))
+    # few rows in an all-gather GEMM: gather kernel + split-K product + plane reduction
+    a7, b7 = matmul_inputs(64 // W if W <= 4 else 8, 512, 4096, rank, bf, dev, seed=207)
+    gold7, ggold7 = ref.allgather_matmul(a7, b7, out_dtype=torch.float32)
+    cases.append(("ag_small", lambda: catcoc.allgather_matmul(a7, b7)[0], _DeviceCheck(gold7, 4096, bf)))
+    _, gath7 = catcoc.allgather_matmul(a7, b7)
+    assert ctx.last_call.get("path", "").startswith("gather kernel"), ctx.last_call
+    assert torch.equal(gath7, ggold7.to(bf)), "gathered activation of the small all-gather path"
     # the all-reduce result lives in the heap: the next call of another shape must not touch it
     keep = catcoc.matmul_allreduce(a2, b2, tiling=t_ar_cols)
     catcoc.matmul_allreduce(a5, b5, tiling=t_ar_rows)
@@ -261,6 +268,20 @@ if mode == "ops":
                        str(ctx.last_call))
                 check("rs_oneshot_" + tag, o, gold[sl2], K2 * W, dtype, mag[sl2])
                 check("rs_oneshot_again_" + tag, catcoc.matmul_reduce_scatter(a, b, trans_b=tb2), gold[sl2], K2 * W, dtype, mag[sl2])
+        # few rows in an all-gather GEMM: gather kernel + split-K product (auto tiling), fused kernel with a tiling
+        for (m3, N3, K3, tb3) in [(16, 1024, 4096, False), (24, 520, 2048, True), (1, 256, 8192, False)]:
+            a, b = matmul_inputs(m3, N3, K3, rank, dtype, dev, trans_b=tb3, seed=m3 + K3)
+            gold, ggold = ref.allgather_matmul(a, b, trans_b=tb3, out_dtype=torch.float32)
+            tag = "%s_%dx%dx%d_%d" % (str(dtype)[6:], m3, N3, K3, tb3)
+            o, gath = catcoc.allgather_matmul(a, b, trans_b=tb3)
+            report("ag_small_path_" + tag, ctx.last_call.get("path", "").startswith("gather kernel"), str(ctx.last_call))
+            check("ag_small_" + tag, o, gold, K3, dtype)
+            report("ag_small_gathered_" + tag, bool(torch.equal(gath, ggold.to(dtype))))
+            o, gath = catcoc.allgather_matmul(a, b, trans_b=tb3)            # planned call, other buffer half
+            check("ag_small_again_" + tag, o, gold, K3, dtype)
+            report("ag_small_gathered_again_" + tag, bool(torch.equal(gath, ggold.to(dtype))))
+            o, _ = catcoc.allgather_matmul(a, b, trans_b=tb3, tiling=catcoc.TilingConfig(bn=128))
+            check("ag_fused_" + tag, o, gold, K3, dtype)
         a, b = matmul_inputs(96, 1024, 256, rank, dtype, dev, seed=11)
         gold = ref.matmul_allreduce(a, b, out_dtype=torch.float32)
         mag = pmag(a, b)

@@ -39,3 +39,33 @@ def test_cpu_tensors_are_refused():
                  lambda: blas.gemv(a, a[0])):
         with pytest.raises(RuntimeError, match="CUDA"):
             call()
+
+
+def test_slices_are_whole_pipeline_stages_and_cover_k():
+    for k, s, elt in [(14336, 4, 2), (7168, 16, 2), (1000, 3, 2), (8192, 5, 1), (96, 8, 2)]:
+        ks, n = blas.slice_k(k, s, elt)
+        assert ks % (256 // elt) == 0                  # a slice is a whole number of 256-byte K stages
+        assert (n - 1) * ks < k <= n * ks and n <= s   # the slices cover K, the last one may be short
+
+
+def test_splitk_plan_prefers_wide_tiles_cut_into_more_slices():
+    # 128 x 8192 x 14336: 32 tiles of 256 columns x 4 slices stream (128 + 256) * 3584 elements per CTA,
+    # 64 tiles of 128 columns x 2 slices (128 + 128) * 7168: the wide tiles win
+    assert blas.splitk_plan(128, 8192, 14336, 2) == (4, 256)
+    s, bn = blas.splitk_plan(128, 8192, 7168, 2)
+    assert bn == 256 and s == 4
+    # nothing to cut: a short K, or tiles enough for every SM
+    assert blas.splitk_plan(128, 8192, 256, 2)[0] == 1
+    assert blas.splitk_plan(4096, 8192, 8192, 2)[0] == 1
+    # a narrow output cannot take 256-column tiles
+    assert blas.splitk_plan(64, 128, 32768, 2)[1] == 128
+
+
+def test_small_allreduce_is_chosen_for_few_rows_and_a_long_k_only():
+    from mm_rs_with_catlass_b200.ops import fused
+    assert fused._small_allreduce_wanted(128, 8192, 14336, 2)
+    assert fused._small_allreduce_wanted(1, 128, 8192, 2)
+    assert not fused._small_allreduce_wanted(fused._SMALL_AR_MAX_M + 1, 8192, 14336, 2)
+    assert not fused._small_allreduce_wanted(128, 8192, 256, 2)        # K too short to cut
+    assert not fused._small_allreduce_wanted(128, 8190, 14336, 2)      # rows of whole 16-byte vectors only
+    assert not fused._small_allreduce_wanted(128, 64, 14336, 2)        # narrower than one tile
