@@ -94,3 +94,56 @@ def test_reduce_scatter_keeps_a_row_range(device):
     assert status.tolist()[0] == 0 and state.tolist()[0] == 1
     local = parts.sum(0).to(torch.bfloat16)
     assert torch.equal(mine, (local[row0:row0 + rows].float() * 2).to(torch.bfloat16))
+
+
+def _gather_setup(device, peer_stamped, m=24, cols=520):
+    from mm_rs_with_catlass_b200 import _native as N
+    lib = N.lib()
+    row_bytes = cols * 2
+    words = int(lib.catcoc_small_allgather_flag_words(m, row_bytes, 2))
+    g_bytes = (2 * m * row_bytes + 255) // 256 * 256
+    heap = torch.zeros(g_bytes + 4 * words, dtype=torch.uint8, device=device)
+    if peer_stamped:
+        heap[g_bytes:].view(torch.int32).view(-1, 2)[:, 1] = 1
+    ctx = N.ShmemCtx()
+    ctx.rank, ctx.W = 0, 2
+    ctx.base[0] = ctx.base[1] = heap.data_ptr()
+    ctx.mc_base = None
+    g = torch.Generator(device=device)
+    g.manual_seed(5)
+    wide = torch.randn(m, cols + 24, device=device, generator=g).to(torch.bfloat16)
+    shard = wide[:, :cols]                                          # a pitch wider than the row
+    state = torch.zeros(2, dtype=torch.int32, device=device)
+    status = torch.zeros(8, dtype=torch.int32, device=device)
+    return lib, N, ctx, heap, shard, state, status, g_bytes, m, cols
+
+
+def _gather(lib, N, ctx, shard, state, status, g_bytes, m, cols, timeout_ns):
+    stream = torch.cuda.current_stream(shard.device).cuda_stream
+    return lib.catcoc_small_allgather(C.byref(ctx), shard.data_ptr(), shard.stride(0) * 2, m, cols * 2, 0, cols * 2, g_bytes, 0,
+                                      state.data_ptr(), state.data_ptr() + 4, status.data_ptr(), timeout_ns,
+                                      C.c_void_p(stream))
+
+
+def test_gather_kernel_places_the_shard_and_advances_the_epoch(device):
+    lib, N, ctx, heap, shard, state, status, g_bytes, m, cols = _gather_setup(device, peer_stamped=True)
+    assert _gather(lib, N, ctx, shard, state, status, g_bytes, m, cols, 2_000_000_000) == 0, N.last_error()
+    torch.cuda.synchronize(device)
+    assert status.tolist()[0] == 0 and state.tolist() == [1, 0]
+    gathered = heap[:2 * m * cols * 2].view(torch.bfloat16).view(2 * m, cols)
+    assert torch.equal(gathered[:m], shard)                         # rank 0's rows
+    assert torch.count_nonzero(gathered[m:]) == 0                   # the peer's rows are the peer's to write
+
+
+def test_gather_kernel_gives_up_on_a_shard_that_never_comes(device):
+    lib, N, ctx, heap, shard, state, status, g_bytes, m, cols = _gather_setup(device, peer_stamped=False)
+    assert _gather(lib, N, ctx, shard, state, status, g_bytes, m, cols, 20_000_000) == 0, N.last_error()
+    torch.cuda.synchronize(device)
+    st = status.tolist()
+    assert st[0] == 4 and st[5] == 1, st                            # STATUS_TIMEOUT_GATHER, source 1
+    assert state.tolist()[0] == 0
+    bad = shard[:, 1:]                                              # rows that do not start on 16 bytes
+    stream = torch.cuda.current_stream(device).cuda_stream
+    rc = lib.catcoc_small_allgather(C.byref(ctx), bad.data_ptr(), bad.stride(0) * 2, m, (cols - 8) * 2, 0, cols * 2, g_bytes, 0,
+                                    state.data_ptr(), state.data_ptr() + 4, status.data_ptr(), 0, C.c_void_p(stream))
+    assert rc == N.E_ALIGNMENT
