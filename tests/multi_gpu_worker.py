@@ -264,8 +264,9 @@ if mode == "ops":
                 rws = M2 // W
                 sl2 = slice(rank * rws, (rank + 1) * rws)
                 o = catcoc.matmul_reduce_scatter(a, b, trans_b=tb2)
-                report("rs_oneshot_path_" + tag, ctx.last_call.get("path", "").endswith("reduce-scatter") == (M2 <= _SMALL_AR_MAX_M),
-                       str(ctx.last_call))
+                from mm_rs_with_catlass_b200.ops.fused import _small_reduce_scatter_wanted
+                report("rs_oneshot_path_" + tag, ctx.last_call.get("path", "").endswith("reduce-scatter")
+                       == _small_reduce_scatter_wanted(M2, N2, K2, a.element_size(), W), str(ctx.last_call))
                 check("rs_oneshot_" + tag, o, gold[sl2], K2 * W, dtype, mag[sl2])
                 check("rs_oneshot_again_" + tag, catcoc.matmul_reduce_scatter(a, b, trans_b=tb2), gold[sl2], K2 * W, dtype, mag[sl2])
         # few rows in an all-gather GEMM: gather kernel + split-K product (auto tiling), fused kernel with a tiling

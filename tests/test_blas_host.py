@@ -69,3 +69,12 @@ def test_small_allreduce_is_chosen_for_few_rows_and_a_long_k_only():
     assert not fused._small_allreduce_wanted(128, 8192, 256, 2)        # K too short to cut
     assert not fused._small_allreduce_wanted(128, 8190, 14336, 2)      # rows of whole 16-byte vectors only
     assert not fused._small_allreduce_wanted(128, 64, 14336, 2)        # narrower than one tile
+
+
+def test_reduce_scatter_takes_the_few_row_path_while_a_rank_keeps_less_than_a_tile():
+    from mm_rs_with_catlass_b200.ops import fused
+    assert fused._small_reduce_scatter_wanted(128, 8192, 14336, 2, 2)       # as the all-reduce
+    assert fused._small_reduce_scatter_wanted(256, 8192, 3584, 2, 8)        # 32 rows per rank
+    assert fused._small_reduce_scatter_wanted(256, 8192, 7168, 2, 4)        # 64 rows per rank
+    assert not fused._small_reduce_scatter_wanted(256, 8192, 14336, 2, 2)   # a full 128-row tile per rank: fused kernel
+    assert not fused._small_reduce_scatter_wanted(512, 8192, 3584, 2, 8)    # enough tiles for every SM: nothing to cut
