@@ -65,13 +65,14 @@ CATCOC_DEVICE void fail(const AttnParams& p, uint32_t what, uint32_t a, uint32_t
   }
 }
 
-CATCOC_DEVICE uint32_t pack16(float lo, float hi, int fmt) {
-  if (fmt == FMT_BF16) { __nv_bfloat162 hh = __floats2bfloat162_rn(lo, hi); return *reinterpret_cast<uint32_t*>(&hh); }
-  __half2 hh = __floats2half2_rn(lo, hi);
-  return *reinterpret_cast<uint32_t*>(&hh);
+template <int FMT>
+CATCOC_DEVICE uint32_t pack16(float lo, float hi) {
+  if constexpr (FMT == FMT_BF16) { __nv_bfloat162 hh = __floats2bfloat162_rn(lo, hi); return *reinterpret_cast<uint32_t*>(&hh); }
+  else { __half2 hh = __floats2half2_rn(lo, hi); return *reinterpret_cast<uint32_t*>(&hh); }
 }
 
-template <int D>
+// D: head dimension; FMT: operand and output dtype (compile time: the softmax loop packs 64 pairs per row and block)
+template <int D, int FMT>
 __global__ void __launch_bounds__(kThreads, 1) flash_attn_kernel(const __grid_constant__ AttnParams p) {
   constexpr int kDB = D / 64;                    // 128-byte blocks along the head dimension
   constexpr int kQBytes = kDB * kBlockBytes;     // one Q tile
@@ -278,16 +279,22 @@ __global__ void __launch_bounds__(kThreads, 1) flash_attn_kernel(const __grid_co
         uint32_t v[32], w[16];
         ptx::tmem_ld_32x32b_x32(t_s + c * 32, v);
         ptx::tcgen05_wait_ld();
+        if (masked) {
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          float e0 = ptx::ex2_approx(fmaf(__uint_as_float(v[i]), sc, -m_safe));
-          float e1 = ptx::ex2_approx(fmaf(__uint_as_float(v[i + 1]), sc, -m_safe));
-          if (masked) {
-            if (key0 + c * 32 + i >= vis) e0 = 0.0f;
-            if (key0 + c * 32 + i + 1 >= vis) e1 = 0.0f;
+          for (int i = 0; i < 32; i += 2) {
+            const float e0 = (key0 + c * 32 + i < vis) ? ptx::ex2_approx(fmaf(__uint_as_float(v[i]), sc, -m_safe)) : 0.0f;
+            const float e1 = (key0 + c * 32 + i + 1 < vis) ? ptx::ex2_approx(fmaf(__uint_as_float(v[i + 1]), sc, -m_safe)) : 0.0f;
+            sum += e0 + e1;
+            w[i >> 1] = pack16<FMT>(e0, e1);
           }
-          sum += e0 + e1;
-          w[i >> 1] = pack16(e0, e1, p.fmt);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            const float e0 = ptx::ex2_approx(fmaf(__uint_as_float(v[i]), sc, -m_safe));
+            const float e1 = ptx::ex2_approx(fmaf(__uint_as_float(v[i + 1]), sc, -m_safe));
+            sum += e0 + e1;
+            w[i >> 1] = pack16<FMT>(e0, e1);
+          }
         }
         ptx::tmem_st_32x32b_x16(t_s + c * 16, w);
       }
@@ -328,7 +335,7 @@ __global__ void __launch_bounds__(kThreads, 1) flash_attn_kernel(const __grid_co
             uint32_t w[4];
 #pragma unroll
             for (int e = 0; e < 4; ++e)
-              w[e] = pack16(__uint_as_float(v[u * 8 + 2 * e]) * inv, __uint_as_float(v[u * 8 + 2 * e + 1]) * inv, p.fmt);
+              w[e] = pack16<FMT>(__uint_as_float(v[u * 8 + 2 * e]) * inv, __uint_as_float(v[u * 8 + 2 * e + 1]) * inv);
             ptx::st_global_v4(orow + c * 64 + u * 16, make_uint4(w[0], w[1], w[2], w[3]));
           }
         }
@@ -404,15 +411,17 @@ extern "C" int catcoc_flash_attention(const void* q, const void* k, const void* 
   const int slots = D == 128 ? 4 : 8;
   const size_t smem = static_cast<size_t>(attn::kTiles * db + slots * db) * attn::kBlockBytes + sizeof(attn::Bars) + 1024 + 64;
   cudaError_t e;
-  if (D == 128) {
-    static cudaError_t once = cudaFuncSetAttribute(attn::flash_attn_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
-    if (once != cudaSuccess) { set_error("cudaFuncSetAttribute failed: %s", cudaGetErrorString(once)); return -1000 - static_cast<int>(once); }
-    attn::flash_attn_kernel<128><<<grid, attn::kThreads, smem, static_cast<cudaStream_t>(stream)>>>(p);
-  } else {
-    static cudaError_t once = cudaFuncSetAttribute(attn::flash_attn_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
-    if (once != cudaSuccess) { set_error("cudaFuncSetAttribute failed: %s", cudaGetErrorString(once)); return -1000 - static_cast<int>(once); }
-    attn::flash_attn_kernel<64><<<grid, attn::kThreads, smem, static_cast<cudaStream_t>(stream)>>>(p);
-  }
+  auto launch = [&](auto kernel) -> int {
+    // (one attribute call per launch: it is cheap and keeps the four instantiations in one place)
+    cudaError_t a = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    if (a != cudaSuccess) { set_error("cudaFuncSetAttribute failed: %s", cudaGetErrorString(a)); return -1000 - static_cast<int>(a); }
+    kernel<<<grid, attn::kThreads, smem, static_cast<cudaStream_t>(stream)>>>(p);
+    return 0;
+  };
+  int lrc;
+  if (D == 128) lrc = fmt == CATCOC_FMT_BF16 ? launch(attn::flash_attn_kernel<128, FMT_BF16>) : launch(attn::flash_attn_kernel<128, FMT_F16>);
+  else lrc = fmt == CATCOC_FMT_BF16 ? launch(attn::flash_attn_kernel<64, FMT_BF16>) : launch(attn::flash_attn_kernel<64, FMT_F16>);
+  if (lrc != 0) return lrc;
   e = cudaGetLastError();
   if (e != cudaSuccess) { set_error("flash_attention launch failed: %s", cudaGetErrorString(e)); return -1000 - static_cast<int>(e); }
   return CATCOC_OK;
