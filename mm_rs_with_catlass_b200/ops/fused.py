@@ -358,25 +358,30 @@ def _small_allreduce_wanted(m: int, n: int, k: int, elt: int) -> bool:
     return splitk_plan(m, n, k, elt)[0] >= 2
 
 
-def _small_allreduce_call(ctx: ShmemContext, plan, out: torch.Tensor) -> torch.Tensor:
-    """Queues the two launches of a planned small all-reduce and advances the host mirror of the epoch."""
-    gemm_args, fixed, part_base, parity_bytes, flags_off, meta = plan
-    dev = ctx.device
-    cm.launch(gemm_args, dev)
+def _small_allreduce_tail(ctx: ShmemContext, plan, out: torch.Tensor) -> None:
+    """The second launch of the few-row path (fold the planes, publish, stamp, reduce through the
+    switch) and the host-side bookkeeping of the whole call."""
+    _, fixed, part_base, parity_bytes, flags_off, meta = plan
     epoch = ctx.epoch + 1
-    stream = torch.cuda.current_stream(dev).cuda_stream
+    stream = torch.cuda.current_stream(ctx.device).cuda_stream
     nctx, parts_ptr, s, slice_elems, m, n, row0, rows, fmt = fixed
     code = N.lib().catcoc_splitk_allreduce(C.byref(nctx), parts_ptr, s, slice_elems, m, n, row0, rows, out.data_ptr(),
-                                           out.stride(0), fmt,
-                                           part_base + (epoch & 1) * parity_bytes, flags_off, 1 if ctx.mc_base else 0,
-                                           ctx.launch_state.data_ptr(), ctx.launch_state.data_ptr() + 4,
-                                           ctx.status.data_ptr(), cm.default_timeout_ns(), C.c_void_p(stream))
+                                           out.stride(0), fmt, part_base + (epoch & 1) * parity_bytes, flags_off,
+                                           1 if ctx.mc_base else 0, ctx.launch_state.data_ptr(),
+                                           ctx.launch_state.data_ptr() + 4, ctx.status.data_ptr(),
+                                           cm.default_timeout_ns(), C.c_void_p(stream))
     if code < 0:
         N.check(code)
     ctx.epoch = epoch
     ctx.counters["launches"] += 2
     ctx.counters["bytes_out"] += meta["bytes_out"]
     ctx.last_call = meta
+
+
+def _small_allreduce_call(ctx: ShmemContext, plan, out: torch.Tensor) -> torch.Tensor:
+    """Both launches of a planned few-row call: the kept argument block of the split-K product, then the tail."""
+    cm.launch(plan[0], ctx.device)
+    _small_allreduce_tail(ctx, plan, out)
     return out
 
 
@@ -441,23 +446,6 @@ def _small_allreduce(ctx: ShmemContext, a: torch.Tensor, b: torch.Tensor, trans_
         # the product is already queued: only the second launch is left for this call
         _small_allreduce_tail(ctx, plan, out)
     return out, (None if copied else plan)
-
-
-def _small_allreduce_tail(ctx: ShmemContext, plan, out: torch.Tensor) -> None:
-    """The second launch alone (the first call of a shape queues its product through the op layer)."""
-    _, fixed, part_base, parity_bytes, flags_off, meta = plan
-    epoch = ctx.epoch + 1
-    stream = torch.cuda.current_stream(ctx.device).cuda_stream
-    nctx, parts_ptr, s, slice_elems, m, n, row0, rows, fmt = fixed
-    N.check(N.lib().catcoc_splitk_allreduce(C.byref(nctx), parts_ptr, s, slice_elems, m, n, row0, rows, out.data_ptr(),
-                                            out.stride(0), fmt, part_base + (epoch & 1) * parity_bytes, flags_off,
-                                            1 if ctx.mc_base else 0, ctx.launch_state.data_ptr(),
-                                            ctx.launch_state.data_ptr() + 4, ctx.status.data_ptr(),
-                                            cm.default_timeout_ns(), C.c_void_p(stream)))
-    ctx.epoch = epoch
-    ctx.counters["launches"] += 2
-    ctx.counters["bytes_out"] += meta["bytes_out"]
-    ctx.last_call = meta
 
 
 # ---------------------------------------------------------------------------------------
