@@ -336,7 +336,13 @@ def splitk_matmul(a: torch.Tensor, b: torch.Tensor, *, split_k: Optional[int] = 
     if out_dtype is None:
         out_dtype = out.dtype if out is not None else (a.dtype if a.dtype in (torch.float16, torch.bfloat16)
                                                        else torch.bfloat16)
-    s = split_k if split_k is not None else pick_split_k(m, n, k, elt)
+    if split_k is None and tiling is None:
+        # tile width and slice count together: the fewest operand bytes per CTA with every SM busy
+        s, bn = splitk_plan(m, n, k, elt)
+        if m % 128 == 0 or bn <= 128:
+            tiling = TilingConfig(bn=bn, cta_pair=1)
+    else:
+        s = split_k if split_k is not None else pick_split_k(m, n, k, elt)
     if slice_k(k, s, elt)[1] <= 1:
         return matmul(a, b, trans_a=trans_a, trans_b=trans_b, out=out, out_dtype=out_dtype, tiling=tiling,
                       alpha=alpha, beta=beta, c=c, bias_f32=bias_f32)
