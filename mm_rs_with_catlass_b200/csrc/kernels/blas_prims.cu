@@ -146,19 +146,19 @@ __global__ void gemv_cols_kernel(const void* __restrict__ A, int64_t lda, int fm
   float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
   int r = r0;
   if (vec) {
-    // four rows per step: their loads are independent, so four 16-byte requests are in flight
+    // eight rows per step: their loads are independent, so eight 16-byte requests are in flight per thread
     const uint8_t* col = static_cast<const uint8_t*>(A) + static_cast<int64_t>(c0) * elt;
     const int64_t pitch = lda * elt;
-    for (; r + 4 <= r1; r += 4) {
-      uint4 w[4];
-      float xv[4];
+    for (; r + 8 <= r1; r += 8) {
+      uint4 w[8];
+      float xv[8];
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
+      for (int j = 0; j < 8; ++j) {
         w[j] = ldg_v4(col + (r + j) * pitch);
         xv[j] = load_elem(x, r + j, fmt);
       }
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
+      for (int j = 0; j < 8; ++j) {
         float fa[8];
         unpack_word(w[j], fmt, fa);
 #pragma unroll
