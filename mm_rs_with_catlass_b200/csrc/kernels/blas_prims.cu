@@ -102,7 +102,26 @@ __global__ void gemv_rows_kernel(const void* __restrict__ A, int64_t lda, int fm
     int c = 0;
     if (vec) {
       const int nvec = cols / per;
-      for (int v = t; v < nvec; v += TPR) {
+      int v = t;
+      // four independent 16-byte loads of A in flight per thread (x comes from L1 / L2)
+      for (; v + 3 * TPR < nvec; v += 4 * TPR) {
+        uint4 wa[4], wx[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          wa[j] = ldg_v4(row + static_cast<int64_t>(v + j * TPR) * 16);
+          wx[j] = ldg_v4(static_cast<const uint8_t*>(x) + static_cast<int64_t>(v + j * TPR) * 16);
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          float fa[8], fx[8];
+          unpack_word(wa[j], fmt, fa);
+          unpack_word(wx[j], fmt, fx);
+#pragma unroll
+          for (int i = 0; i < 8; ++i)
+            if (i < per) acc += fa[i] * fx[i];
+        }
+      }
+      for (; v < nvec; v += TPR) {
         float fa[8], fx[8];
         unpack_word(ldg_v4(row + static_cast<int64_t>(v) * 16), fmt, fa);
         unpack_word(ldg_v4(static_cast<const uint8_t*>(x) + static_cast<int64_t>(v) * 16), fmt, fx);
