@@ -258,9 +258,16 @@ extern "C" int catcoc_gemv(const void* A, int64_t lda, int fmt, int rows, int co
   const int elt = (fmt == CATCOC_FMT_F32) ? 4 : 2;
   const int per = 16 / elt;
   const int col_groups = (cols + per - 1) / per;
-  const int chunks = (rows + 127) / 128;
-  dim3 grid((col_groups + 127) / 128, chunks, 1);
-  gemv_cols_kernel<<<grid, 128, 0, st>>>(A, lda, fmt, rows, cols, x, workspace, 128);
+  // Row chunks of at least 128 rows (what the workspace is sized for), longer when that still leaves about six blocks
+  // per SM: fewer partial rows to write and fold.
+  const int col_blocks = (col_groups + 127) / 128;
+  int want_chunks = (148 * 6 + col_blocks - 1) / col_blocks;
+  if (want_chunks < 1) want_chunks = 1;
+  int rpc = ((rows + want_chunks - 1) / want_chunks + 7) / 8 * 8;
+  if (rpc < 128) rpc = 128;
+  const int chunks = (rows + rpc - 1) / rpc;
+  dim3 grid(col_blocks, chunks, 1);
+  gemv_cols_kernel<<<grid, 128, 0, st>>>(A, lda, fmt, rows, cols, x, workspace, rpc);
   CATCOC_CUDA_OK(cudaGetLastError());
   // y = alpha * sum_chunks part + beta * y_in, as a [1, cols] split-K reduction
   const int64_t slice = cols;   // a width that is not a multiple of 4 is reduced with scalar loads
