@@ -119,3 +119,53 @@ def test_shape_lists_parse():
     ref = read_shapes(os.path.join(d, "reference_shapes.csv"))
     assert (16384, 27392, 4096, 0, 0) in ref and (8144, 5120, 1696, 0, 1) in ref and len(ref) == 9
     assert read_shapes(os.path.join(d, "reference_shapes.csv"), start_line=1, rows=2) == ref[1:3]
+
+
+def test_few_row_collectives_size_their_stamps_and_check_arguments_without_a_gpu():
+    lib = N.lib()
+    # one stamp word per (chunk of 2048 elements, source)
+    assert lib.catcoc_splitk_allreduce_flag_words(128, 8192, 4) == (128 * 8192 // 2048) * 4
+    assert lib.catcoc_splitk_allreduce_flag_words(1, 128, 8) == 8
+    # one per (chunk of 256 sixteen-byte vectors, source)
+    assert lib.catcoc_small_allgather_flag_words(16, 8192 * 2, 8) == (16 * 1024 // 256) * 8
+    assert lib.catcoc_small_allgather_flag_words(1, 16, 2) == 2
+    ctx = N.ShmemCtx()
+    ctx.rank, ctx.W = 0, 2
+    dummy = C.c_void_p(4096)                     # never dereferenced: every call below is refused before a launch
+    words = (C.c_uint32 * 8)()
+    # a world of one has nothing to reduce
+    one = N.ShmemCtx()
+    one.rank, one.W = 0, 1
+    assert lib.catcoc_splitk_allreduce(C.byref(one), dummy, 2, 128 * 256, 128, 256, 0, 128, dummy, 256, N.FMT_BF16, 0, 0, 0,
+                                       words, words, words, 0, None) == N.E_BAD_ARG
+    # rows outside the matrix, rows that are not whole 16-byte vectors, an fp32 output
+    assert lib.catcoc_splitk_allreduce(C.byref(ctx), dummy, 2, 128 * 256, 128, 256, 100, 64, dummy, 256, N.FMT_BF16, 0, 0, 0,
+                                       words, words, words, 0, None) == N.E_BAD_ARG
+    assert lib.catcoc_splitk_allreduce(C.byref(ctx), dummy, 2, 128 * 250, 128, 250, 0, 128, dummy, 250, N.FMT_BF16, 0, 0, 0,
+                                       words, words, words, 0, None) == N.E_ALIGNMENT
+    assert lib.catcoc_splitk_allreduce(C.byref(ctx), dummy, 2, 128 * 256, 128, 256, 0, 128, dummy, 256, N.FMT_F32, 0, 0, 0,
+                                       words, words, words, 0, None) == N.E_UNSUPPORTED
+    assert "fp16 / bf16" in N.last_error()
+    # gather: a row length or a pitch that is not a multiple of 16 bytes
+    assert lib.catcoc_small_allgather(C.byref(ctx), dummy, 1040, 8, 1030, 0, 1040, 0, 0, words, words, words, 0, None) == N.E_ALIGNMENT
+    assert lib.catcoc_small_allgather(C.byref(ctx), dummy, 1032, 8, 1024, 0, 1024, 0, 0, words, words, words, 0, None) == N.E_ALIGNMENT
+    assert lib.catcoc_small_allgather(C.byref(ctx), dummy, 1024, 0, 1024, 0, 1024, 0, 0, words, words, words, 0, None) == N.E_BAD_ARG
+
+
+def test_attention_entry_points_refuse_bad_arguments_without_a_gpu():
+    lib = N.lib()
+    dummy = C.c_void_p(4096)
+    words = (C.c_uint32 * 8)()
+    args = lambda d, hq, hk, sq, sk, causal, scale: (dummy, dummy, dummy, dummy, 1, hq, hk, sq, sk, d, N.FMT_BF16, causal, scale,
+                                                     words, 0, None)
+    assert lib.catcoc_flash_attention(*args(96, 2, 2, 16, 16, 0, 0.1)) == N.E_UNSUPPORTED      # head dimension
+    assert lib.catcoc_flash_attention(*args(128, 3, 2, 16, 16, 0, 0.1)) == N.E_BAD_ARG         # heads do not divide
+    assert lib.catcoc_flash_attention(*args(128, 2, 2, 16, 8, 1, 0.1)) == N.E_BAD_ARG          # causal with Sk < Sq
+    assert lib.catcoc_flash_attention(*args(128, 2, 2, 16, 16, 0, -0.1)) == N.E_UNSUPPORTED    # the scale must be positive
+    assert lib.catcoc_mla_workspace_bytes(4, 1, 16, 1) == 0
+    assert lib.catcoc_mla_workspace_bytes(4, 2, 16, 3) == 3 * (4 * 2 * 16) * (512 + 2) * 4
+    mla = lambda q_len, splits, ws: lib.catcoc_mla_decode(dummy, dummy, dummy, dummy, dummy, dummy, dummy, ws, 2, q_len, 16, 8, 4,
+                                                          N.FMT_BF16, 0, 0.05, splits, words, 0, None)
+    assert mla(5, 1, None) == N.E_UNSUPPORTED                                                  # 1 to 4 new tokens
+    assert mla(1, 3, None) == N.E_BAD_ARG                                                      # slices need the workspace
+    assert mla(1, 100, dummy) == N.E_BAD_ARG
