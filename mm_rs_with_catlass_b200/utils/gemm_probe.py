@@ -3,8 +3,10 @@ profiler captures and quick timing.
 
     python -m mm_rs_with_catlass_b200.utils.gemm_probe M N K [--trans-b] [--pair 1|2] [--bn 256]
                                                       [--dtype bf16|fp16|int8] [--launches 3] [--time] [--trace]
+                                                      [--split-k S]
 
-``--time`` prints CUDA-event time and the cuBLAS time of the same shape; ``--trace`` prints the
+``--split-k S`` runs the split-K form (K slices as the groups of one launch + the plane reduction;
+``S = 0`` lets the library pick tile width and slice count). ``--time`` prints CUDA-event time and the cuBLAS time of the same shape; ``--trace`` prints the
 kernel's per-role cycle counters (see ``FusedParams::trace`` in csrc/include/catcoc/params.h).
 """
 from __future__ import annotations
@@ -31,6 +33,7 @@ def main(argv=None) -> int:
     ap.add_argument("--launches", type=int, default=3)
     ap.add_argument("--time", action="store_true")
     ap.add_argument("--trace", action="store_true")
+    ap.add_argument("--split-k", type=int, default=None)
     a = ap.parse_args(argv)
 
     from mm_rs_with_catlass_b200 import TilingConfig
@@ -48,7 +51,13 @@ def main(argv=None) -> int:
         B = (torch.randn((a.n, a.k) if a.trans_b else (a.k, a.n), device=dev) * 0.02).to(dt)
         out = torch.empty((a.m, a.n), dtype=dt, device=dev)
     cfg = TilingConfig(cta_pair=a.pair, bn=a.bn)
-    run = lambda trace=None: matmul(A, B, trans_b=a.trans_b, out=out, tiling=cfg, trace=trace)
+    if a.split_k is not None and dt != torch.int8:
+        from mm_rs_with_catlass_b200.ops.blas import splitk_matmul
+        explicit = a.bn or a.pair != 1
+        run = lambda trace=None: splitk_matmul(A, B, trans_b=a.trans_b, out=out, split_k=a.split_k or None,
+                                               tiling=cfg if explicit else None)
+    else:
+        run = lambda trace=None: matmul(A, B, trans_b=a.trans_b, out=out, tiling=cfg, trace=trace)
     for _ in range(a.launches):
         run()
     torch.cuda.synchronize()
